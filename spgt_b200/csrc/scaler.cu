@@ -1,0 +1,165 @@
+// Interpolation kernels of the down- and up-scaler (bilinear, align_corners=True, NHWC), fused with the
+// neighbouring element-wise work.  All are bandwidth-bound gather + lerp kernels with 16-byte accesses.
+#include "common.cuh"
+
+namespace spgt {
+
+// Source coordinate exactly as ATen computes it in fp32: scale = (in-1)/(out-1), src = scale*dst,
+// i0 = min(int(src), in-1), lambda = clamp(src - i0, 0, 1), i1 = i0 + (i0 < in-1).
+struct Tap { int i0, i1; float w0, w1; };
+__device__ __forceinline__ Tap make_tap(int dst, int in_size, int out_size) {
+    Tap tp;
+    if (in_size == out_size) { tp.i0 = tp.i1 = dst; tp.w0 = 1.0f; tp.w1 = 0.0f; return tp; }
+    const float scale = out_size > 1 ? (float)(in_size - 1) / (float)(out_size - 1) : 0.0f;
+    const float src = scale * (float)dst;
+    int i0 = (int)src;
+    if (i0 > in_size - 1) i0 = in_size - 1;
+    float lam = src - (float)i0;
+    lam = fminf(fmaxf(lam, 0.0f), 1.0f);
+    tp.i0 = i0; tp.i1 = i0 + (i0 < in_size - 1 ? 1 : 0); tp.w1 = lam; tp.w0 = 1.0f - lam;
+    return tp;
+}
+
+__global__ void __launch_bounds__(256)
+bilinear_kernel(const float4* __restrict__ x, float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int C4, int act,
+                int64_t total) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C4);
+        int64_t p = i / C4;
+        const int xo = (int)(p % Wo); p /= Wo;
+        const int yo = (int)(p % Ho);
+        const int64_t b = p / Ho;
+        const Tap ty = make_tap(yo, Hi, Ho), tx = make_tap(xo, Wi, Wo);
+        const float4* base = x + b * (int64_t)Hi * Wi * C4 + c;
+        const float4 v00 = __ldg(base + ((int64_t)ty.i0 * Wi + tx.i0) * C4);
+        const float4 v01 = __ldg(base + ((int64_t)ty.i0 * Wi + tx.i1) * C4);
+        const float4 v10 = __ldg(base + ((int64_t)ty.i1 * Wi + tx.i0) * C4);
+        const float4 v11 = __ldg(base + ((int64_t)ty.i1 * Wi + tx.i1) * C4);
+        const float w00 = ty.w0 * tx.w0, w01 = ty.w0 * tx.w1, w10 = ty.w1 * tx.w0, w11 = ty.w1 * tx.w1;
+        float4 o;
+        o.x = apply_act(v00.x * w00 + v01.x * w01 + v10.x * w10 + v11.x * w11, act);
+        o.y = apply_act(v00.y * w00 + v01.y * w01 + v10.y * w10 + v11.y * w11, act);
+        o.z = apply_act(v00.z * w00 + v01.z * w01 + v10.z * w10 + v11.z * w11, act);
+        o.w = apply_act(v00.w * w00 + v01.w * w01 + v10.w * w10 + v11.w * w11, act);
+        y[i] = o;
+    }
+}
+
+// y[b,yo,xo,c] = act( lerp over the 4 taps of act(conv3x3(node)[tap] + bias[c]) ).  One thread per (pixel, channel):
+// the 4x4 input patch of a pixel is shared by all channel-threads of the warp (broadcast loads), each thread keeps
+// its 9 weights in registers.  A block walks PIX consecutive output pixels.
+constexpr int C0_PIX = 8;
+__global__ void __launch_bounds__(128)
+conv0_down_kernel(const float* __restrict__ node, const float* __restrict__ w, const float* __restrict__ bias,
+                  float* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int Cout, int act, int64_t npix) {
+    for (int c = threadIdx.x; c < Cout; c += blockDim.x) {
+        float wk[9];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) wk[k] = __ldg(w + k * Cout + c);
+        const float bc = __ldg(bias + c);
+        for (int pi = 0; pi < C0_PIX; ++pi) {
+            const int64_t p = (int64_t)blockIdx.x * C0_PIX + pi;
+            if (p >= npix) break;
+            const int xo = (int)(p % Wo);
+            const int yo = (int)((p / Wo) % Ho);
+            const int64_t b = p / ((int64_t)Wo * Ho);
+            const Tap ty = make_tap(yo, Hi, Ho), tx = make_tap(xo, Wi, Wo);
+            const float* img = node + b * (int64_t)Hi * Wi;
+            float conv[2][2];
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int d = 0; d < 2; ++d) {
+                    const int cy = a ? ty.i1 : ty.i0, cx = d ? tx.i1 : tx.i0;
+                    float s = bc;
+#pragma unroll
+                    for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+                        for (int kx = 0; kx < 3; ++kx) {
+                            const int yy = cy + ky - 1, xx = cx + kx - 1;
+                            const float v = (yy >= 0 && yy < Hi && xx >= 0 && xx < Wi) ? __ldg(img + (int64_t)yy * Wi + xx) : 0.0f;
+                            s = fmaf(v, wk[ky * 3 + kx], s);
+                        }
+                    conv[a][d] = apply_act(s, act);
+                }
+            const float o = conv[0][0] * (ty.w0 * tx.w0) + conv[0][1] * (ty.w0 * tx.w1) + conv[1][0] * (ty.w1 * tx.w0) +
+                            conv[1][1] * (ty.w1 * tx.w1);
+            y[p * Cout + c] = apply_act(o, act);
+        }
+    }
+}
+
+// y[b,yo,xo,:] = bilinear(uw)[b,yo,xo,:] + grid[b,yo,xo,0]*wg[0,:] + grid[b,yo,xo,1]*wg[1,:] + bias
+__global__ void __launch_bounds__(256)
+upsample_grid_kernel(const float4* __restrict__ uw, const float2* __restrict__ grid, const float4* __restrict__ wg,
+                     const float4* __restrict__ bias, float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int C4,
+                     int64_t total) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C4);
+        const int64_t pix = i / C4;
+        int64_t p = pix;
+        const int xo = (int)(p % Wo); p /= Wo;
+        const int yo = (int)(p % Ho);
+        const int64_t b = p / Ho;
+        const Tap ty = make_tap(yo, Hi, Ho), tx = make_tap(xo, Wi, Wo);
+        const float4* base = uw + b * (int64_t)Hi * Wi * C4 + c;
+        const float4 v00 = __ldg(base + ((int64_t)ty.i0 * Wi + tx.i0) * C4);
+        const float4 v01 = __ldg(base + ((int64_t)ty.i0 * Wi + tx.i1) * C4);
+        const float4 v10 = __ldg(base + ((int64_t)ty.i1 * Wi + tx.i0) * C4);
+        const float4 v11 = __ldg(base + ((int64_t)ty.i1 * Wi + tx.i1) * C4);
+        const float w00 = ty.w0 * tx.w0, w01 = ty.w0 * tx.w1, w10 = ty.w1 * tx.w0, w11 = ty.w1 * tx.w1;
+        const float2 gxy = __ldg(grid + pix);
+        const float4 g0 = __ldg(wg + c), g1 = __ldg(wg + C4 + c), bb = __ldg(bias + c);
+        float4 o;
+        o.x = v00.x * w00 + v01.x * w01 + v10.x * w10 + v11.x * w11 + gxy.x * g0.x + gxy.y * g1.x + bb.x;
+        o.y = v00.y * w00 + v01.y * w01 + v10.y * w10 + v11.y * w11 + gxy.x * g0.y + gxy.y * g1.y + bb.y;
+        o.z = v00.z * w00 + v01.z * w01 + v10.z * w10 + v11.z * w11 + gxy.x * g0.z + gxy.y * g1.z + bb.z;
+        o.w = v00.w * w00 + v01.w * w01 + v10.w * w10 + v11.w * w11 + gxy.x * g0.w + gxy.y * g1.w + bb.w;
+        y[i] = o;
+    }
+}
+
+static unsigned grid_for(int64_t items, int threads, int per_sm) {
+    const int64_t want = ceil_div(items, (int64_t)threads);
+    const int64_t cap = (int64_t)num_sms() * per_sm;
+    return (unsigned)(want < cap ? want : cap);
+}
+
+}  // namespace spgt
+
+using namespace spgt;
+
+extern "C" int spgt_bilinear_fwd(const float* x, float* y, int B, int Hi, int Wi, int Ho, int Wo, int C, int act,
+                                 spgt_stream_t stream) {
+    if (!x || !y) return SPGT_ERR_NULL;
+    if (B <= 0 || Hi <= 0 || Wi <= 0 || Ho <= 0 || Wo <= 0 || C <= 0 || (C & 3) || act < 0 || act > 3) return SPGT_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(y)) return SPGT_ERR_ALIGN;
+    const int64_t total = (int64_t)B * Ho * Wo * (C / 4);
+    bilinear_kernel<<<grid_for(total, 256, 16), 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), Hi, Wi, Ho, Wo, C / 4, act, total);
+    return launch_status();
+}
+
+extern "C" int spgt_conv0_down_fwd(const float* node, const float* w, const float* bias, float* y, int B, int Hi, int Wi,
+                                   int Ho, int Wo, int Cout, int act, spgt_stream_t stream) {
+    if (!node || !w || !bias || !y) return SPGT_ERR_NULL;
+    if (B <= 0 || Hi <= 0 || Wi <= 0 || Ho <= 0 || Wo <= 0 || Cout <= 0 || (Cout & 3) || Cout > 512 || act < 0 || act > 3)
+        return SPGT_ERR_SHAPE;
+    const int64_t npix = (int64_t)B * Ho * Wo;
+    const int64_t blocks = ceil_div(npix, (int64_t)C0_PIX);
+    if (blocks > 0x7fffffffLL) return SPGT_ERR_SHAPE;
+    conv0_down_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(node, w, bias, y, Hi, Wi, Ho, Wo, Cout, act, npix);
+    return launch_status();
+}
+
+extern "C" int spgt_upsample_grid_fwd(const float* uw, const float* grid, const float* wg, const float* bias, float* y,
+                                      int B, int Hi, int Wi, int Ho, int Wo, int C, spgt_stream_t stream) {
+    if (!uw || !grid || !wg || !bias || !y) return SPGT_ERR_NULL;
+    if (B <= 0 || Hi <= 0 || Wi <= 0 || Ho <= 0 || Wo <= 0 || C <= 0 || (C & 3)) return SPGT_ERR_SHAPE;
+    if (!aligned16(uw) || !aligned16(grid) || !aligned16(wg) || !aligned16(bias) || !aligned16(y)) return SPGT_ERR_ALIGN;
+    const int64_t total = (int64_t)B * Ho * Wo * (C / 4);
+    upsample_grid_kernel<<<grid_for(total, 256, 16), 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const float4*>(uw), reinterpret_cast<const float2*>(grid), reinterpret_cast<const float4*>(wg),
+        reinterpret_cast<const float4*>(bias), reinterpret_cast<float4*>(y), Hi, Wi, Ho, Wo, C / 4, total);
+    return launch_status();
+}

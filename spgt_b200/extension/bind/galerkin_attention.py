@@ -1,0 +1,35 @@
+"""Drop-in for the reference's extension/bind/galerkin_attention.py (forward / inference only).
+
+Same function names, argument order and tensor layouts as the reference's public functions
+(extension/bind/galerkin_attention.py:87-107); the work is done by the sm_100a kernels of libspgt_b200.so
+instead of a JIT-built pybind module.  Inputs must be contiguous fp32 CUDA tensors: the reference reads raw
+data pointers without checking, here a wrong device, dtype or layout raises.
+"""
+from torch import Tensor
+
+from ... import ops
+
+
+def multihead_projection_with_position_rrc_cuda(
+    input: Tensor, weight: Tensor, bias: Tensor, position: Tensor, num_head, dim_head, dim_position
+) -> Tensor:
+    """[B,S,D] -> [B, num_head, dim_position + dim_head, S]; computes input @ weight (weight used as [k][n])."""
+    return ops.projpos(input, weight, bias, position, num_head, dim_head, dim_position)
+
+
+def multihead_projection_layernorm_with_position_rrc_cuda(
+    input: Tensor, weight: Tensor, bias: Tensor, ln_weight: Tensor, ln_bias: Tensor, position: Tensor,
+    norm_eps, num_head, dim_head, dim_position
+) -> Tensor:
+    """As above with a LayerNorm over each head's channels; position rows are not normalised."""
+    return ops.projpos_lnorm(input, weight, bias, ln_weight, ln_bias, position, norm_eps, num_head, dim_head, dim_position)
+
+
+def multihead_galerkin_attention_cccr_cuda(Q: Tensor, K: Tensor, V: Tensor) -> Tensor:
+    """Q,K,V [B,H,d_posk,S] -> [B,H,S,d_posk] = Q^T (K V^T / S)."""
+    return ops.galerkin_attention(Q, K, V)
+
+
+def batched_skinny_gemm(A: Tensor, B: Tensor, alpha: float = 1.0) -> Tensor:
+    """[...,M,K] @ [...,K,N] * alpha with K the long dimension."""
+    return ops.batched_skinny_gemm(A, B, alpha)

@@ -1,0 +1,293 @@
+"""Tensor-level wrappers of the C ABI: torch supplies device memory and the current stream, nothing else.
+
+Every function checks device, dtype and contiguity (the kernels read raw pointers), allocates its output with
+torch.empty on the input's device and launches on torch's current stream.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence, Tuple
+
+import torch
+from torch import Tensor
+
+from ._lib import lib, check
+
+ACT = {None: 0, 'none': 0, 'relu': 1, 'silu': 2, 'silu2': 3}
+
+
+def act_code(name) -> int:
+    """The reference selects SiLU for 'silu' and ReLU for any other string (network/layer.py:14,163)."""
+    if name in ACT:
+        return ACT[name]
+    return 1
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(t: Tensor, name: str, dtype=torch.float32) -> Tensor:
+    if not isinstance(t, Tensor):
+        raise TypeError(f'{name} must be a torch.Tensor')
+    if not t.is_cuda:
+        raise ValueError(f'{name} must be a CUDA tensor (spgt_b200 has no CPU path)')
+    if t.dtype != dtype:
+        raise TypeError(f'{name} must be {dtype}, got {t.dtype}')
+    if not t.is_contiguous():
+        raise ValueError(f'{name} must be contiguous')
+    return t
+
+
+def _p(t: Optional[Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# attention ops
+# ---------------------------------------------------------------------------------------------------------
+def projpos(x: Tensor, weight: Tensor, bias: Optional[Tensor], position: Tensor, num_head: int, dim_head: int,
+            dim_position: int) -> Tensor:
+    _chk(x, 'input'); _chk(weight, 'weight'); _chk(position, 'position')
+    if bias is not None:
+        _chk(bias, 'bias')
+    B, S, D = x.shape
+    out = torch.empty(B, num_head, dim_position + dim_head, S, device=x.device, dtype=x.dtype)
+    with torch.cuda.device(x.device):
+        check(lib.spgt_projpos_fwd(x.data_ptr(), weight.data_ptr(), _p(bias), position.data_ptr(), out.data_ptr(),
+                                   B, S, D, num_head, dim_head, dim_position, _stream()), 'spgt_projpos_fwd')
+    return out
+
+
+def projpos_lnorm(x: Tensor, weight: Tensor, bias: Optional[Tensor], ln_weight: Tensor, ln_bias: Tensor,
+                  position: Tensor, norm_eps: float, num_head: int, dim_head: int, dim_position: int,
+                  return_invsigma: bool = False):
+    _chk(x, 'input'); _chk(weight, 'weight'); _chk(position, 'position'); _chk(ln_weight, 'ln_weight'); _chk(ln_bias, 'ln_bias')
+    if bias is not None:
+        _chk(bias, 'bias')
+    B, S, D = x.shape
+    out = torch.empty(B, num_head, dim_position + dim_head, S, device=x.device, dtype=x.dtype)
+    inv = torch.empty(B, num_head, S, device=x.device, dtype=x.dtype) if return_invsigma else None
+    with torch.cuda.device(x.device):
+        check(lib.spgt_projpos_lnorm_fwd(x.data_ptr(), weight.data_ptr(), _p(bias), ln_weight.data_ptr(), ln_bias.data_ptr(),
+                                         float(norm_eps), position.data_ptr(), out.data_ptr(), _p(inv),
+                                         B, S, D, num_head, dim_head, dim_position, _stream()), 'spgt_projpos_lnorm_fwd')
+    return (out, inv) if return_invsigma else out
+
+
+def projpos_qkv(x, wq, bq, wk, bk, wv, bv, lnwk, lnbk, lnwv, lnbv, eps, position, num_head, dim_head, dim_position):
+    for n, t in (('x', x), ('wq', wq), ('wk', wk), ('wv', wv), ('position', position)):
+        _chk(t, n)
+    B, S, D = x.shape
+    q, k, v = (torch.empty(B, num_head, dim_position + dim_head, S, device=x.device, dtype=x.dtype) for _ in range(3))
+    with torch.cuda.device(x.device):
+        check(lib.spgt_projpos_qkv_fwd(x.data_ptr(), wq.data_ptr(), _p(bq), wk.data_ptr(), _p(bk), wv.data_ptr(), _p(bv),
+                                       lnwk.data_ptr(), lnbk.data_ptr(), lnwv.data_ptr(), lnbv.data_ptr(), float(eps),
+                                       position.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                       B, S, D, num_head, dim_head, dim_position, _stream()), 'spgt_projpos_qkv_fwd')
+    return q, k, v
+
+
+def galerkin_attention(Q: Tensor, K: Tensor, V: Tensor, merged_heads: bool = False, return_kv: bool = False):
+    _chk(Q, 'Q'); _chk(K, 'K'); _chk(V, 'V')
+    if Q.dim() != 4 or Q.shape != K.shape or Q.shape != V.shape:
+        raise ValueError('Q, K, V must share the shape [batch, num_head, d_posk, seqlen]')
+    B, H, dpk, S = Q.shape
+    shape = (B, S, H * dpk) if merged_heads else (B, H, S, dpk)
+    out = torch.empty(shape, device=Q.device, dtype=Q.dtype)
+    T = torch.empty(B, H, dpk, dpk, device=Q.device, dtype=Q.dtype) if return_kv else None
+    with torch.cuda.device(Q.device):
+        check(lib.spgt_galerkin_attn_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), _p(T),
+                                         B, H, dpk, S, int(merged_heads), _stream()), 'spgt_galerkin_attn_fwd')
+    return (out, T) if return_kv else out
+
+
+def skinny_gemm_workspace_bytes(M: int, N: int, K: int, batch: int) -> int:
+    return int(lib.spgt_skinny_gemm_workspace_bytes(M, N, K, batch))
+
+
+def batched_skinny_gemm(A: Tensor, Bm: Tensor, alpha: float = 1.0, workspace: Optional[Tensor] = None) -> Tensor:
+    _chk(A, 'A'); _chk(Bm, 'B')
+    if A.dim() < 2 or A.dim() != Bm.dim() or A.shape[:-2] != Bm.shape[:-2] or A.shape[-1] != Bm.shape[-2]:
+        raise ValueError('A must be [..., M, K] and B [..., K, N] with equal batch dims')
+    M, K, N = A.shape[-2], A.shape[-1], Bm.shape[-1]
+    batch = int(math.prod(A.shape[:-2]))
+    Cm = torch.empty(*A.shape[:-2], M, N, device=A.device, dtype=A.dtype)
+    need = skinny_gemm_workspace_bytes(M, N, K, batch)
+    if workspace is None:
+        workspace = torch.empty(need, device=A.device, dtype=torch.uint8)
+    with torch.cuda.device(A.device):
+        check(lib.spgt_batched_skinny_gemm(A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(), float(alpha), M, N, K, batch,
+                                           workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream()),
+              'spgt_batched_skinny_gemm')
+    return Cm
+
+
+# ---------------------------------------------------------------------------------------------------------
+# data movement
+# ---------------------------------------------------------------------------------------------------------
+def batched_transpose(X: Tensor, batch_list: Sequence[int], M_list: Sequence[int], N_list: Sequence[int]) -> Tensor:
+    _chk(X, 'X')
+    b, M, N = math.prod(batch_list), math.prod(M_list), math.prod(N_list)
+    if X.numel() != b * M * N:
+        raise ValueError('X does not have prod(batch)*prod(M)*prod(N) elements')
+    out = torch.empty(*batch_list, *N_list, *M_list, device=X.device, dtype=X.dtype)
+    with torch.cuda.device(X.device):
+        check(lib.spgt_batched_transpose(X.data_ptr(), out.data_ptr(), M, N, b, _stream()), 'spgt_batched_transpose')
+    return out
+
+
+def transpose_gather_dual(src: Tensor, dim_list, H_all, W_all, H_low, W_low, hb1, wb1, hb2, wb2) -> Tuple[Tensor, Tensor]:
+    _chk(src, 'src', torch.complex64)
+    dim = math.prod(dim_list)
+    if src.numel() != dim * H_all * W_all:
+        raise ValueError('src does not have prod(dim)*H_all*W_all elements')
+    o1 = torch.empty(H_low, W_low, *dim_list, device=src.device, dtype=src.dtype)
+    o2 = torch.empty_like(o1)
+    with torch.cuda.device(src.device):
+        check(lib.spgt_transpose_gather_dual(src.data_ptr(), o1.data_ptr(), o2.data_ptr(), dim, H_all, W_all, H_low, W_low,
+                                             hb1, wb1, hb2, wb2, _stream()), 'spgt_transpose_gather_dual')
+    return o1, o2
+
+
+def transpose_scatter_dual(src1: Tensor, src2: Tensor, dim_list, H_all, W_all, H_low, W_low, hb1, wb1, hb2, wb2) -> Tensor:
+    _chk(src1, 'src1', torch.complex64); _chk(src2, 'src2', torch.complex64)
+    dim = math.prod(dim_list)
+    if src1.numel() != dim * H_low * W_low or src2.numel() != src1.numel():
+        raise ValueError('src1/src2 do not have H_low*W_low*prod(dim) elements')
+    out = torch.empty(*dim_list, H_all, W_all, device=src1.device, dtype=src1.dtype)
+    with torch.cuda.device(src1.device):
+        check(lib.spgt_transpose_scatter_dual(src1.data_ptr(), src2.data_ptr(), out.data_ptr(), dim, H_all, W_all,
+                                              H_low, W_low, hb1, wb1, hb2, wb2, _stream()), 'spgt_transpose_scatter_dual')
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# dense layers
+# ---------------------------------------------------------------------------------------------------------
+def pad_cols(w: Tensor, multiple: int = 4) -> Tensor:
+    """[K, N] -> contiguous [K, ceil(N/multiple)*multiple] with zero columns appended (kernel weight pitch rule)."""
+    K, N = w.shape
+    Np = (N + multiple - 1) // multiple * multiple
+    if Np == N:
+        return w.contiguous()
+    out = torch.zeros(K, Np, device=w.device, dtype=w.dtype)
+    out[:, :N] = w
+    return out
+
+
+def linear(x: Tensor, w_kn: Tensor, bias: Optional[Tensor], N: int, act=None, residual: Optional[Tensor] = None,
+           out: Optional[Tensor] = None) -> Tensor:
+    """y = act(x @ w_kn[:, :N] + bias) (+ residual).  x [..., K] contiguous, w_kn [K, ldw] (ldw % 4 == 0)."""
+    _chk(x, 'x'); _chk(w_kn, 'weight')
+    K = x.shape[-1]
+    rows = x.numel() // K
+    if w_kn.shape[0] != K:
+        raise ValueError('weight must be [K, ldw]')
+    if out is None:
+        out = torch.empty(*x.shape[:-1], N, device=x.device, dtype=x.dtype)
+    if residual is not None:
+        _chk(residual, 'residual')
+    with torch.cuda.device(x.device):
+        check(lib.spgt_linear_fwd(x.data_ptr(), K, w_kn.data_ptr(), w_kn.shape[1], _p(bias), _p(residual), N,
+                                  out.data_ptr(), N, rows, K, N, act_code(act), _stream()), 'spgt_linear_fwd')
+    return out
+
+
+def conv3x3(x: Tensor, cin_off: int, Cin: int, w_kn: Tensor, bias: Tensor, y: Tensor, cout_off: int, Cout: int, act) -> Tensor:
+    """NHWC 3x3 convolution reading channels [cin_off, cin_off+Cin) of x and writing [cout_off, cout_off+Cout) of y."""
+    _chk(x, 'x'); _chk(w_kn, 'weight'); _chk(y, 'y'); _chk(bias, 'bias')
+    B, Hh, Ww, cp = x.shape
+    if y.shape[:3] != x.shape[:3]:
+        raise ValueError('x and y must share [B, H, W]')
+    with torch.cuda.device(x.device):
+        check(lib.spgt_conv3x3_fwd(x.data_ptr(), cp, cin_off, Cin, w_kn.data_ptr(), w_kn.shape[1], bias.data_ptr(),
+                                   y.data_ptr(), y.shape[3], cout_off, Cout, B, Hh, Ww, act_code(act), _stream()),
+              'spgt_conv3x3_fwd')
+    return y
+
+
+def bilinear(x: Tensor, Ho: int, Wo: int, act=None) -> Tensor:
+    _chk(x, 'x')
+    B, Hi, Wi, Cc = x.shape
+    y = torch.empty(B, Ho, Wo, Cc, device=x.device, dtype=x.dtype)
+    with torch.cuda.device(x.device):
+        check(lib.spgt_bilinear_fwd(x.data_ptr(), y.data_ptr(), B, Hi, Wi, Ho, Wo, Cc, act_code(act), _stream()),
+              'spgt_bilinear_fwd')
+    return y
+
+
+def conv0_down(node: Tensor, w9: Tensor, bias: Tensor, Ho: int, Wo: int, act) -> Tensor:
+    """node [B,Hi,Wi] (one channel), w9 [9, Cout] -> act(bilinear(act(conv3x3)))  [B,Ho,Wo,Cout]."""
+    _chk(node, 'node'); _chk(w9, 'weight'); _chk(bias, 'bias')
+    B, Hi, Wi = node.shape
+    Cout = w9.shape[1]
+    y = torch.empty(B, Ho, Wo, Cout, device=node.device, dtype=node.dtype)
+    with torch.cuda.device(node.device):
+        check(lib.spgt_conv0_down_fwd(node.data_ptr(), w9.data_ptr(), bias.data_ptr(), y.data_ptr(), B, Hi, Wi, Ho, Wo, Cout,
+                                      act_code(act), _stream()), 'spgt_conv0_down_fwd')
+    return y
+
+
+def upsample_grid(uw: Tensor, grid: Tensor, wg: Tensor, bias: Tensor, Ho: int, Wo: int) -> Tensor:
+    _chk(uw, 'uw'); _chk(grid, 'grid'); _chk(wg, 'wg'); _chk(bias, 'bias')
+    B, Hi, Wi, Cc = uw.shape
+    y = torch.empty(B, Ho, Wo, Cc, device=uw.device, dtype=uw.dtype)
+    with torch.cuda.device(uw.device):
+        check(lib.spgt_upsample_grid_fwd(uw.data_ptr(), grid.data_ptr(), wg.data_ptr(), bias.data_ptr(), y.data_ptr(),
+                                         B, Hi, Wi, Ho, Wo, Cc, _stream()), 'spgt_upsample_grid_fwd')
+    return y
+
+
+def decoder_head(x: Tensor, w1_kn: Tensor, b1: Tensor, w2: Tensor, b2: float, scale: float, shift: float,
+                 dirichlet: bool, act) -> Tensor:
+    """x [B,H,W,K] -> [B,H,W,1]: ((act(x@w1+b1) . w2) + b2) * scale + shift with an optional zero frame."""
+    _chk(x, 'x'); _chk(w1_kn, 'w1'); _chk(b1, 'b1'); _chk(w2, 'w2')
+    B, Hh, Ww, K = x.shape
+    out = torch.empty(B, Hh, Ww, 1, device=x.device, dtype=x.dtype)
+    with torch.cuda.device(x.device):
+        check(lib.spgt_decoder_head_fwd(x.data_ptr(), w1_kn.data_ptr(), b1.data_ptr(), w2.data_ptr(), float(b2), float(scale),
+                                        float(shift), int(dirichlet), out.data_ptr(), B, Hh, Ww, K, w1_kn.shape[1],
+                                        act_code(act), _stream()), 'spgt_decoder_head_fwd')
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# spectral layer
+# ---------------------------------------------------------------------------------------------------------
+_TABLES = {}
+
+
+def spectral_tables(r: int, m: int, device) -> Tensor:
+    """DFT tables for (r, m), computed once per device by a setup kernel and cached."""
+    key = (r, m, torch.device(device).index)
+    if key not in _TABLES:
+        n = int(lib.spgt_spectral_tables_bytes(r, m))
+        if n == 0:
+            raise ValueError(f'unsupported spectral shape r={r}, m={m}')
+        t = torch.empty(n, device=device, dtype=torch.uint8)
+        with torch.cuda.device(device):
+            check(lib.spgt_spectral_tables_init(t.data_ptr(), n, r, m, _stream()), 'spgt_spectral_tables_init')
+        _TABLES[key] = t
+    return _TABLES[key]
+
+
+def spectral_conv2d(x: Tensor, wr_kn: Tensor, br: Tensor, fw0: Tensor, fw1: Tensor, mode: int, act,
+                    workspace: Optional[Tensor] = None) -> Tensor:
+    """x [B,r,r,32]; wr_kn [32,32] = residual weight transposed; fw0/fw1 [m,m,32,32,2]."""
+    _chk(x, 'x'); _chk(wr_kn, 'wr'); _chk(br, 'br'); _chk(fw0, 'fw0'); _chk(fw1, 'fw1')
+    B, r, r2, Cc = x.shape
+    if r != r2:
+        raise ValueError('the spectral layer expects a square grid')
+    tab = spectral_tables(r, mode, x.device)
+    need = int(lib.spgt_spectral_workspace_bytes(B, r, mode, Cc))
+    if need == 0:
+        raise ValueError(f'unsupported spectral shape B={B} r={r} m={mode} C={Cc}')
+    if workspace is None:
+        workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(lib.spgt_spectral_conv2d_fwd(x.data_ptr(), wr_kn.data_ptr(), br.data_ptr(), fw0.data_ptr(), fw1.data_ptr(),
+                                           tab.data_ptr(), workspace.data_ptr(), workspace.numel(), y.data_ptr(),
+                                           B, r, Cc, mode, act_code(act), _stream()), 'spgt_spectral_conv2d_fwd')
+    return y

@@ -1,0 +1,250 @@
+"""Parity of every C-ABI op against the CPU oracle (and the recorded reference outputs) on a B200."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import load_golden, rel_l2
+from oracle import gt_oracle as O
+
+pytestmark = pytest.mark.gpu
+PER_LAYER_TOL = 1e-5      # relative L2 per op / layer (the tolerance the hot-path spec states)
+
+
+@pytest.fixture(scope='module')
+def dev():
+    return torch.device('cuda:0')
+
+
+def _bind():
+    from spgt_b200.extension.bind import galerkin_attention as ga, datamove as dm
+    return ga, dm
+
+
+def test_library_loaded_is_in_tree():
+    import os
+    import spgt_b200._lib as L
+    assert os.path.samefile(os.path.dirname(L.LIB_PATH), os.path.dirname(L.__file__))
+    assert L.lib.spgt_abi_version() == 1
+
+
+@pytest.mark.parametrize('M,N,batch', [(5, 7, 3), (32, 32, 1), (211 * 3, 32, 2), (32, 1849, 2), (1, 1, 1), (33, 65, 2)])
+def test_batched_transpose_bit_exact(dev, M, N, batch):
+    _, dm = _bind()
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    X = torch.randn(batch, M, N, generator=g)
+    out = dm.batched_transpose(X.to(dev), [batch], [M], [N])
+    assert torch.equal(out.cpu(), O.batched_transpose(X, [batch], [M], [N]))
+
+
+def test_batched_transpose_spectral_shapes(dev):
+    _, dm = _bind()
+    X = torch.randn(2, 13, 13, 32, generator=torch.Generator().manual_seed(1))
+    a = dm.batched_transpose(X.to(dev), [2], [13, 13], [32])
+    assert a.shape == (2, 32, 13, 13) and torch.equal(a.cpu(), X.permute(0, 3, 1, 2))
+    b = dm.batched_transpose(a, [2], [32], [13, 13])
+    assert torch.equal(b.cpu(), X)
+
+
+@pytest.mark.parametrize('dims,H_all,W_all,lo', [([2, 3], 9, 5, 4), ([4, 32], 29, 15, 4), ([1, 33], 7, 4, 3)])
+def test_gather_scatter_bit_exact(dev, dims, H_all, W_all, lo):
+    _, dm = _bind()
+    g = torch.Generator().manual_seed(7)
+    src = torch.view_as_complex(torch.randn(*dims, H_all, W_all, 2, generator=g))
+    args = (dims, H_all, W_all, lo, lo, 0, 0, H_all - lo, 0)
+    a, b = dm.transpose_gather_dual(src.to(dev), *args)
+    ra, rb = O.transpose_gather_dual(src, *args)
+    assert torch.equal(a.cpu(), ra) and torch.equal(b.cpu(), rb)
+    back = dm.transpose_scatter_dual(a, b, *args)
+    assert torch.equal(back.cpu(), O.transpose_scatter_dual(ra, rb, *args))
+
+
+def test_projection_ops_against_golden(dev):
+    ga, _ = _bind()
+    d, p = load_golden('attention_layer.npz')
+    x, pos = d['x'].to(dev), d['pos'].to(dev)
+    P = {k: v.to(dev) for k, v in p.items()}
+    Q = ga.multihead_projection_with_position_rrc_cuda(x, P['weight_Q'], P['bias_Q'], pos, 4, 32, 2)
+    K = ga.multihead_projection_layernorm_with_position_rrc_cuda(
+        x, P['weight_K'], P['bias_K'], P['ln_weight_K'], P['ln_bias_K'], pos, 1e-6, 4, 32, 2)
+    V = ga.multihead_projection_layernorm_with_position_rrc_cuda(
+        x, P['weight_V'], P['bias_V'], P['ln_weight_V'], P['ln_bias_V'], pos, 1e-6, 4, 32, 2)
+    for name, got in (('Q', Q), ('K', K), ('V', V)):
+        assert got.shape == d[name].shape
+        assert torch.equal(got[:, :, :2].cpu(), d[name][:, :, :2]), name     # position rows are copies
+        assert rel_l2(got, d[name]) < PER_LAYER_TOL, name
+    A = ga.multihead_galerkin_attention_cccr_cuda(Q, K, V)
+    assert rel_l2(A, d['attn']) < PER_LAYER_TOL
+
+
+@pytest.mark.parametrize('B,S', [(1, 1), (1, 31), (2, 33), (1, 127), (3, 129), (1, 300)])
+def test_projection_edge_shapes(dev, B, S):
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(S)
+    x = torch.randn(B, S, 128, generator=g)
+    w = torch.randn(128, 128, generator=g) * 0.1
+    b = torch.randn(128, generator=g) * 0.1
+    lw, lb = 1 + 0.1 * torch.randn(4, 32, generator=g), 0.1 * torch.randn(4, 32, generator=g)
+    pos = torch.rand(B, S, 2, generator=g)
+    q = ops.projpos(x.to(dev), w.to(dev), b.to(dev), pos.to(dev), 4, 32, 2)
+    assert rel_l2(q, O.projpos(x, w, b, pos, 4, 32)) < PER_LAYER_TOL
+    k, inv = ops.projpos_lnorm(x.to(dev), w.to(dev), b.to(dev), lw.to(dev), lb.to(dev), pos.to(dev), 1e-6, 4, 32, 2,
+                               return_invsigma=True)
+    rk, rinv = O.projpos_lnorm(x.double(), w.double(), b.double(), lw.double(), lb.double(), pos.double(), 1e-6, 4, 32, True)
+    assert rel_l2(k, rk) < PER_LAYER_TOL and rel_l2(inv, rinv) < PER_LAYER_TOL
+    q3, k3, v3 = ops.projpos_qkv(x.to(dev), w.to(dev), b.to(dev), w.to(dev), b.to(dev), w.to(dev), b.to(dev),
+                                 lw.to(dev), lb.to(dev), lw.to(dev), lb.to(dev), 1e-6, pos.to(dev), 4, 32, 2)
+    assert torch.equal(q3, q) and torch.equal(k3, k) and torch.equal(v3, k)
+
+
+@pytest.mark.parametrize('B,H,dpk,S', [(1, 1, 34, 1), (1, 2, 34, 31), (2, 4, 34, 129), (4, 4, 34, 1849), (1, 4, 32, 257),
+                                       (1, 1, 33, 100), (1, 3, 35, 77), (2, 4, 34, 2809)])
+def test_attention_shapes_and_kv(dev, B, H, dpk, S):
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(S + dpk)
+    Q, K, V = (torch.randn(B, H, dpk, S, generator=g) for _ in range(3))
+    out, T = ops.galerkin_attention(Q.to(dev), K.to(dev), V.to(dev), return_kv=True)
+    ref = O.galerkin_attention(Q.double(), K.double(), V.double())
+    assert rel_l2(T, O.galerkin_kv(K.double(), V.double())) < PER_LAYER_TOL
+    assert rel_l2(out, ref) < PER_LAYER_TOL
+    merged = ops.galerkin_attention(Q.to(dev), K.to(dev), V.to(dev), merged_heads=True)
+    assert torch.equal(merged, out.transpose(1, 2).contiguous().view(B, S, H * dpk))
+
+
+def test_attention_cluster_sizes_agree_and_are_deterministic(dev):
+    from spgt_b200 import ops
+    from spgt_b200._lib import lib
+    g = torch.Generator().manual_seed(11)
+    Q, K, V = (torch.randn(2, 4, 34, 1849, generator=g).to(dev) for _ in range(3))
+    ref = O.galerkin_attention(Q.cpu().double(), K.cpu().double(), V.cpu().double())
+    try:
+        for c in (1, 2, 4, 8):
+            assert lib.spgt_set_tuning(b'attn_cluster', c) == 0
+            a = ops.galerkin_attention(Q, K, V)
+            b = ops.galerkin_attention(Q, K, V)
+            assert torch.equal(a, b), c
+            assert rel_l2(a, ref) < PER_LAYER_TOL, c
+    finally:
+        lib.spgt_set_tuning(b'attn_cluster', 0)
+
+
+@pytest.mark.parametrize('batch,M,N,K', [(64, 32, 32, 1849), (3, 34, 34, 500), (2, 5, 70, 33), (1, 32, 32, 19881), (2, 32, 30, 7)])
+def test_skinny_gemm(dev, batch, M, N, K):
+    ga, _ = _bind()
+    g = torch.Generator().manual_seed(K)
+    A, Bm = torch.randn(batch, M, K, generator=g), torch.randn(batch, K, N, generator=g)
+    C1 = ga.batched_skinny_gemm(A.to(dev), Bm.to(dev), 1.0 / K)
+    assert rel_l2(C1, O.batched_skinny_gemm(A.double(), Bm.double(), 1.0 / K)) < PER_LAYER_TOL
+    assert torch.equal(C1, ga.batched_skinny_gemm(A.to(dev), Bm.to(dev), 1.0 / K))
+
+
+@pytest.mark.parametrize('rows,K,N,act,res', [(300, 128, 256, 'relu', False), (257, 256, 128, None, True), (100, 136, 128, None, True),
+                                              (1000, 128, 32, None, False), (77, 32, 32, 'silu', False), (5, 4, 42, 'silu2', False)])
+def test_linear(dev, rows, K, N, act, res):
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(rows)
+    x, w, b = torch.randn(rows, K, generator=g), torch.randn(N, K, generator=g) / K ** 0.5, torch.randn(N, generator=g)
+    r = torch.randn(rows, N, generator=g) if res else None
+    y = ops.linear(x.to(dev), ops.pad_cols(w.t().contiguous().to(dev)), b.to(dev), N, act, None if r is None else r.to(dev))
+    ref = torch.nn.functional.linear(x.double(), w.double(), b.double())
+    ref = {'relu': torch.relu, 'silu': torch.nn.functional.silu, None: lambda t: t,
+           'silu2': lambda t: torch.nn.functional.silu(torch.nn.functional.silu(t))}[act](ref)
+    if res:
+        ref = ref + r.double()
+    assert rel_l2(y, ref) < PER_LAYER_TOL
+
+
+@pytest.mark.parametrize('B,Hh,Ww,cin_pitch,cin_off,Cin,Cout,act', [(2, 9, 11, 128, 0, 128, 42, 'relu'), (1, 13, 13, 128, 42, 42, 44, 'relu'),
+                                                                    (2, 8, 8, 128, 0, 42, 42, 'relu'), (1, 20, 17, 128, 0, 128, 128, 'silu2')])
+def test_conv3x3(dev, B, Hh, Ww, cin_pitch, cin_off, Cin, Cout, act):
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(Cin + Cout)
+    x = torch.randn(B, Hh, Ww, cin_pitch, generator=g)
+    w = torch.randn(Cout, Cin, 3, 3, generator=g) / (9 * Cin) ** 0.5
+    b = torch.randn(Cout, generator=g)
+    w_kn = ops.pad_cols(w.permute(2, 3, 1, 0).reshape(9 * Cin, Cout).contiguous().to(dev))
+    off = 4 if Cout + 4 <= 128 else 0
+    y = torch.full((B, Hh, Ww, 128), float('nan'), device=dev)
+    ops.conv3x3(x.to(dev), cin_off, Cin, w_kn, b.to(dev), y, off, Cout, act)
+    ref = torch.nn.functional.conv2d(x[..., cin_off:cin_off + Cin].permute(0, 3, 1, 2).double(), w.double(), b.double(), padding=1)
+    ref = torch.relu(ref) if act == 'relu' else torch.nn.functional.silu(torch.nn.functional.silu(ref))
+    assert rel_l2(y[..., off:off + Cout], ref.permute(0, 2, 3, 1)) < PER_LAYER_TOL
+    assert torch.isnan(y[..., :off]).all() and torch.isnan(y[..., off + Cout:]).all()  # nothing outside the slice is touched
+
+
+@pytest.mark.parametrize('Hi,Ho', [(29, 21), (21, 15), (15, 21), (21, 29), (7, 7), (211, 106), (53, 106)])
+def test_bilinear_matches_aten(dev, Hi, Ho):
+    from spgt_b200 import ops
+    x = torch.randn(2, Hi, Hi, 8, generator=torch.Generator().manual_seed(Hi))
+    y = ops.bilinear(x.to(dev), Ho, Ho, 'relu')
+    ref = torch.relu(torch.nn.functional.interpolate(x.permute(0, 3, 1, 2), size=(Ho, Ho), mode='bilinear', align_corners=True))
+    assert rel_l2(y, ref.permute(0, 2, 3, 1)) < 2e-6
+
+
+def test_conv0_down_and_upsample_grid(dev):
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    node = torch.randn(2, 29, 29, generator=g)
+    w, b = torch.randn(128, 1, 3, 3, generator=g) / 3, torch.randn(128, generator=g)
+    y = ops.conv0_down(node.to(dev), w.reshape(128, 9).t().contiguous().to(dev), b.to(dev), 21, 21, 'relu')
+    ref = torch.relu(torch.nn.functional.conv2d(node.unsqueeze(1).double(), w.double(), b.double(), padding=1))
+    ref = torch.relu(torch.nn.functional.interpolate(ref, size=(21, 21), mode='bilinear', align_corners=True))
+    assert rel_l2(y, ref.permute(0, 2, 3, 1)) < PER_LAYER_TOL
+    u = torch.randn(2, 21, 21, 128, generator=g)
+    grid = torch.rand(2, 29, 29, 2, generator=g)
+    W, bb = torch.randn(32, 130, generator=g) / 11, torch.randn(32, generator=g)
+    uw = ops.linear(u.to(dev), ops.pad_cols(W[:, :128].t().contiguous().to(dev)), None, 32)
+    out = ops.upsample_grid(uw, grid.to(dev), W[:, 128:].t().contiguous().to(dev), bb.to(dev), 29, 29)
+    up = torch.nn.functional.interpolate(u.permute(0, 3, 1, 2).double(), size=(29, 29), mode='bilinear', align_corners=True)
+    ref = torch.nn.functional.linear(torch.cat([up.permute(0, 2, 3, 1), grid.double()], -1), W.double(), bb.double())
+    assert rel_l2(out, ref) < PER_LAYER_TOL
+
+
+def test_decoder_head(dev):
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(2, 13, 13, 32, generator=g)
+    w1, b1 = torch.randn(128, 32, generator=g) / 6, torch.randn(128, generator=g)
+    w2, b2 = torch.randn(1, 128, generator=g) / 11, 0.3
+    out = ops.decoder_head(x.to(dev), w1.t().contiguous().to(dev), b1.to(dev), w2.reshape(-1).contiguous().to(dev), b2, 1.00001, 0.5, True, 'silu')
+    h = torch.nn.functional.silu(torch.nn.functional.linear(x.double(), w1.double(), b1.double()))
+    ref = (torch.nn.functional.linear(h, w2.double()) + b2) * 1.00001 + 0.5
+    ref = torch.nn.functional.pad(ref[:, 1:-1, 1:-1], (0, 0, 1, 1, 1, 1))
+    assert rel_l2(out, ref) < PER_LAYER_TOL
+    assert float(out[:, 0].abs().max()) == 0.0
+
+
+def test_spectral_layer_against_golden(dev):
+    from spgt_b200 import ops
+    d, p = load_golden('spectral_layer.npz')
+    y = ops.spectral_conv2d(d['x'].to(dev), p['residual_layer.weight'].t().contiguous().to(dev), p['residual_layer.bias'].to(dev),
+                            p['fourier_weight.0'].to(dev), p['fourier_weight.1'].to(dev), 4, 'silu')
+    assert rel_l2(y, d['y']) < PER_LAYER_TOL
+
+
+@pytest.mark.parametrize('B,r,m', [(1, 29, 4), (2, 64, 8), (1, 211, 12), (1, 141, 12), (1, 33, 16), (3, 40, 1)])
+def test_spectral_layer_shapes(dev, B, r, m):
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(r + m)
+    x = torch.randn(B, r, r, 32, generator=g)
+    p = {'residual_layer.weight': torch.randn(32, 32, generator=g) / 6, 'residual_layer.bias': torch.randn(32, generator=g),
+         'fourier_weight.0': torch.randn(m, m, 32, 32, 2, generator=g) / 6, 'fourier_weight.1': torch.randn(m, m, 32, 32, 2, generator=g) / 6}
+    y = ops.spectral_conv2d(x.to(dev), p['residual_layer.weight'].t().contiguous().to(dev), p['residual_layer.bias'].to(dev),
+                            p['fourier_weight.0'].to(dev), p['fourier_weight.1'].to(dev), m, 'silu')
+    ref = O.spectral_conv2d(x.double(), O.to_dtype(p, torch.float64), '', m, 'silu')
+    assert rel_l2(y, ref) < PER_LAYER_TOL
+
+
+def test_error_codes_do_not_launch(dev):
+    from spgt_b200 import ops
+    from spgt_b200._lib import SpgtError, lib
+    x = torch.randn(1, 8, 128, device=dev)
+    with pytest.raises(SpgtError):
+        ops.projpos(x, torch.randn(128, 128, device=dev), None, torch.rand(1, 8, 2, device=dev), 2, 64, 2)     # d_head != 32
+    with pytest.raises(ValueError):
+        ops.projpos(x.cpu(), torch.randn(128, 128), None, torch.rand(1, 8, 2), 4, 32, 2)
+    with pytest.raises(TypeError):
+        ops.batched_transpose(x.double(), [1], [8], [128])
+    assert lib.spgt_batched_transpose(None, None, 4, 4, 1, None) == -1
+    assert lib.spgt_galerkin_attn_fwd(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), None, 1, 1, 40, 8, 0, None) == -2
+    assert lib.spgt_batched_skinny_gemm(x.data_ptr(), x.data_ptr(), x.data_ptr(), 1.0, 8, 8, 16, 1, None, 0, None) == -4
+    torch.cuda.synchronize()
