@@ -1,0 +1,271 @@
+#!/usr/bin/env python
+"""Darcy Galerkin Transformer inference benchmark (211 x 211 fine grid, 53 x 53 attention grid).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One rank per GPU (torchrun for N > 1).  A step is one forward of the full model over this rank's batch of
+synthetic Darcy coefficient fields; rank 0 prints one JSON line.  `value` is samples/s with the inputs resident
+in HBM, `e2e` the same metric through the host-facing API with pinned host buffers (upload and download inside
+the timed region), `roofline` the Galerkin attention kernel's achieved HBM bandwidth measured with CUDA events
+around its launches inside the timed steps, `cpu_baseline` the CPU oracle (a port of the reference's own CPU
+path) on a bounded sample.  `--impl reference` times that CPU path alone with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+METRIC = 'darcy_gt_inference_samples_per_s_211'
+FINE, SUB_NODE, SUB_ATTN, MODES, SEED = 421, 2, 8, 12, 4
+# DRAM bytes (read + write) of one galerkin_attn_kernel launch at B=64, H=4, S=2809 from the ncu capture
+# summarised in profiles/ (None until a capture of the current kernel exists).
+ATTN_TRAFFIC_BYTES = None
+
+
+def measured_peak():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    try:
+        with open(path) as f:
+            return float(json.load(f)['hbm_gbs']), 'measured'
+    except Exception:
+        return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs (read-only query)."""
+    Q = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits', '-lms', '200',
+                                          '-i', str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        return False
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith('active'):
+                    reasons.add(n)
+        if not sm:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        sm.sort()
+        return {'sm_mhz': sm[len(sm) // 2], 'sm_max_mhz': max(mx), 'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+def oracle_setup(batch: int, seed: int = SEED):
+    from oracle import gt_oracle as O
+    from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
+    cfg = O.default_config(FINE, SUB_NODE, SUB_ATTN, MODES)
+    data = synthetic_darcy_batch(range(batch), FINE, SUB_NODE, SUB_ATTN, seed)
+    return O, cfg, data
+
+
+def oracle_params(seed: int = SEED):
+    """Random-init weights of the benchmark architecture in the SpGT layout (same construction as the GPU model)."""
+    from spgt_b200.config.config_accessor import get_darcy_config
+    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+    torch.manual_seed(seed)
+    model = Sp_GalerkinTransformer2D(get_darcy_config(SUB_NODE, SUB_ATTN, num_frequence_mode=MODES))
+    return {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+
+def time_oracle(sample_batch: int, steps: int, warmup: int):
+    O, cfg, data = oracle_setup(sample_batch)
+    p = oracle_params()
+    fwd = lambda: O.model_forward(data['node'], data['position'], data['grid'], p, cfg)
+    with torch.no_grad():
+        for _ in range(warmup):
+            fwd()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fwd()
+        dt = time.perf_counter() - t0
+    return sample_batch * steps / dt, dt / steps
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    sample = 8
+    sps, per_step = time_oracle(sample, args.steps, args.warmup)
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': sps, 'unit': 'samples/s', 'n_gpus': args.gpus, 'steps': args.steps,
+        'warmup': args.warmup, 'ms_per_step': per_step * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'dtype': 'f32', 'data': 'synthetic', 'gpu_launches': 0,
+        'config': {'workload': f'full Darcy GT forward 211x211 / 53x53, 6 encoder layers, FNO 12 modes; CPU sample of {sample} of the 64-sample batch per step'},
+        'cpu_baseline': {'value': sps, 'unit': 'samples/s', 'cores': cores, 'kind': 'port',
+                         'sample': f'{sample} samples per step (1/8 of the 64-sample batch), torch CPU fp32, {cores} threads'},
+        'e2e': {'value': sps, 'unit': 'samples/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='spgt_b200', choices=['spgt_b200', 'reference'])
+    ap.add_argument('--batch', type=int, default=64, help='samples per GPU per step')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--breakdown', action='store_true', help='also print a per-entry-point time table to stderr')
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != 'reference' else args.warmup
+    rank, world, local = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1)), int(os.environ.get('LOCAL_RANK', 0))
+
+    if args.impl == 'reference':
+        run_reference(args, rank)
+        return
+
+    from spgt_b200 import ops
+    from spgt_b200.config.config_accessor import get_darcy_config
+    from spgt_b200.dataset.darcy_dataset import GaussNormalizer, synthetic_darcy_batch
+    from spgt_b200.engine.darcy_engine import HostInference
+    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+
+    device = torch.device('cuda', local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group('nccl', init_method='env://', device_id=device)
+
+    cfg = get_darcy_config(SUB_NODE, SUB_ATTN, num_frequence_mode=MODES)
+    cfg['target_normalizer'] = GaussNormalizer()
+    torch.manual_seed(SEED)
+    model = Sp_GalerkinTransformer2D(cfg).to(device).eval()
+    B = args.batch
+    host = synthetic_darcy_batch(range(rank * B, (rank + 1) * B), FINE, SUB_NODE, SUB_ATTN, SEED)
+    host = {k: v.pin_memory() for k, v in host.items() if k != 'coeff'}
+    dev = {k: v.to(device) for k, v in host.items()}
+    S, H, DPK = cfg['r_attn'] ** 2, cfg['num_head'], 34
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    # ---------------- device-resident throughput ----------------
+    for _ in range(args.warmup):
+        model(dev['node'], dev['position'], dev['grid'])
+    barrier()
+    launches0 = ops.LAUNCHES
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks, ops.profile_ops(only=['spgt_galerkin_attn_fwd']) as prof:
+        e0.record()
+        for _ in range(args.steps):
+            out = model(dev['node'], dev['position'], dev['grid'])
+        e1.record()
+        barrier()
+    elapsed_ms = max_over_ranks(e0.elapsed_time(e1))
+    launches = ops.LAUNCHES - launches0
+    attn_ms = prof.times_ms().get('spgt_galerkin_attn_fwd', [])
+    attn_avg_ms = sum(attn_ms) / max(1, len(attn_ms))
+    value = world * B * args.steps / (elapsed_ms * 1e-3)
+
+    # ---------------- end to end through the host-facing API ----------------
+    engine = HostInference(model, device)
+    outs = [torch.empty(B, cfg['r_node'], cfg['r_node'], 1, dtype=torch.float32, pin_memory=True) for _ in range(2)]
+    engine.run([host] * args.warmup, [outs[i & 1] for i in range(args.warmup)])
+    barrier()
+    t0 = time.perf_counter()
+    engine.run([host] * args.steps, [outs[i & 1] for i in range(args.steps)])
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    nbytes = engine.bytes_per_batch(host)
+    e2e_value = world * B * args.steps / e2e_s
+
+    # ---------------- roofline of the attention kernel ----------------
+    peak, peak_kind = measured_peak()
+    algo_bytes = 4 * B * H * DPK * S * 4                      # read Q, K, V and write out, fp32
+    achieved = algo_bytes / (attn_avg_ms * 1e-3) / 1e9 if attn_avg_ms > 0 else None
+    roofline = {'kernel': 'galerkin_attn_kernel', 'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'peak_kind': peak_kind,
+                'unit': 'GB/s', 'frac': (achieved / peak) if achieved else None, 'traffic': ATTN_TRAFFIC_BYTES,
+                'algorithmic_bytes': algo_bytes, 'avg_launch_ms': attn_avg_ms, 'launches_timed': len(attn_ms)}
+
+    if args.breakdown and rank == 0:
+        with ops.profile_ops() as pall:
+            model(dev['node'], dev['position'], dev['grid'])
+        tm = pall.times_ms()
+        tot = sum(sum(v) for v in tm.values())
+        for k, v in sorted(tm.items(), key=lambda kv: -sum(kv[1])):
+            print(f'{k:34s} calls {len(v):3d}  total {sum(v):8.3f} ms  {100 * sum(v) / tot:5.1f} %', file=sys.stderr)
+        print(f'{"sum":34s} {tot:8.3f} ms', file=sys.stderr)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = torch.get_num_threads()
+        sps, per_step = time_oracle(8, 3, 1)
+        cpu = {'value': sps, 'unit': 'samples/s', 'cores': cores, 'kind': 'port',
+               'sample': f'8 samples per forward (1/8 of the batch), 3 timed forwards after 1 warm-up, torch CPU fp32, {cores} threads'}
+
+    if rank == 0:
+        line = {
+            'metric': METRIC, 'value': value, 'unit': 'samples/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': elapsed_ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'dtype': 'f32', 'data': 'synthetic',
+            'config': {'workload': 'full Darcy Galerkin Transformer forward, fine grid 211x211, attention grid 53x53, 6 encoder '
+                                   'layers (hidden 128, 4 heads, FFN 256), FNO2d regressor (2 spectral layers, width 32, 12 modes)',
+                       'batch_per_gpu': B, 'global_batch': B * world, 'parallelism': f'dp{world}', 'seed': SEED,
+                       'l2_policy': 'per-step working set (several GB of activations) is far larger than the 126 MB L2'},
+            'clocks': clocks.summary(), 'gpu_launches': launches,
+            'e2e': {'value': e2e_value, 'unit': 'samples/s', 'h2d_bytes_per_step': nbytes['h2d'], 'd2h_bytes_per_step': nbytes['d2h'],
+                    'ms_per_step': e2e_s * 1e3 / args.steps},
+            'roofline': roofline, 'cpu_baseline': cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

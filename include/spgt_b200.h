@@ -148,11 +148,13 @@ int spgt_upsample_grid_fwd(const float* uw, const float* grid, const float* wg, 
 
 /* Decoder FeedForward with a scalar target, de-normalisation and the Dirichlet frame in one pass:
  * out[b,y,x] = ((act(x*w1+b1) . w2) + b2) * scale + shift, then 0 on the 1-pixel frame if dirichlet != 0.
+ * scale_map / shift_map [Hh*Ww] are optional per-pixel replacements of scale / shift (a normaliser fitted per
+ * grid node); pass NULL to use the scalars.
  * x [B*Hh*Ww, K] (K % 4 == 0, K <= 64), w1 [K,N1] (N1 == 128), w2 [N1].
  * (network/sp_model.py:63, 109-112; dataset/darcy_dataset.py:30-31.) */
 int spgt_decoder_head_fwd(const float* x, const float* w1, const float* b1, const float* w2, float b2,
-                          float scale, float shift, int dirichlet, float* out, int B, int Hh, int Ww, int K, int N1,
-                          int act, spgt_stream_t stream);
+                          float scale, float shift, const float* scale_map, const float* shift_map, int dirichlet,
+                          float* out, int B, int Hh, int Ww, int K, int N1, int act, spgt_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * FNO2d spectral layer (reference: Sp_SpectralConv2D.forward, network/sp_layer.py:125-156)

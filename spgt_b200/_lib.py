@@ -42,7 +42,7 @@ SIGNATURES = {
     'spgt_bilinear_fwd': (_i, [_f, _f, _i, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_conv0_down_fwd': (_i, [_f, _f, _f, _f, _i, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_upsample_grid_fwd': (_i, [_f, _f, _f, _f, _f, _i, _i, _i, _i, _i, _i, _st]),
-    'spgt_decoder_head_fwd': (_i, [_f, _f, _f, _f, _fl, _fl, _fl, _i, _f, _i, _i, _i, _i, _i, _i, _st]),
+    'spgt_decoder_head_fwd': (_i, [_f, _f, _f, _f, _fl, _fl, _fl, _f, _f, _i, _f, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_spectral_tables_bytes': (_sz, [_i, _i]),
     'spgt_spectral_tables_init': (_i, [_f, _sz, _i, _i, _st]),
     'spgt_spectral_workspace_bytes': (_sz, [_i, _i, _i, _i]),

@@ -86,7 +86,8 @@ struct ProjEpi {           // up to three projections (q, k, v) selected by the 
     float eps; int S, H, d_pos, D;
 };
 struct HeadEpi {
-    const float* b1; const float* w2; float b2, scale, shift; int dirichlet, Hh, Ww, act; float* out;
+    const float* b1; const float* w2; float b2, scale, shift; const float* scale_map; const float* shift_map;
+    int dirichlet, Hh, Ww, act; float* out;
 };
 
 template <int WN> struct GemmSmem {
@@ -387,9 +388,11 @@ gemm_head_kernel(DenseLoader<4> ld, const float* __restrict__ W1, int K, int row
     if (tid < G_BM) {
         const int row = row0 + tid;
         if (row < rows) {
-            float v = (red[tid] + red[G_BM + tid] + ep.b2) * ep.scale + ep.shift;
+            const int rem = row % (ep.Hh * ep.Ww);
+            const float sc = ep.scale_map ? __ldg(ep.scale_map + rem) : ep.scale;
+            const float sh = ep.shift_map ? __ldg(ep.shift_map + rem) : ep.shift;
+            float v = (red[tid] + red[G_BM + tid] + ep.b2) * sc + sh;
             if (ep.dirichlet) {
-                const int rem = row % (ep.Hh * ep.Ww);
                 const int y = rem / ep.Ww, x = rem - y * ep.Ww;
                 if (y == 0 || x == 0 || y == ep.Hh - 1 || x == ep.Ww - 1) v = 0.0f;
             }
@@ -524,8 +527,9 @@ extern "C" int spgt_projpos_qkv_fwd(const float* x, const float* wq, const float
 }
 
 extern "C" int spgt_decoder_head_fwd(const float* x, const float* w1, const float* b1, const float* w2, float b2,
-                                     float scale, float shift, int dirichlet, float* out, int B, int Hh, int Ww, int K,
-                                     int N1, int act, spgt_stream_t stream) {
+                                     float scale, float shift, const float* scale_map, const float* shift_map,
+                                     int dirichlet, float* out, int B, int Hh, int Ww, int K, int N1, int act,
+                                     spgt_stream_t stream) {
     if (!x || !w1 || !b1 || !w2 || !out) return SPGT_ERR_NULL;
     if (B <= 0 || Hh <= 0 || Ww <= 0 || K <= 0 || (K & 3) || K > 64 || N1 != 128 || act < 0 || act > 3) return SPGT_ERR_SHAPE;
     const int64_t rows64 = (int64_t)B * Hh * Ww;
@@ -535,7 +539,7 @@ extern "C" int spgt_decoder_head_fwd(const float* x, const float* w1, const floa
     if (int e = set_smem(gemm_head_kernel, GemmSmem<8>::BYTES, done)) return e;
     DenseLoader<4> ld;
     ld.x = x; ld.lda = K; ld.rows = (int)rows64; ld.K = K;
-    HeadEpi ep{b1, w2, b2, scale, shift, dirichlet, Hh, Ww, act, out};
+    HeadEpi ep{b1, w2, b2, scale, shift, scale_map, shift_map, dirichlet, Hh, Ww, act, out};
     gemm_head_kernel<<<(unsigned)ceil_div((int)rows64, G_BM), G_THREADS, GemmSmem<8>::BYTES, (cudaStream_t)stream>>>(
         ld, w1, K, (int)rows64, ep);
     return launch_status();

@@ -1,0 +1,74 @@
+"""Host-facing inference loop: pinned host batches in, host predictions out.
+
+Mirrors what the reference's validate_epoch_darcy does per batch (engine/darcy_engine.py:33-46: host -> device
+copies of node / position / grid, forward, result back) with the copies on a side stream so that the upload of
+batch i+1 and the download of batch i-1 overlap the kernels of batch i.
+"""
+from typing import Dict, Iterable, List
+
+import torch
+
+
+class HostInference:
+    """Runs model.forward over host batches with double-buffered device staging.
+
+    Each batch is a dict with float32 tensors 'node' [n,r,r,1], 'position' [n,ra,ra,2], 'grid' [n,r,r,2] in pinned
+    host memory; the result for each batch is written into a pinned host tensor [n,r,r,1]."""
+
+    def __init__(self, model, device):
+        self.model, self.device = model, torch.device(device)
+        self.copy_in, self.copy_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self._slots = [{}, {}]
+        self._out_host = {}
+
+    def _stage(self, slot: Dict, batch: Dict[str, torch.Tensor]):
+        for k in ('node', 'position', 'grid'):
+            t = batch[k]
+            if k not in slot or slot[k].shape != t.shape:
+                slot[k] = torch.empty(t.shape, dtype=torch.float32, device=self.device)
+            slot[k].copy_(t, non_blocking=True)
+
+    def bytes_per_batch(self, batch) -> Dict[str, int]:
+        n, r = batch['node'].shape[0], batch['node'].shape[1]
+        return dict(h2d=sum(batch[k].numel() * 4 for k in ('node', 'position', 'grid')), d2h=n * r * r * 4)
+
+    def run(self, batches: Iterable[Dict[str, torch.Tensor]], outputs: List[torch.Tensor] = None) -> List[torch.Tensor]:
+        """Returns one pinned host tensor per batch.  `outputs`, if given, supplies the destination tensors."""
+        batches = list(batches)
+        compute = torch.cuda.current_stream(self.device)
+        results, pending = [], []
+        ready = [None, None]
+        with torch.cuda.device(self.device):
+            if batches:
+                with torch.cuda.stream(self.copy_in):
+                    self._stage(self._slots[0], batches[0])
+                    ready[0] = self.copy_in.record_event()
+            for i, batch in enumerate(batches):
+                slot = self._slots[i & 1]
+                compute.wait_event(ready[i & 1])
+                if i + 1 < len(batches):
+                    nxt = (i + 1) & 1
+                    with torch.cuda.stream(self.copy_in):
+                        if pending and len(pending) > 0:
+                            self.copy_in.wait_event(pending[-1][1])     # slot nxt was read by batch i-1: wait for it
+                        self._stage(self._slots[nxt], batches[i + 1])
+                        ready[nxt] = self.copy_in.record_event()
+                pred = self.model(slot['node'], slot['position'], slot['grid'])
+                done = compute.record_event()
+                host = outputs[i] if outputs is not None else self._host_out(i, pred.shape)
+                with torch.cuda.stream(self.copy_out):
+                    self.copy_out.wait_event(done)
+                    host.copy_(pred, non_blocking=True)
+                    pred.record_stream(self.copy_out)
+                    out_done = self.copy_out.record_event()
+                pending.append((host, done, out_done))
+                results.append(host)
+            for _, _, out_done in pending:
+                out_done.synchronize()
+        return results
+
+    def _host_out(self, i, shape):
+        key = (i & 3, tuple(shape))
+        if key not in self._out_host:
+            self._out_host[key] = torch.empty(shape, dtype=torch.float32, pin_memory=True)
+        return self._out_host[key]

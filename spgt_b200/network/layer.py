@@ -1,0 +1,77 @@
+"""Shared layers of the Darcy model with the reference's parameter names (network/layer.py), inference only.
+
+Each module keeps ordinary torch Parameters (so a reference state_dict loads unchanged) and a cache of the same
+weights re-laid-out for the kernels ([K, N] row-major, column count padded to a multiple of 4).
+"""
+import torch
+from torch import Tensor
+
+from .. import ops
+
+
+class _KernelWeights(torch.nn.Module):
+    """Caches derived weight layouts; the cache is dropped whenever parameters are (re)loaded or moved."""
+
+    def __init__(self):
+        super().__init__()
+        self._kw = {}
+        self.register_load_state_dict_post_hook(lambda module, incompatible: module._kw.clear())
+
+    def _apply(self, fn, *args, **kwargs):
+        self._kw.clear()
+        return super()._apply(fn, *args, **kwargs)
+
+    def _cached(self, key, make):
+        if key not in self._kw:
+            with torch.no_grad():
+                self._kw[key] = make()
+        return self._kw[key]
+
+
+def _linear_kn(weight: Tensor) -> Tensor:
+    """torch Linear weight [out, in] -> [in, out4] row-major."""
+    return ops.pad_cols(weight.detach().t().contiguous())
+
+
+def _conv_kn(weight: Tensor) -> Tensor:
+    """Conv2d weight [Cout, Cin, 3, 3] -> [(ky*3+kx)*Cin + ci, Cout4] row-major."""
+    cout, cin = weight.shape[:2]
+    return ops.pad_cols(weight.detach().permute(2, 3, 1, 0).reshape(9 * cin, cout).contiguous())
+
+
+class ConvResBlock2D(_KernelWeights):
+    """conv3x3(pad 1) -> [dropout, rate treated as 0] -> activation; NHWC in and out.
+    Reference: network/layer.py:7-24 (NCHW there; the kernels keep channels last throughout)."""
+
+    def __init__(self, in_dim, out_dim, kernel_size, padding, droprate, activation) -> None:
+        super().__init__()
+        assert kernel_size == 3 and padding == 1
+        self.droprate = droprate
+        self.activation = activation
+        self.conv_layer = torch.nn.Conv2d(in_dim, out_dim, kernel_size=kernel_size, padding=padding)
+
+    def kernel_weight(self):
+        return self._cached('w', lambda: _conv_kn(self.conv_layer.weight))
+
+    def forward_nhwc(self, X: Tensor, cin_off: int, out: Tensor, cout_off: int, act=None) -> Tensor:
+        w = self.conv_layer.weight
+        return ops.conv3x3(X, cin_off, w.shape[1], self.kernel_weight(), self.conv_layer.bias.detach(), out, cout_off,
+                           w.shape[0], self.activation if act is None else act)
+
+
+class FeedForward(_KernelWeights):
+    """Linear -> activation -> Linear (dropout rate treated as 0).  Reference: network/layer.py:155-174."""
+
+    def __init__(self, in_dim, out_dim, dim_hidden, droprate, activation) -> None:
+        super().__init__()
+        self.droprate = droprate
+        self.activation = activation
+        self.layer1 = torch.nn.Linear(in_dim, dim_hidden)
+        self.layer2 = torch.nn.Linear(dim_hidden, out_dim)
+
+    def forward(self, X: Tensor, residual: Tensor = None) -> Tensor:
+        """X [..., in_dim] -> [..., out_dim] (+ residual when given, fused into the second GEMM)."""
+        w1 = self._cached('w1', lambda: _linear_kn(self.layer1.weight))
+        w2 = self._cached('w2', lambda: _linear_kn(self.layer2.weight))
+        h = ops.linear(X, w1, self.layer1.bias.detach(), self.layer1.out_features, self.activation)
+        return ops.linear(h, w2, self.layer2.bias.detach(), self.layer2.out_features, None, residual)

@@ -1,0 +1,65 @@
+"""DownScaler2D / UpScaler2D with the reference's parameter names (network/model.py:7-65), inference only."""
+import torch
+from torch import Tensor
+
+from .. import ops
+from .layer import ConvResBlock2D, _KernelWeights
+
+
+class DownScaler2D(_KernelWeights):
+    """[N,r,r,1] -> [N,r_attn,r_attn,out_dim]:
+    conv0+act -> bilinear to r_mid -> act -> conv1, conv2, conv3 (+act) concatenated -> bilinear to r_attn -> act.
+    conv0, its activation, the first interpolation and the activation after it run as one kernel, so the
+    out_dim-channel full-resolution tensor is never written; conv1..3 write straight into their channel slice
+    of the concatenated tensor."""
+
+    def __init__(self, resolution_size, in_dim, out_dim, droprate, activation) -> None:
+        super().__init__()
+        assert in_dim == 1, 'the fused first stage handles the single-channel Darcy coefficient'
+        self.resolution_size = resolution_size
+        self.activation = activation
+        out_dim1 = out_dim // 3
+        out_dim2 = out_dim // 3
+        out_dim3 = int(out_dim - out_dim1 - out_dim2)
+        self.dims = (out_dim1, out_dim2, out_dim3)
+        self.conv0 = ConvResBlock2D(in_dim, out_dim, 3, 1, droprate, activation)
+        self.conv1 = ConvResBlock2D(out_dim, out_dim1, 3, 1, droprate, activation)
+        self.conv2 = ConvResBlock2D(out_dim1, out_dim2, 3, 1, droprate, activation)
+        self.conv3 = ConvResBlock2D(out_dim2, out_dim3, 3, 1, droprate, activation)
+
+    def forward(self, X: Tensor) -> Tensor:
+        N, r, _, _ = X.shape
+        mid, ra = self.resolution_size[1], self.resolution_size[2]
+        w0 = self._cached('w0', lambda: self.conv0.conv_layer.weight.detach().reshape(-1, 9).t().contiguous())
+        X = ops.conv0_down(X.reshape(N, r, r), w0, self.conv0.conv_layer.bias.detach(), mid[0], mid[1], self.activation)
+        d1, d2, d3 = self.dims
+        cat = torch.empty(N, mid[0], mid[1], d1 + d2 + d3, device=X.device, dtype=X.dtype)
+        self.conv1.forward_nhwc(X, 0, cat, 0)
+        self.conv2.forward_nhwc(cat, 0, cat, d1)
+        self.conv3.forward_nhwc(cat, d1, cat, d1 + d2)
+        return ops.bilinear(cat, ra[0], ra[1], self.activation)
+
+
+class UpScaler2D(_KernelWeights):
+    """[N,r_attn,r_attn,in_dim] -> [N,r,r,out_dim]: bilinear to r_mid -> conv+act -> act -> bilinear to r.
+    The activation is applied twice, as in the reference (once inside ConvResBlock2D.forward, network/layer.py:23,
+    once more in UpScaler2D.forward, network/model.py:62)."""
+
+    def __init__(self, resolution_size, in_dim, out_dim, droprate, activation) -> None:
+        super().__init__()
+        self.resolution_size = resolution_size
+        self.droprate = droprate
+        self.activation = activation
+        self.conv = ConvResBlock2D(in_dim, out_dim, 3, 1, droprate, activation)
+
+    def forward_mid(self, X: Tensor) -> Tensor:
+        """Everything up to (not including) the last interpolation: [N, r_mid, r_mid, out_dim]."""
+        mid = self.resolution_size[3]
+        X = ops.bilinear(X, mid[0], mid[1], None)
+        out = torch.empty(X.shape[0], mid[0], mid[1], self.conv.conv_layer.out_channels, device=X.device, dtype=X.dtype)
+        twice = 'silu2' if self.activation == 'silu' else 'relu'
+        return self.conv.forward_nhwc(X, 0, out, 0, act=twice)
+
+    def forward(self, X: Tensor) -> Tensor:
+        r = self.resolution_size[4]
+        return ops.bilinear(self.forward_mid(X), r[0], r[1], None)

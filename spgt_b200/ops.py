@@ -27,6 +27,50 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+# kernels launched by one call of each entry point (everything else launches one)
+_KERNELS_PER_CALL = {'spgt_batched_skinny_gemm': 2, 'spgt_spectral_conv2d_fwd': 5}
+LAUNCHES = 0          # running count of kernels launched through this module
+_PROFILE = None       # None, or a dict name -> list of (start_event, end_event) filled while profiling
+
+
+def _call(name: str, *args) -> None:
+    global LAUNCHES
+    fn = getattr(lib, name)
+    prof = _PROFILE
+    if prof is not None and (prof.get('__only__') is None or name in prof['__only__']):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        code = fn(*args)
+        e1.record()
+        prof.setdefault(name, []).append((e0, e1))
+    else:
+        code = fn(*args)
+    check(code, name)
+    LAUNCHES += _KERNELS_PER_CALL.get(name, 1)
+
+
+class profile_ops:
+    """Context manager: CUDA-event timing around every entry point (or only the named ones) on the current stream.
+    After the block (and a synchronize) `times_ms()` gives name -> list of durations."""
+
+    def __init__(self, only=None):
+        self.records = {'__only__': set(only) if only else None}
+
+    def __enter__(self):
+        global _PROFILE
+        self._prev, _PROFILE = _PROFILE, self.records
+        return self
+
+    def __exit__(self, *exc):
+        global _PROFILE
+        _PROFILE = self._prev
+        return False
+
+    def times_ms(self):
+        torch.cuda.synchronize()
+        return {k: [a.elapsed_time(b) for a, b in v] for k, v in self.records.items() if k != '__only__'}
+
+
 def _chk(t: Tensor, name: str, dtype=torch.float32) -> Tensor:
     if not isinstance(t, Tensor):
         raise TypeError(f'{name} must be a torch.Tensor')
@@ -54,8 +98,8 @@ def projpos(x: Tensor, weight: Tensor, bias: Optional[Tensor], position: Tensor,
     B, S, D = x.shape
     out = torch.empty(B, num_head, dim_position + dim_head, S, device=x.device, dtype=x.dtype)
     with torch.cuda.device(x.device):
-        check(lib.spgt_projpos_fwd(x.data_ptr(), weight.data_ptr(), _p(bias), position.data_ptr(), out.data_ptr(),
-                                   B, S, D, num_head, dim_head, dim_position, _stream()), 'spgt_projpos_fwd')
+        _call('spgt_projpos_fwd', x.data_ptr(), weight.data_ptr(), _p(bias), position.data_ptr(), out.data_ptr(),
+                                   B, S, D, num_head, dim_head, dim_position, _stream())
     return out
 
 
@@ -69,9 +113,9 @@ def projpos_lnorm(x: Tensor, weight: Tensor, bias: Optional[Tensor], ln_weight: 
     out = torch.empty(B, num_head, dim_position + dim_head, S, device=x.device, dtype=x.dtype)
     inv = torch.empty(B, num_head, S, device=x.device, dtype=x.dtype) if return_invsigma else None
     with torch.cuda.device(x.device):
-        check(lib.spgt_projpos_lnorm_fwd(x.data_ptr(), weight.data_ptr(), _p(bias), ln_weight.data_ptr(), ln_bias.data_ptr(),
+        _call('spgt_projpos_lnorm_fwd', x.data_ptr(), weight.data_ptr(), _p(bias), ln_weight.data_ptr(), ln_bias.data_ptr(),
                                          float(norm_eps), position.data_ptr(), out.data_ptr(), _p(inv),
-                                         B, S, D, num_head, dim_head, dim_position, _stream()), 'spgt_projpos_lnorm_fwd')
+                                         B, S, D, num_head, dim_head, dim_position, _stream())
     return (out, inv) if return_invsigma else out
 
 
@@ -81,10 +125,10 @@ def projpos_qkv(x, wq, bq, wk, bk, wv, bv, lnwk, lnbk, lnwv, lnbv, eps, position
     B, S, D = x.shape
     q, k, v = (torch.empty(B, num_head, dim_position + dim_head, S, device=x.device, dtype=x.dtype) for _ in range(3))
     with torch.cuda.device(x.device):
-        check(lib.spgt_projpos_qkv_fwd(x.data_ptr(), wq.data_ptr(), _p(bq), wk.data_ptr(), _p(bk), wv.data_ptr(), _p(bv),
+        _call('spgt_projpos_qkv_fwd', x.data_ptr(), wq.data_ptr(), _p(bq), wk.data_ptr(), _p(bk), wv.data_ptr(), _p(bv),
                                        lnwk.data_ptr(), lnbk.data_ptr(), lnwv.data_ptr(), lnbv.data_ptr(), float(eps),
                                        position.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                       B, S, D, num_head, dim_head, dim_position, _stream()), 'spgt_projpos_qkv_fwd')
+                                       B, S, D, num_head, dim_head, dim_position, _stream())
     return q, k, v
 
 
@@ -97,8 +141,8 @@ def galerkin_attention(Q: Tensor, K: Tensor, V: Tensor, merged_heads: bool = Fal
     out = torch.empty(shape, device=Q.device, dtype=Q.dtype)
     T = torch.empty(B, H, dpk, dpk, device=Q.device, dtype=Q.dtype) if return_kv else None
     with torch.cuda.device(Q.device):
-        check(lib.spgt_galerkin_attn_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), _p(T),
-                                         B, H, dpk, S, int(merged_heads), _stream()), 'spgt_galerkin_attn_fwd')
+        _call('spgt_galerkin_attn_fwd', Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), _p(T),
+                                         B, H, dpk, S, int(merged_heads), _stream())
     return (out, T) if return_kv else out
 
 
@@ -117,9 +161,8 @@ def batched_skinny_gemm(A: Tensor, Bm: Tensor, alpha: float = 1.0, workspace: Op
     if workspace is None:
         workspace = torch.empty(need, device=A.device, dtype=torch.uint8)
     with torch.cuda.device(A.device):
-        check(lib.spgt_batched_skinny_gemm(A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(), float(alpha), M, N, K, batch,
-                                           workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream()),
-              'spgt_batched_skinny_gemm')
+        _call('spgt_batched_skinny_gemm', A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(), float(alpha), M, N, K, batch,
+                                           workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream())
     return Cm
 
 
@@ -133,7 +176,7 @@ def batched_transpose(X: Tensor, batch_list: Sequence[int], M_list: Sequence[int
         raise ValueError('X does not have prod(batch)*prod(M)*prod(N) elements')
     out = torch.empty(*batch_list, *N_list, *M_list, device=X.device, dtype=X.dtype)
     with torch.cuda.device(X.device):
-        check(lib.spgt_batched_transpose(X.data_ptr(), out.data_ptr(), M, N, b, _stream()), 'spgt_batched_transpose')
+        _call('spgt_batched_transpose', X.data_ptr(), out.data_ptr(), M, N, b, _stream())
     return out
 
 
@@ -145,8 +188,8 @@ def transpose_gather_dual(src: Tensor, dim_list, H_all, W_all, H_low, W_low, hb1
     o1 = torch.empty(H_low, W_low, *dim_list, device=src.device, dtype=src.dtype)
     o2 = torch.empty_like(o1)
     with torch.cuda.device(src.device):
-        check(lib.spgt_transpose_gather_dual(src.data_ptr(), o1.data_ptr(), o2.data_ptr(), dim, H_all, W_all, H_low, W_low,
-                                             hb1, wb1, hb2, wb2, _stream()), 'spgt_transpose_gather_dual')
+        _call('spgt_transpose_gather_dual', src.data_ptr(), o1.data_ptr(), o2.data_ptr(), dim, H_all, W_all, H_low, W_low,
+                                             hb1, wb1, hb2, wb2, _stream())
     return o1, o2
 
 
@@ -157,8 +200,8 @@ def transpose_scatter_dual(src1: Tensor, src2: Tensor, dim_list, H_all, W_all, H
         raise ValueError('src1/src2 do not have H_low*W_low*prod(dim) elements')
     out = torch.empty(*dim_list, H_all, W_all, device=src1.device, dtype=src1.dtype)
     with torch.cuda.device(src1.device):
-        check(lib.spgt_transpose_scatter_dual(src1.data_ptr(), src2.data_ptr(), out.data_ptr(), dim, H_all, W_all,
-                                              H_low, W_low, hb1, wb1, hb2, wb2, _stream()), 'spgt_transpose_scatter_dual')
+        _call('spgt_transpose_scatter_dual', src1.data_ptr(), src2.data_ptr(), out.data_ptr(), dim, H_all, W_all,
+                                              H_low, W_low, hb1, wb1, hb2, wb2, _stream())
     return out
 
 
@@ -189,8 +232,8 @@ def linear(x: Tensor, w_kn: Tensor, bias: Optional[Tensor], N: int, act=None, re
     if residual is not None:
         _chk(residual, 'residual')
     with torch.cuda.device(x.device):
-        check(lib.spgt_linear_fwd(x.data_ptr(), K, w_kn.data_ptr(), w_kn.shape[1], _p(bias), _p(residual), N,
-                                  out.data_ptr(), N, rows, K, N, act_code(act), _stream()), 'spgt_linear_fwd')
+        _call('spgt_linear_fwd', x.data_ptr(), K, w_kn.data_ptr(), w_kn.shape[1], _p(bias), _p(residual), N,
+                                  out.data_ptr(), N, rows, K, N, act_code(act), _stream())
     return out
 
 
@@ -201,9 +244,8 @@ def conv3x3(x: Tensor, cin_off: int, Cin: int, w_kn: Tensor, bias: Tensor, y: Te
     if y.shape[:3] != x.shape[:3]:
         raise ValueError('x and y must share [B, H, W]')
     with torch.cuda.device(x.device):
-        check(lib.spgt_conv3x3_fwd(x.data_ptr(), cp, cin_off, Cin, w_kn.data_ptr(), w_kn.shape[1], bias.data_ptr(),
-                                   y.data_ptr(), y.shape[3], cout_off, Cout, B, Hh, Ww, act_code(act), _stream()),
-              'spgt_conv3x3_fwd')
+        _call('spgt_conv3x3_fwd', x.data_ptr(), cp, cin_off, Cin, w_kn.data_ptr(), w_kn.shape[1], bias.data_ptr(),
+                                   y.data_ptr(), y.shape[3], cout_off, Cout, B, Hh, Ww, act_code(act), _stream())
     return y
 
 
@@ -212,8 +254,7 @@ def bilinear(x: Tensor, Ho: int, Wo: int, act=None) -> Tensor:
     B, Hi, Wi, Cc = x.shape
     y = torch.empty(B, Ho, Wo, Cc, device=x.device, dtype=x.dtype)
     with torch.cuda.device(x.device):
-        check(lib.spgt_bilinear_fwd(x.data_ptr(), y.data_ptr(), B, Hi, Wi, Ho, Wo, Cc, act_code(act), _stream()),
-              'spgt_bilinear_fwd')
+        _call('spgt_bilinear_fwd', x.data_ptr(), y.data_ptr(), B, Hi, Wi, Ho, Wo, Cc, act_code(act), _stream())
     return y
 
 
@@ -224,8 +265,8 @@ def conv0_down(node: Tensor, w9: Tensor, bias: Tensor, Ho: int, Wo: int, act) ->
     Cout = w9.shape[1]
     y = torch.empty(B, Ho, Wo, Cout, device=node.device, dtype=node.dtype)
     with torch.cuda.device(node.device):
-        check(lib.spgt_conv0_down_fwd(node.data_ptr(), w9.data_ptr(), bias.data_ptr(), y.data_ptr(), B, Hi, Wi, Ho, Wo, Cout,
-                                      act_code(act), _stream()), 'spgt_conv0_down_fwd')
+        _call('spgt_conv0_down_fwd', node.data_ptr(), w9.data_ptr(), bias.data_ptr(), y.data_ptr(), B, Hi, Wi, Ho, Wo, Cout,
+                                      act_code(act), _stream())
     return y
 
 
@@ -234,21 +275,22 @@ def upsample_grid(uw: Tensor, grid: Tensor, wg: Tensor, bias: Tensor, Ho: int, W
     B, Hi, Wi, Cc = uw.shape
     y = torch.empty(B, Ho, Wo, Cc, device=uw.device, dtype=uw.dtype)
     with torch.cuda.device(uw.device):
-        check(lib.spgt_upsample_grid_fwd(uw.data_ptr(), grid.data_ptr(), wg.data_ptr(), bias.data_ptr(), y.data_ptr(),
-                                         B, Hi, Wi, Ho, Wo, Cc, _stream()), 'spgt_upsample_grid_fwd')
+        _call('spgt_upsample_grid_fwd', uw.data_ptr(), grid.data_ptr(), wg.data_ptr(), bias.data_ptr(), y.data_ptr(),
+                                         B, Hi, Wi, Ho, Wo, Cc, _stream())
     return y
 
 
 def decoder_head(x: Tensor, w1_kn: Tensor, b1: Tensor, w2: Tensor, b2: float, scale: float, shift: float,
-                 dirichlet: bool, act) -> Tensor:
-    """x [B,H,W,K] -> [B,H,W,1]: ((act(x@w1+b1) . w2) + b2) * scale + shift with an optional zero frame."""
+                 dirichlet: bool, act, scale_map: Optional[Tensor] = None, shift_map: Optional[Tensor] = None) -> Tensor:
+    """x [B,H,W,K] -> [B,H,W,1]: ((act(x@w1+b1) . w2) + b2) * scale + shift with an optional zero frame.
+    scale_map / shift_map [H*W] replace the scalars per grid node when given."""
     _chk(x, 'x'); _chk(w1_kn, 'w1'); _chk(b1, 'b1'); _chk(w2, 'w2')
     B, Hh, Ww, K = x.shape
     out = torch.empty(B, Hh, Ww, 1, device=x.device, dtype=x.dtype)
     with torch.cuda.device(x.device):
-        check(lib.spgt_decoder_head_fwd(x.data_ptr(), w1_kn.data_ptr(), b1.data_ptr(), w2.data_ptr(), float(b2), float(scale),
-                                        float(shift), int(dirichlet), out.data_ptr(), B, Hh, Ww, K, w1_kn.shape[1],
-                                        act_code(act), _stream()), 'spgt_decoder_head_fwd')
+        _call('spgt_decoder_head_fwd', x.data_ptr(), w1_kn.data_ptr(), b1.data_ptr(), w2.data_ptr(), float(b2), float(scale),
+                                        float(shift), _p(scale_map), _p(shift_map), int(dirichlet), out.data_ptr(), B, Hh, Ww, K, w1_kn.shape[1],
+                                        act_code(act), _stream())
     return out
 
 
@@ -267,7 +309,7 @@ def spectral_tables(r: int, m: int, device) -> Tensor:
             raise ValueError(f'unsupported spectral shape r={r}, m={m}')
         t = torch.empty(n, device=device, dtype=torch.uint8)
         with torch.cuda.device(device):
-            check(lib.spgt_spectral_tables_init(t.data_ptr(), n, r, m, _stream()), 'spgt_spectral_tables_init')
+            _call('spgt_spectral_tables_init', t.data_ptr(), n, r, m, _stream())
         _TABLES[key] = t
     return _TABLES[key]
 
@@ -287,7 +329,7 @@ def spectral_conv2d(x: Tensor, wr_kn: Tensor, br: Tensor, fw0: Tensor, fw1: Tens
         workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
     y = torch.empty_like(x)
     with torch.cuda.device(x.device):
-        check(lib.spgt_spectral_conv2d_fwd(x.data_ptr(), wr_kn.data_ptr(), br.data_ptr(), fw0.data_ptr(), fw1.data_ptr(),
+        _call('spgt_spectral_conv2d_fwd', x.data_ptr(), wr_kn.data_ptr(), br.data_ptr(), fw0.data_ptr(), fw1.data_ptr(),
                                            tab.data_ptr(), workspace.data_ptr(), workspace.numel(), y.data_ptr(),
-                                           B, r, Cc, mode, act_code(act), _stream()), 'spgt_spectral_conv2d_fwd')
+                                           B, r, Cc, mode, act_code(act), _stream())
     return y

@@ -1,0 +1,120 @@
+"""Batch-sharded multi-GPU Darcy inference (reference: run/ddp_darcy_inference.py:15-72).
+
+One process per GPU (torchrun).  Every sample is independent through the whole forward, so the global sample
+range is cut into one contiguous slice per rank and there is no collective inside the forward; NCCL is used only
+after the last batch, to gather the predictions and to sum the metric.  (The reference wraps the model in
+DistributedDataParallel, whose only effect at inference is a parameter broadcast at construction; here every
+rank builds identical weights from the same seed or loads the same checkpoint.)
+
+    torchrun --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 -m spgt_b200.run.ddp_darcy_inference
+"""
+import os
+import time
+from typing import Callable, Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_total: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous slice [begin, end) of rank; sizes differ by at most one and earlier ranks get the larger ones."""
+    base, extra = divmod(n_total, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def distributed_initialize(backend: Optional[str] = None) -> Tuple[int, int, int]:
+    """env:// rendezvous from RANK / WORLD_SIZE / LOCAL_RANK / MASTER_*; returns (rank, world, local_rank).
+    Single-process runs (no RANK in the environment) do not create a process group."""
+    if 'RANK' not in os.environ:
+        return 0, 1, 0
+    rank, world, local = int(os.environ['RANK']), int(os.environ['WORLD_SIZE']), int(os.environ.get('LOCAL_RANK', 0))
+    if not dist.is_initialized():
+        backend = backend or ('nccl' if torch.cuda.is_available() else 'gloo')
+        if backend == 'nccl':
+            torch.cuda.set_device(local)
+        dist.init_process_group(backend=backend, init_method='env://')
+    return rank, world, local
+
+
+def gather_predictions(local_pred: torch.Tensor, n_total: int, rank: int, world: int) -> torch.Tensor:
+    """All ranks obtain [n_total, ...] in global sample order from their contiguous slices (sizes may differ by 1)."""
+    if world == 1:
+        return local_pred
+    sizes = [shard_range(n_total, r, world) for r in range(world)]
+    counts = [e - b for b, e in sizes]
+    if len(set(counts)) == 1:
+        out = torch.empty((n_total, *local_pred.shape[1:]), dtype=local_pred.dtype, device=local_pred.device)
+        dist.all_gather_into_tensor(out, local_pred.contiguous())
+        return out
+    parts = [torch.empty((c, *local_pred.shape[1:]), dtype=local_pred.dtype, device=local_pred.device) for c in counts]
+    dist.all_gather(parts, local_pred.contiguous())
+    return torch.cat(parts, dim=0)
+
+
+def reduce_metric(metric_sum: torch.Tensor, count: torch.Tensor, world: int) -> float:
+    """Global mean of the per-sample metric from per-rank (sum, count)."""
+    packed = torch.stack([metric_sum.reshape(()).double(), count.reshape(()).double()])
+    if world > 1:
+        dist.all_reduce(packed, op=dist.ReduceOp.SUM)
+    return float(packed[0] / packed[1].clamp_min(1.0))
+
+
+def run_sharded(forward: Callable[[Dict[str, torch.Tensor]], torch.Tensor], make_batch: Callable[[range], Dict[str, torch.Tensor]],
+                n_total: int, batch_size: int, rank: int, world: int, target_fn: Optional[Callable] = None):
+    """Evaluate samples [0, n_total) sharded over ranks.  `make_batch(range)` builds the inputs of global sample
+    indices, `forward(batch)` returns predictions [n, ...].  Returns (all predictions in global order, metric or None)."""
+    from ..engine.metric import relative_l2_sums
+    begin, end = shard_range(n_total, rank, world)
+    preds, msum, cnt = [], None, None
+    for b0 in range(begin, end, batch_size):
+        idx = range(b0, min(b0 + batch_size, end))
+        batch = make_batch(idx)
+        pred = forward(batch)
+        preds.append(pred)
+        if target_fn is not None:
+            s, c = relative_l2_sums(pred, target_fn(idx, batch))
+            msum = s if msum is None else msum + s
+            cnt = c if cnt is None else cnt + c
+    local = torch.cat(preds, dim=0) if preds else None
+    full = gather_predictions(local, n_total, rank, world)
+    metric = reduce_metric(msum, cnt, world) if msum is not None else None
+    return full, metric
+
+
+def darcy_inference_ddp(cfg: dict, checkpoint: Optional[dict] = None, num_samples: int = 64, seed: int = 4):
+    """Synthetic-field stand-in for the reference driver: build the model (checkpoint['Module'] if given, else
+    seeded random init), shard `num_samples` synthetic coefficient fields over the ranks in batches of
+    2 * cfg['batch_size'] (as the reference's DataLoader does), gather predictions."""
+    from ..dataset.darcy_dataset import GaussNormalizer, synthetic_darcy_batch
+    from ..network.sp_model import Sp_GalerkinTransformer2D
+    rank, world, local = distributed_initialize()
+    device = torch.device('cuda', local)
+    torch.cuda.set_device(device)
+    cfg = dict(cfg)
+    cfg.setdefault('target_normalizer', GaussNormalizer())
+    torch.manual_seed(seed)
+    model = Sp_GalerkinTransformer2D(cfg)
+    if checkpoint is not None:
+        model.load_state_dict(checkpoint['Module'])
+    model = model.to(device).eval()
+
+    def make_batch(idx):
+        data = synthetic_darcy_batch(idx, cfg['fine_resolution'], cfg['subsample_node'], cfg['subsample_attn'], seed)
+        return {k: v.to(device, non_blocking=True) for k, v in data.items()}
+
+    t0 = time.time()
+    pred, _ = run_sharded(lambda b: model(b['node'], b['position'], b['grid']), make_batch, num_samples,
+                          2 * cfg['batch_size'], rank, world)
+    torch.cuda.synchronize()
+    if rank == 0:
+        print(f'========== valid_time: {time.time() - t0:.6f} ==========')
+        print(f'========== predictions: {tuple(pred.shape)} on {world} rank(s) ==========')
+    return pred
+
+
+if __name__ == '__main__':
+    from ..config.config_accessor import get_darcy_config
+    darcy_inference_ddp(get_darcy_config(2, 8, num_frequence_mode=12))
+    if dist.is_initialized():
+        dist.destroy_process_group()

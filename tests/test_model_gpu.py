@@ -1,0 +1,99 @@
+"""Layer- and model-level parity on a B200: recorded reference outputs (tests/golden) and the CPU oracle."""
+import pytest
+import torch
+
+from tests.helpers import load_golden, rel_l2
+from oracle import gt_oracle as O
+
+pytestmark = pytest.mark.gpu
+PER_LAYER_TOL = 1e-5     # relative L2 per layer
+MODEL_TOL = 1e-4         # relative L2 at the model output
+
+
+def small_cfg():
+    from spgt_b200.config.config_accessor import get_darcy_config
+    from spgt_b200.dataset.darcy_dataset import GaussNormalizer
+    cfg = get_darcy_config(3, 6, num_frequence_mode=4, clamp_attn=False, fine_resolution=85, num_encoder_layer=2)
+    cfg['target_normalizer'] = GaussNormalizer()
+    return cfg
+
+
+def test_attention_layer_against_golden():
+    from spgt_b200.network.sp_layer import Sp_GalerkinAttention
+    d, p = load_golden('attention_layer.npz')
+    layer = Sp_GalerkinAttention(128, 4, 2, 1e-6, 0.0, 0.0, 0.01, 0.01, False)
+    layer.load_state_dict(p)
+    layer = layer.cuda()
+    x, pos = d['x'].cuda(), d['pos'].cuda()
+    with torch.no_grad():
+        out = layer(x, x, x, pos)
+        out2 = layer(x, x.clone(), x.clone(), pos)       # separate-launch path
+    assert rel_l2(out, d['out']) < PER_LAYER_TOL
+    assert torch.equal(out, out2)
+
+
+def test_spectral_layer_both_structures():
+    from spgt_b200.network.sp_layer import Sp_SpectralConv2D
+    d, p = load_golden('spectral_layer.npz')
+    for structure in ('fused', 'reference'):
+        layer = Sp_SpectralConv2D(32, 32, 4, 0.0, 'silu', structure=structure)
+        layer.load_state_dict(p)
+        layer = layer.cuda()
+        with torch.no_grad():
+            y = layer(d['x'].cuda())
+        assert rel_l2(y, d['y']) < PER_LAYER_TOL, structure
+
+
+def test_small_model_against_golden():
+    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+    d, p = load_golden('model_small.npz')
+    model = Sp_GalerkinTransformer2D(small_cfg())
+    missing = model.load_state_dict(p, strict=True)
+    model = model.cuda().eval()
+    node, position, grid = d['node'].cuda(), d['position'].cuda(), d['grid'].cuda()
+    taps = {}
+    out = model(node, position, grid, taps)
+    assert rel_l2(taps['down'], d['t_down']) < PER_LAYER_TOL
+    assert rel_l2(taps['enc0'].reshape(-1), d['t_enc0'].reshape(-1)) < PER_LAYER_TOL
+    assert rel_l2(taps['enc1'].reshape(-1), d['t_enc1'].reshape(-1)) < 2 * PER_LAYER_TOL      # two layers deep
+    with torch.no_grad():
+        up = model.up_scaler(d['t_enc1'].reshape(1, 15, 15, 128).cuda())
+        dec = model.decoder_regressor(d['t_up'].cuda(), grid)
+        dec_fused = model.decoder_regressor.forward_from_mid(
+            model.up_scaler.forward_mid(d['t_enc1'].reshape(1, 15, 15, 128).cuda()), grid, 1.0, 0.0, False)
+    assert rel_l2(up, d['t_up']) < PER_LAYER_TOL
+    assert rel_l2(dec, d['t_decoder']) < 3 * PER_LAYER_TOL            # fc + two spectral layers + head
+    assert rel_l2(dec_fused, d['t_decoder']) < 3 * PER_LAYER_TOL
+    assert rel_l2(out, d['out']) < MODEL_TOL
+    assert float(out[:, 0].abs().max()) == 0.0 and float(out[:, :, -1].abs().max()) == 0.0
+    assert torch.equal(out, model(node, position, grid))                 # bitwise reproducible
+
+
+@pytest.mark.parametrize('sub_node,sub_attn,batch', [(3, 10, 2), (2, 8, 1)])
+def test_full_size_model_against_oracle(sub_node, sub_attn, batch):
+    """BASELINE configs 1 (141^2/43^2) and 4 (211^2/53^2) with random-init weights, vs the fp32 CPU oracle."""
+    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+    from spgt_b200.config.config_accessor import get_darcy_config
+    from spgt_b200.dataset.darcy_dataset import GaussNormalizer, synthetic_darcy_batch
+    cfg = get_darcy_config(sub_node, sub_attn, num_frequence_mode=12)
+    cfg['target_normalizer'] = GaussNormalizer()
+    torch.manual_seed(sub_node)
+    model = Sp_GalerkinTransformer2D(cfg).eval()
+    with torch.no_grad():
+        for n, prm in model.named_parameters():
+            if 'fourier_weight' in n:
+                prm.mul_(30.0)          # make the spectral branch contribute visibly
+    data = synthetic_darcy_batch(range(batch), 421, sub_node, cfg['subsample_attn'], seed=sub_node)
+    ocfg = O.default_config(421, sub_node, cfg['subsample_attn'], 12)
+    assert tuple(ocfg['resolution_size']) == tuple(cfg['resolution_size'])
+    p = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    ref_taps = {}
+    torch.set_num_threads(max(1, torch.get_num_threads()))
+    ref = O.model_forward(data['node'], data['position'], data['grid'], p, ocfg, ref_taps)
+    model = model.cuda()
+    taps = {}
+    out = model(data['node'].cuda(), data['position'].cuda(), data['grid'].cuda(), taps)
+    assert rel_l2(taps['down'], ref_taps['down']) < PER_LAYER_TOL
+    for i in range(6):
+        assert rel_l2(taps[f'enc{i}'].reshape(-1), ref_taps[f'enc{i}'].reshape(-1)) < (i + 1) * PER_LAYER_TOL, i
+    assert rel_l2(out, ref) < MODEL_TOL
