@@ -143,8 +143,89 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def micro_cases(device):
+    """Single-op workloads at the benchmark's shapes: name -> (callable, algorithmic bytes, flops)."""
+    from spgt_b200 import ops
+    g = torch.Generator(device='cpu').manual_seed(2)
+    rnd = lambda *shape: torch.randn(*shape, generator=g).to(device)
+    cases = {}
+
+    def attn(B=64, H=4, S=2809):
+        Q, K, V = rnd(B, H, 34, S), rnd(B, H, 34, S), rnd(B, H, 34, S)
+        return (lambda: ops.galerkin_attention(Q, K, V)), 4 * B * H * 34 * S * 4, 4 * B * H * 34 * 34 * S
+    cases['attn'] = attn
+    cases['attn_1849'] = lambda: attn(64, 4, 1849)
+
+    def skinny(S):
+        def make():
+            A, Bm = rnd(64, 32, S), rnd(64, S, 32)
+            ws = torch.empty(ops.skinny_gemm_workspace_bytes(32, 32, S, 64), dtype=torch.uint8, device=device)
+            return (lambda: ops.batched_skinny_gemm(A, Bm, 1.0 / S, ws)), 64 * (2 * S * 32 + 32 * 32) * 4, 64 * 2 * S * 32 * 32
+        return make
+    for S in (1849, 19881, 44521):
+        cases[f'skinny_{S}'] = skinny(S)
+
+    def spectral(B=8, r=211, m=12):
+        x, wr, br = rnd(B, r, r, 32), rnd(32, 32) / 6, rnd(32)
+        f0, f1 = rnd(m, m, 32, 32, 2) / 1024, rnd(m, m, 32, 32, 2) / 1024
+        ws = torch.empty(int(ops.lib.spgt_spectral_workspace_bytes(B, r, m, 32)), dtype=torch.uint8, device=device)
+        flops = B * r * (2 * 32 * 2 * m * r * 2 + 2 * r * 32 * 32) + B * 8 * 2 * m * r * m * 32 * 2
+        return (lambda: ops.spectral_conv2d(x, wr, br, f0, f1, m, 'silu', ws)), 2 * B * r * r * 32 * 4 + 2 * 2 * m * m * 32 * 32 * 8, flops
+    cases['spectral'] = spectral
+    cases['spectral_b64'] = lambda: spectral(64)
+
+    def qkv(B=64, S=2809):
+        x, pos = rnd(B, S, 128), rnd(B, S, 2)
+        w, b_, lw, lb = [rnd(128, 128) / 11 for _ in range(3)], [rnd(128) for _ in range(3)], rnd(4, 32), rnd(4, 32)
+        fn = lambda: ops.projpos_qkv(x, w[0], b_[0], w[1], b_[1], w[2], b_[2], lw, lb, lw, lb, 1e-6, pos, 4, 32, 2)
+        return fn, B * S * (128 + 2 + 3 * 136) * 4, 3 * 2 * B * S * 128 * 128
+    cases['qkv'] = qkv
+
+    def ffn(B=64, S=2809):
+        x, w1, b1, w2, b2 = rnd(B * S, 128), rnd(128, 256) / 11, rnd(256), rnd(256, 128) / 16, rnd(128)
+        def fn():
+            h = ops.linear(x, w1, b1, 256, 'relu')
+            return ops.linear(h, w2, b2, 128, None, x)
+        return fn, B * S * (128 + 256 + 256 + 128 + 128) * 4, 2 * 2 * B * S * 128 * 256
+    cases['ffn'] = ffn
+
+    def conv(B=64, Hh=106, C=128):
+        x, w, b_ = rnd(B, Hh, Hh, C), rnd(9 * C, C) / 34, rnd(C)
+        y = torch.empty_like(x)
+        return (lambda: ops.conv3x3(x, 0, C, w, b_, y, 0, C, 'silu2')), 2 * B * Hh * Hh * C * 4, 2 * B * Hh * Hh * 9 * C * C
+    cases['conv128'] = conv
+    return cases
+
+
+def run_micro(args):
+    """One op in isolation: JSON line with achieved GB/s (algorithmic bytes) and TFLOP/s; L2 is flushed between
+    timed launches by writing a 256 MB buffer."""
+    from spgt_b200 import ops
+    device = torch.device('cuda', 0)
+    torch.cuda.set_device(device)
+    fn, nbytes, flops = micro_cases(device)[args.micro]()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    times = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    med = times[len(times) // 2]
+    peak, kind = measured_peak()
+    print(json.dumps({'micro': args.micro, 'median_ms': med, 'min_ms': times[0], 'algorithmic_bytes': nbytes, 'flops': flops,
+                      'GBps': nbytes / med / 1e6, 'frac_of_hbm_peak': nbytes / med / 1e6 / peak, 'peak_kind': kind,
+                      'TFLOPs': flops / med / 1e9, 'steps': args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument('--micro', default=None, help='time one op in isolation (see micro_cases) instead of the model')
+    ap.add_argument('--tune', default=None, help='key=value passed to spgt_set_tuning before running (experiments)')
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
@@ -158,6 +239,13 @@ def main():
 
     if args.impl == 'reference':
         run_reference(args, rank)
+        return
+    if args.tune:
+        from spgt_b200._lib import lib
+        k, v = args.tune.split('=')
+        assert lib.spgt_set_tuning(k.encode(), int(v)) == 0, 'unknown tuning key or value'
+    if args.micro:
+        run_micro(args)
         return
 
     from spgt_b200 import ops

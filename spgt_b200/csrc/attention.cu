@@ -123,15 +123,26 @@ galerkin_attn_kernel(const float* __restrict__ Q, const float* __restrict__ K, c
                 split_tf32(p[4], ahi[i][2], alo[i][2]);
                 split_tf32(p[8 * ATT_KP + 4], ahi[i][3], alo[i][3]);
             }
+            uint32_t bhi[NT][2], blo[NT][2];
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const float* p = vb + (n0[j] + g) * ATT_KP + kk;
-                uint32_t bhi[2], blo[2];
-                split_tf32(p[0], bhi[0], blo[0]);
-                split_tf32(p[4], bhi[1], blo[1]);
-#pragma unroll
-                for (int i = 0; i < MT; ++i) mma_3xtf32(acc[i][j], ahi[i], alo[i], bhi, blo);
+                split_tf32(p[0], bhi[j][0], blo[j][0]);
+                split_tf32(p[4], bhi[j][1], blo[j][1]);
             }
+            // three passes over all tiles: consecutive MMAs never touch the same accumulator
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(acc[i][j], alo[i], bhi[j]);
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(acc[i][j], ahi[i], blo[j]);
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(acc[i][j], ahi[i], bhi[j]);
         }
         __syncwarp();
     }
@@ -228,17 +239,27 @@ galerkin_attn_kernel(const float* __restrict__ Q, const float* __restrict__ K, c
                 split_tf32(p[4 * ATT_QP], ahi[i][2], alo[i][2]);
                 split_tf32(p[4 * ATT_QP + 8], ahi[i][3], alo[i][3]);
             }
+            uint32_t bhi[NT][2], blo[NT][2];
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int off = kr * ATT_QP + n0[j] + g;
-                uint32_t bhi[2], blo[2];
-                bhi[0] = __float_as_uint(Thi[off]);
-                bhi[1] = __float_as_uint(Thi[off + 4 * ATT_QP]);
-                blo[0] = __float_as_uint(Tlo[off]);
-                blo[1] = __float_as_uint(Tlo[off + 4 * ATT_QP]);
-#pragma unroll
-                for (int i = 0; i < 2; ++i) mma_3xtf32(o[i][j], ahi[i], alo[i], bhi, blo);
+                bhi[j][0] = __float_as_uint(Thi[off]);
+                bhi[j][1] = __float_as_uint(Thi[off + 4 * ATT_QP]);
+                blo[j][0] = __float_as_uint(Tlo[off]);
+                blo[j][1] = __float_as_uint(Tlo[off + 4 * ATT_QP]);
             }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(o[i][j], alo[i], bhi[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(o[i][j], ahi[i], blo[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(o[i][j], ahi[i], bhi[j]);
         }
         // stage the 32 x D tile in shared memory in the global row-major order, then store coalesced
         float* os = wreg + L::OS_OFF;
@@ -376,15 +397,25 @@ skinny_splitk_kernel(const float* __restrict__ A, const float* __restrict__ B, f
                 split_tf32(p[4], ahi[i][2], alo[i][2]);
                 split_tf32(p[8 * SK_AP + 4], ahi[i][3], alo[i][3]);
             }
+            uint32_t bhi[4][2], blo[4][2];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float* p = bs + kk * SK_BP + 8 * j + g;
-                uint32_t bhi[2], blo[2];
-                split_tf32(p[0], bhi[0], blo[0]);
-                split_tf32(p[4 * SK_BP], bhi[1], blo[1]);
-#pragma unroll
-                for (int i = 0; i < 2; ++i) mma_3xtf32(acc[i][j], ahi[i], alo[i], bhi, blo);
+                split_tf32(p[0], bhi[j][0], blo[j][0]);
+                split_tf32(p[4 * SK_BP], bhi[j][1], blo[j][1]);
             }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], alo[i], bhi[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ahi[i], blo[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ahi[i], bhi[j]);
         }
         __syncwarp();
     }

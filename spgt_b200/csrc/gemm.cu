@@ -163,14 +163,31 @@ __device__ __forceinline__ void gemm_mainloop(Loader& ld, const float* __restric
                 split_tf32(p[4], ahi[i][2], alo[i][2]);
                 split_tf32(p[8 * G_AP + 4], ahi[i][3], alo[i][3]);
             }
+            constexpr int JG = WN < 4 ? WN : 4;          // n-tiles per group: keeps the B fragments in registers
 #pragma unroll
-            for (int j = 0; j < WN; ++j) {
-                const float* p = bs + kk * L::BP + wn * (8 * WN) + j * 8 + g;
-                uint32_t bhi[2], blo[2];
-                split_tf32(p[0], bhi[0], blo[0]);
-                split_tf32(p[4 * L::BP], bhi[1], blo[1]);
+            for (int j0 = 0; j0 < WN; j0 += JG) {
+                uint32_t bhi[JG][2], blo[JG][2];
 #pragma unroll
-                for (int i = 0; i < 2; ++i) mma_3xtf32(acc[i][j], ahi[i], alo[i], bhi, blo);
+                for (int j = 0; j < JG; ++j) {
+                    if (j0 + j < WN) {
+                        const float* p = bs + kk * L::BP + wn * (8 * WN) + (j0 + j) * 8 + g;
+                        split_tf32(p[0], bhi[j][0], blo[j][0]);
+                        split_tf32(p[4 * L::BP], bhi[j][1], blo[j][1]);
+                    }
+                }
+                // three passes: consecutive MMAs never touch the same accumulator
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < JG; ++j) if (j0 + j < WN) mma_tf32(acc[i][j0 + j], alo[i], bhi[j]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < JG; ++j) if (j0 + j < WN) mma_tf32(acc[i][j0 + j], ahi[i], blo[j]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < JG; ++j) if (j0 + j < WN) mma_tf32(acc[i][j0 + j], ahi[i], bhi[j]);
             }
         }
     }

@@ -139,15 +139,25 @@ spectral_fwd_y_kernel(const float* __restrict__ X, const float* __restrict__ tab
                 split_tf32(p[4 * SP_XP1], ahi[i][2], alo[i][2]);
                 split_tf32(p[4 * SP_XP1 + 8], ahi[i][3], alo[i][3]);
             }
+            uint32_t bhi[NT][2], blo[NT][2];
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const float* p = fs + kk * SP_F1P + 8 * j + g;         // B[k=y][n=j]
-                uint32_t bhi[2], blo[2];
-                split_tf32(p[0], bhi[0], blo[0]);
-                split_tf32(p[4 * SP_F1P], bhi[1], blo[1]);
-#pragma unroll
-                for (int i = 0; i < 2; ++i) mma_3xtf32(acc[i][j], ahi[i], alo[i], bhi, blo);
+                split_tf32(p[0], bhi[j][0], blo[j][0]);
+                split_tf32(p[4 * SP_F1P], bhi[j][1], blo[j][1]);
             }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(acc[i][j], alo[i], bhi[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(acc[i][j], ahi[i], blo[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_tf32(acc[i][j], ahi[i], bhi[j]);
         }
         __syncwarp();
         if (chunk == nchunk - 1) {
@@ -352,15 +362,25 @@ spectral_inv_y_kernel(const float* __restrict__ X, const float* __restrict__ P, 
                 split_tf32(p[4], ahi[i][2], alo[i][2]);
                 split_tf32(p[8 * T.F3P + 4], ahi[i][3], alo[i][3]);
             }
+            uint32_t bhi[4][2], blo[4][2];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float* p = ps + kk * SP_PP + 8 * j + g;
-                uint32_t bhi[2], blo[2];
-                split_tf32(p[0], bhi[0], blo[0]);
-                split_tf32(p[4 * SP_PP], bhi[1], blo[1]);
-#pragma unroll
-                for (int i = 0; i < 2; ++i) mma_3xtf32(acc[i][j], ahi[i], alo[i], bhi, blo);
+                split_tf32(p[0], bhi[j][0], blo[j][0]);
+                split_tf32(p[4 * SP_PP], bhi[j][1], blo[j][1]);
             }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], alo[i], bhi[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ahi[i], blo[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ahi[i], bhi[j]);
         }
         // residual part: A = X chunk [32 y][32 i], B = Wr [32 i][32 o]
 #pragma unroll
@@ -375,15 +395,25 @@ spectral_inv_y_kernel(const float* __restrict__ X, const float* __restrict__ P, 
                 split_tf32(p[4], ahi[i][2], alo[i][2]);
                 split_tf32(p[8 * SP_XP3 + 4], ahi[i][3], alo[i][3]);
             }
+            uint32_t bhi[4][2], blo[4][2];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float* p = wr + kk * SP_PP + 8 * j + g;
-                uint32_t bhi[2], blo[2];
-                split_tf32(p[0], bhi[0], blo[0]);
-                split_tf32(p[4 * SP_PP], bhi[1], blo[1]);
-#pragma unroll
-                for (int i = 0; i < 2; ++i) mma_3xtf32(acc[i][j], ahi[i], alo[i], bhi, blo);
+                split_tf32(p[0], bhi[j][0], blo[j][0]);
+                split_tf32(p[4 * SP_PP], bhi[j][1], blo[j][1]);
             }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], alo[i], bhi[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ahi[i], blo[j]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ahi[i], bhi[j]);
         }
         __syncwarp();
         const int64_t row = gw + ri * nw;
