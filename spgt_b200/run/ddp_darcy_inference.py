@@ -47,9 +47,13 @@ def gather_predictions(local_pred: torch.Tensor, n_total: int, rank: int, world:
         out = torch.empty((n_total, *local_pred.shape[1:]), dtype=local_pred.dtype, device=local_pred.device)
         dist.all_gather_into_tensor(out, local_pred.contiguous())
         return out
-    parts = [torch.empty((c, *local_pred.shape[1:]), dtype=local_pred.dtype, device=local_pred.device) for c in counts]
-    dist.all_gather(parts, local_pred.contiguous())
-    return torch.cat(parts, dim=0)
+    # uneven slices: pad every rank's block to the largest count (collectives need equal sizes), then trim
+    cmax = max(counts)
+    padded = torch.zeros((cmax, *local_pred.shape[1:]), dtype=local_pred.dtype, device=local_pred.device)
+    padded[:local_pred.shape[0]] = local_pred
+    out = torch.empty((world * cmax, *local_pred.shape[1:]), dtype=local_pred.dtype, device=local_pred.device)
+    dist.all_gather_into_tensor(out, padded)
+    return torch.cat([out[r * cmax:r * cmax + c] for r, c in enumerate(counts)], dim=0)
 
 
 def reduce_metric(metric_sum: torch.Tensor, count: torch.Tensor, world: int) -> float:

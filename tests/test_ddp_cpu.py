@@ -1,0 +1,60 @@
+"""Sharding, gather and metric reduction of the multi-GPU driver, run as 2 gloo ranks on CPU."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from spgt_b200.run.ddp_darcy_inference import shard_range
+
+
+def test_shard_range_partitions_exactly():
+    for n, w in ((64, 8), (64, 1), (10, 4), (3, 8), (0, 2)):
+        spans = [shard_range(n, r, w) for r in range(w)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(w - 1))
+        sizes = [e - b for b, e in spans]
+        assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+
+
+def _worker(rank, world, port, n_total, batch, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    from spgt_b200.run.ddp_darcy_inference import distributed_initialize, run_sharded
+    r, w, _ = distributed_initialize('gloo')
+    assert (r, w) == (rank, world)
+
+    def make_batch(idx):
+        return {'node': torch.tensor([[float(i)] for i in idx]).view(-1, 1, 1, 1).expand(-1, 3, 3, 1).contiguous()}
+
+    forward = lambda b: b['node'] * 2.0 + 1.0                     # stands in for the model: sample i -> 2 i + 1
+    target = lambda idx, b: b['node'] * 2.0 + 1.5                  # constant offset -> known relative error
+    pred, metric = run_sharded(forward, make_batch, n_total, batch, r, w, target_fn=target)
+    torch.save({'pred': pred, 'metric': metric}, os.path.join(out_dir, f'rank{rank}.pt'))
+    dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
+
+
+def _run(n_total, batch, tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), n_total, batch, str(tmp_path)), nprocs=world, join=True)
+    res = [torch.load(os.path.join(tmp_path, f'rank{r}.pt')) for r in range(world)]
+    expect = (torch.arange(n_total, dtype=torch.float32) * 2 + 1).view(-1, 1, 1, 1).expand(-1, 3, 3, 1)
+    ref_metric = float((0.5 / (torch.arange(n_total, dtype=torch.float64) * 2 + 1.5)).mean())
+    for r in res:
+        assert torch.equal(r['pred'], expect)                      # every rank holds all samples, in global order
+        assert abs(r['metric'] - ref_metric) < 1e-6
+    return res
+
+
+def test_two_ranks_even_split(tmp_path):
+    _run(8, 3, tmp_path)
+
+
+def test_two_ranks_uneven_split(tmp_path):
+    _run(7, 2, tmp_path)
