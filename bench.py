@@ -194,6 +194,39 @@ def micro_cases(device):
         y = torch.empty_like(x)
         return (lambda: ops.conv3x3(x, 0, C, w, b_, y, 0, C, 'silu2')), 2 * B * Hh * Hh * C * 4, 2 * B * Hh * Hh * 9 * C * C
     cases['conv128'] = conv
+
+    def ffn_tc(B=64, S=2809):
+        x, w1, b1, w2, b2 = rnd(B * S, 128), ops.TcWeight(rnd(128, 256) / 11), rnd(256), ops.TcWeight(rnd(256, 128) / 16), rnd(128)
+        def fn():
+            h = ops.linear_tc(x, w1, b1, 'relu')
+            return ops.linear_tc(h, w2, b2, None, x)
+        return fn, B * S * (128 + 256 + 256 + 128 + 128) * 4, 2 * 2 * B * S * 128 * 256
+    cases['ffn_tc'] = ffn_tc
+
+    def lin_tc(B=64, S=2809, K=128, N=128):
+        x, w, b_ = rnd(B * S, K), ops.TcWeight(rnd(K, N) / 11), rnd(N)
+        return (lambda: ops.linear_tc(x, w, b_, None)), B * S * (K + N) * 4, 2 * B * S * K * N
+    cases['lin_tc'] = lin_tc
+    cases['lin_tc_k256'] = lambda: lin_tc(K=256)
+    cases['lin_tc_n32'] = lambda: lin_tc(N=32)
+
+    def qkv_tc(B=64, S=2809):
+        x, pos = rnd(B, S, 128), rnd(B, S, 2)
+        w, b_, lw, lb = ops.TcWeight(rnd(128, 384) / 11), [rnd(128) for _ in range(3)], rnd(4, 32), rnd(4, 32)
+        fn = lambda: ops.projpos_qkv_tc(x, w, b_[0], b_[1], b_[2], lw, lb, lw, lb, 1e-6, pos, 4, 32, 2)
+        return fn, B * S * (128 + 2 + 3 * 136) * 4, 3 * 2 * B * S * 128 * 128
+    cases['qkv_tc'] = qkv_tc
+
+    def conv_tc(B=64, Hh=106, C=128):
+        x, w, b_ = rnd(B, Hh, Hh, C), ops.TcWeight(rnd(9 * C, C) / 34), rnd(C)
+        y = torch.empty_like(x)
+        return (lambda: ops.conv3x3_tc(x, 0, C, w, b_, y, 0, C, 'silu2')), 2 * B * Hh * Hh * C * 4, 2 * B * Hh * Hh * 9 * C * C
+    cases['conv128_tc'] = conv_tc
+
+    def head_tc(B=64, r=211):
+        x, w1, b1, w2 = rnd(B, r, r, 32), ops.TcWeight(rnd(32, 128) / 6), rnd(128), rnd(128)
+        return (lambda: ops.decoder_head_tc(x, w1, b1, w2, 0.1, 1.0, 0.0, True, 'silu')), B * r * r * 33 * 4, 2 * B * r * r * 32 * 128
+    cases['head_tc'] = head_tc
     return cases
 
 

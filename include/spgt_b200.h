@@ -133,6 +133,12 @@ int spgt_conv3x3_fwd(const float* x, int cin_pitch, int cin_off, int Cin, const 
 int spgt_bilinear_fwd(const float* x, float* y, int B, int Hi, int Wi, int Ho, int Wo, int C, int act,
                       spgt_stream_t stream);
 
+/* Bilinear resize of the channel concatenation of three NHWC tensors that keep their own channel pitch p_k
+ * (only the first c_k channels of each are used), followed by act; y [B,Ho,Wo,c1+c2+c3] dense.
+ * Covers torch.concat + F.interpolate + activation at the end of DownScaler2D (network/model.py:35-37). */
+int spgt_bilinear_concat3_fwd(const float* x1, const float* x2, const float* x3, int p1, int p2, int p3, int c1, int c2,
+                              int c3, float* y, int B, int Hi, int Wi, int Ho, int Wo, int act, spgt_stream_t stream);
+
 /* First stage of DownScaler2D fused: y = act(bilinear(act(conv3x3(node) + bias))) with a 1-channel input.
  * node [B,Hi,Wi], w [9,Cout] (row = ky*3+kx), bias [Cout], y [B,Ho,Wo,Cout]; the Cout-channel full-resolution
  * tensor is never materialised.  Cout % 4 == 0, Cout <= 512.  (network/model.py:29-31.) */
@@ -155,6 +161,36 @@ int spgt_upsample_grid_fwd(const float* uw, const float* grid, const float* wg, 
 int spgt_decoder_head_fwd(const float* x, const float* w1, const float* b1, const float* w2, float b2,
                           float scale, float shift, const float* scale_map, const float* shift_map, int dirichlet,
                           float* out, int B, int Hh, int Ww, int K, int N1, int act, spgt_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * tcgen05 / TMEM variants of the dense layers (same math, 3xTF32 on the 5th-generation tensor cores).
+ * Weights are prepared once: split into tf32 hi / lo planes, transposed to K-major [Npad][Kpad], zero padded.
+ * No counterpart in the reference, which leaves these layers to cuBLAS / cuDNN.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Bytes of a prepared weight for a [K,N] matrix, and the preparation itself (w_kn row-major, pitch ldw). */
+size_t spgt_tc_weight_bytes(int K, int N);
+int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, void* out, size_t out_bytes, spgt_stream_t stream);
+/* 0 if no tensor-core kernel ever gave up on a bounded wait, else the code of the first one that did
+ * (1 producer, 2 accumulator-free, 3 operands-ready, 4 accumulator-ready).  Synchronises the device. */
+int spgt_tc_status(void);
+
+/* As spgt_linear_fwd with wprep = spgt_tc_weight_prepare(w, ...). */
+int spgt_linear_tc_fwd(const float* x, int lda, const void* wprep, const float* bias, const float* residual, int ldr,
+                       float* y, int ldc, int rows, int K, int N, int act, spgt_stream_t stream);
+/* As spgt_conv3x3_fwd with a prepared [9*Cin, Cout] weight; Cin, cin_off, cin_pitch must be multiples of 4. */
+int spgt_conv3x3_tc_fwd(const float* x, int cin_pitch, int cin_off, int Cin, const void* wprep, const float* bias,
+                        float* y, int cout_pitch, int cout_off, int Cout, int B, int Hh, int Ww, int act,
+                        spgt_stream_t stream);
+/* As spgt_projpos_qkv_fwd for D == 128, H == 4; wprep_qkv is prepared from the [128, 384] matrix Wq | Wk | Wv. */
+int spgt_projpos_qkv_tc_fwd(const float* x, const void* wprep_qkv, const float* bq, const float* bk, const float* bv,
+                            const float* lnwk, const float* lnbk, const float* lnwv, const float* lnbv, float eps,
+                            const float* pos, float* q, float* k, float* v, int B, int S, int D, int H, int d_head,
+                            int d_pos, spgt_stream_t stream);
+/* As spgt_decoder_head_fwd with a prepared w1. */
+int spgt_decoder_head_tc_fwd(const float* x, const void* w1prep, const float* b1, const float* w2, float b2,
+                             float scale, float shift, const float* scale_map, const float* shift_map, int dirichlet,
+                             float* out, int B, int Hh, int Ww, int K, int N1, int act, spgt_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * FNO2d spectral layer (reference: Sp_SpectralConv2D.forward, network/sp_layer.py:125-156)

@@ -40,9 +40,17 @@ SIGNATURES = {
     'spgt_linear_fwd': (_i, [_f, _i, _f, _i, _f, _f, _i, _f, _i, _i, _i, _i, _i, _st]),
     'spgt_conv3x3_fwd': (_i, [_f, _i, _i, _i, _f, _i, _f, _f, _i, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_bilinear_fwd': (_i, [_f, _f, _i, _i, _i, _i, _i, _i, _i, _st]),
+    'spgt_bilinear_concat3_fwd': (_i, [_f, _f, _f] + [_i] * 6 + [_f] + [_i] * 6 + [_st]),
     'spgt_conv0_down_fwd': (_i, [_f, _f, _f, _f, _i, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_upsample_grid_fwd': (_i, [_f, _f, _f, _f, _f, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_decoder_head_fwd': (_i, [_f, _f, _f, _f, _fl, _fl, _fl, _f, _f, _i, _f, _i, _i, _i, _i, _i, _i, _st]),
+    'spgt_tc_weight_bytes': (_sz, [_i, _i]),
+    'spgt_tc_weight_prepare': (_i, [_f, _i, _i, _i, _f, _sz, _st]),
+    'spgt_tc_status': (_i, []),
+    'spgt_linear_tc_fwd': (_i, [_f, _i, _f, _f, _f, _i, _f, _i, _i, _i, _i, _i, _st]),
+    'spgt_conv3x3_tc_fwd': (_i, [_f, _i, _i, _i, _f, _f, _f, _i, _i, _i, _i, _i, _i, _i, _st]),
+    'spgt_projpos_qkv_tc_fwd': (_i, [_f] * 9 + [_fl] + [_f] * 4 + [_i] * 6 + [_st]),
+    'spgt_decoder_head_tc_fwd': (_i, [_f, _f, _f, _f, _fl, _fl, _fl, _f, _f, _i, _f, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_spectral_tables_bytes': (_sz, [_i, _i]),
     'spgt_spectral_tables_init': (_i, [_f, _sz, _i, _i, _st]),
     'spgt_spectral_workspace_bytes': (_sz, [_i, _i, _i, _i]),

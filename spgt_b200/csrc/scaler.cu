@@ -119,6 +119,39 @@ upsample_grid_kernel(const float4* __restrict__ uw, const float2* __restrict__ g
     }
 }
 
+// y[b,yo,xo,:] = act(bilinear(concat(x1[..., :c1], x2[..., :c2], x3[..., :c3])))  -- the three sources keep their own
+// (padded) channel pitch, the output is dense.  One thread per (pixel, 4 output channels), scalar gathers.
+__global__ void __launch_bounds__(256)
+bilinear_concat3_kernel(const float* __restrict__ x1, const float* __restrict__ x2, const float* __restrict__ x3, int p1,
+                        int p2, int p3, int c1, int c2, int c3, float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo,
+                        int act, int64_t total) {
+    const int C4 = (c1 + c2 + c3) / 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int cg = (int)(i % C4);
+        int64_t p = i / C4;
+        const int xo = (int)(p % Wo); p /= Wo;
+        const int yo = (int)(p % Ho);
+        const int64_t b = p / Ho;
+        const Tap ty = make_tap(yo, Hi, Ho), tx = make_tap(xo, Wi, Wo);
+        const float w00 = ty.w0 * tx.w0, w01 = ty.w0 * tx.w1, w10 = ty.w1 * tx.w0, w11 = ty.w1 * tx.w1;
+        const int64_t o00 = (b * Hi + ty.i0) * Wi + tx.i0, o01 = (b * Hi + ty.i0) * Wi + tx.i1;
+        const int64_t o10 = (b * Hi + ty.i1) * Wi + tx.i0, o11 = (b * Hi + ty.i1) * Wi + tx.i1;
+        float o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int c = cg * 4 + k;
+            const float* src; int pitch;
+            if (c < c1) { src = x1; pitch = p1; }
+            else if (c < c1 + c2) { src = x2; pitch = p2; c -= c1; }
+            else { src = x3; pitch = p3; c -= c1 + c2; }
+            const float v = __ldg(src + o00 * pitch + c) * w00 + __ldg(src + o01 * pitch + c) * w01 +
+                            __ldg(src + o10 * pitch + c) * w10 + __ldg(src + o11 * pitch + c) * w11;
+            o[k] = apply_act(v, act);
+        }
+        y[i] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 static unsigned grid_for(int64_t items, int threads, int per_sm) {
     const int64_t want = ceil_div(items, (int64_t)threads);
     const int64_t cap = (int64_t)num_sms() * per_sm;
@@ -137,6 +170,19 @@ extern "C" int spgt_bilinear_fwd(const float* x, float* y, int B, int Hi, int Wi
     const int64_t total = (int64_t)B * Ho * Wo * (C / 4);
     bilinear_kernel<<<grid_for(total, 256, 16), 256, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), Hi, Wi, Ho, Wo, C / 4, act, total);
+    return launch_status();
+}
+
+extern "C" int spgt_bilinear_concat3_fwd(const float* x1, const float* x2, const float* x3, int p1, int p2, int p3, int c1,
+                                         int c2, int c3, float* y, int B, int Hi, int Wi, int Ho, int Wo, int act,
+                                         spgt_stream_t stream) {
+    if (!x1 || !x2 || !x3 || !y) return SPGT_ERR_NULL;
+    if (B <= 0 || Hi <= 0 || Wi <= 0 || Ho <= 0 || Wo <= 0 || c1 <= 0 || c2 <= 0 || c3 <= 0 || act < 0 || act > 3) return SPGT_ERR_SHAPE;
+    if (p1 < c1 || p2 < c2 || p3 < c3 || ((c1 + c2 + c3) & 3)) return SPGT_ERR_SHAPE;
+    if (!aligned16(y)) return SPGT_ERR_ALIGN;
+    const int64_t total = (int64_t)B * Ho * Wo * ((c1 + c2 + c3) / 4);
+    bilinear_concat3_kernel<<<grid_for(total, 256, 16), 256, 0, (cudaStream_t)stream>>>(
+        x1, x2, x3, p1, p2, p3, c1, c2, c3, reinterpret_cast<float4*>(y), Hi, Wi, Ho, Wo, act, total);
     return launch_status();
 }
 

@@ -39,6 +39,22 @@ def _conv_kn(weight: Tensor) -> Tensor:
     return ops.pad_cols(weight.detach().permute(2, 3, 1, 0).reshape(9 * cin, cout).contiguous())
 
 
+def _linear_tc(weight: Tensor) -> 'ops.TcWeight':
+    """torch Linear weight [out, in] prepared for the tcgen05 GEMM."""
+    return ops.TcWeight(weight.detach().t().contiguous())
+
+
+def _conv_tc(weight: Tensor, bias: Tensor, cin_pad: int, cout_pad: int):
+    """Conv2d weight [Cout, Cin, 3, 3] (+ bias) prepared for the tcgen05 implicit GEMM, with input / output channels
+    zero-padded to cin_pad / cout_pad (padded outputs come out as act(0))."""
+    cout, cin = weight.shape[:2]
+    w = torch.zeros(cout_pad, cin_pad, 3, 3, device=weight.device, dtype=weight.dtype)
+    w[:cout, :cin] = weight.detach()
+    b = torch.zeros(cout_pad, device=weight.device, dtype=weight.dtype)
+    b[:cout] = bias.detach()
+    return ops.TcWeight(w.permute(2, 3, 1, 0).reshape(9 * cin_pad, cout_pad).contiguous()), b
+
+
 class ConvResBlock2D(_KernelWeights):
     """conv3x3(pad 1) -> [dropout, rate treated as 0] -> activation; NHWC in and out.
     Reference: network/layer.py:7-24 (NCHW there; the kernels keep channels last throughout)."""
@@ -54,9 +70,18 @@ class ConvResBlock2D(_KernelWeights):
         return self._cached('w', lambda: _conv_kn(self.conv_layer.weight))
 
     def forward_nhwc(self, X: Tensor, cin_off: int, out: Tensor, cout_off: int, act=None) -> Tensor:
+        """Generic path (any even channel counts / offsets): warp-MMA implicit GEMM."""
         w = self.conv_layer.weight
         return ops.conv3x3(X, cin_off, w.shape[1], self.kernel_weight(), self.conv_layer.bias.detach(), out, cout_off,
                            w.shape[0], self.activation if act is None else act)
+
+    def forward_tc(self, X: Tensor, cin_pad: int, cout_pad: int, act=None) -> Tensor:
+        """tcgen05 path: X [N,H,W,cin_pad] (channels beyond in_dim must be finite; their weights are zero) ->
+        new tensor [N,H,W,cout_pad] whose channels beyond out_dim hold act(0)."""
+        wt, b = self._cached(('tc', cin_pad, cout_pad),
+                             lambda: _conv_tc(self.conv_layer.weight, self.conv_layer.bias, cin_pad, cout_pad))
+        out = torch.empty(*X.shape[:3], cout_pad, device=X.device, dtype=X.dtype)
+        return ops.conv3x3_tc(X, 0, cin_pad, wt, b, out, 0, cout_pad, self.activation if act is None else act)
 
 
 class FeedForward(_KernelWeights):
@@ -71,7 +96,7 @@ class FeedForward(_KernelWeights):
 
     def forward(self, X: Tensor, residual: Tensor = None) -> Tensor:
         """X [..., in_dim] -> [..., out_dim] (+ residual when given, fused into the second GEMM)."""
-        w1 = self._cached('w1', lambda: _linear_kn(self.layer1.weight))
-        w2 = self._cached('w2', lambda: _linear_kn(self.layer2.weight))
-        h = ops.linear(X, w1, self.layer1.bias.detach(), self.layer1.out_features, self.activation)
-        return ops.linear(h, w2, self.layer2.bias.detach(), self.layer2.out_features, None, residual)
+        w1 = self._cached('w1', lambda: _linear_tc(self.layer1.weight))
+        w2 = self._cached('w2', lambda: _linear_tc(self.layer2.weight))
+        h = ops.linear_tc(X, w1, self.layer1.bias.detach(), self.activation)
+        return ops.linear_tc(h, w2, self.layer2.bias.detach(), None, residual)

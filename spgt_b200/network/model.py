@@ -33,11 +33,11 @@ class DownScaler2D(_KernelWeights):
         w0 = self._cached('w0', lambda: self.conv0.conv_layer.weight.detach().reshape(-1, 9).t().contiguous())
         X = ops.conv0_down(X.reshape(N, r, r), w0, self.conv0.conv_layer.bias.detach(), mid[0], mid[1], self.activation)
         d1, d2, d3 = self.dims
-        cat = torch.empty(N, mid[0], mid[1], d1 + d2 + d3, device=X.device, dtype=X.dtype)
-        self.conv1.forward_nhwc(X, 0, cat, 0)
-        self.conv2.forward_nhwc(cat, 0, cat, d1)
-        self.conv3.forward_nhwc(cat, d1, cat, d1 + d2)
-        return ops.bilinear(cat, ra[0], ra[1], self.activation)
+        pad4 = lambda c: (c + 3) // 4 * 4          # the tcgen05 implicit GEMM wants channel counts that are multiples of 4
+        X1 = self.conv1.forward_tc(X, X.shape[3], pad4(d1))
+        X2 = self.conv2.forward_tc(X1, pad4(d1), pad4(d2))
+        X3 = self.conv3.forward_tc(X2, pad4(d2), pad4(d3))
+        return ops.bilinear_concat3(X1, X2, X3, d1, d2, d3, ra[0], ra[1], self.activation)
 
 
 class UpScaler2D(_KernelWeights):
@@ -56,8 +56,11 @@ class UpScaler2D(_KernelWeights):
         """Everything up to (not including) the last interpolation: [N, r_mid, r_mid, out_dim]."""
         mid = self.resolution_size[3]
         X = ops.bilinear(X, mid[0], mid[1], None)
-        out = torch.empty(X.shape[0], mid[0], mid[1], self.conv.conv_layer.out_channels, device=X.device, dtype=X.dtype)
         twice = 'silu2' if self.activation == 'silu' else 'relu'
+        cin, cout = self.conv.conv_layer.in_channels, self.conv.conv_layer.out_channels
+        if cin % 4 == 0 and cout % 4 == 0:
+            return self.conv.forward_tc(X, cin, cout, act=twice)
+        out = torch.empty(X.shape[0], mid[0], mid[1], cout, device=X.device, dtype=X.dtype)
         return self.conv.forward_nhwc(X, 0, out, 0, act=twice)
 
     def forward(self, X: Tensor) -> Tensor:

@@ -11,7 +11,7 @@ import torch
 from torch import Tensor
 
 from .. import ops
-from .layer import FeedForward, _KernelWeights, _linear_kn
+from .layer import FeedForward, _KernelWeights, _linear_kn, _linear_tc
 
 
 class Sp_GalerkinAttention(_KernelWeights):
@@ -49,7 +49,13 @@ class Sp_GalerkinAttention(_KernelWeights):
         When Q, K and V are the same tensor (self-attention) all three projections run in one launch."""
         d = lambda t: t.detach()
         H, dh, dp = self.num_head, self.dim_head, self.dim_position
-        if Q is K and K is V:
+        if Q is K and K is V and self.dim_hidden == 128:
+            wqkv = self._cached('wqkv', lambda: ops.TcWeight(
+                torch.cat([d(self.weight_Q), d(self.weight_K), d(self.weight_V)], dim=1).contiguous()))
+            q, k, v = ops.projpos_qkv_tc(
+                Q, wqkv, d(self.bias_Q), d(self.bias_K), d(self.bias_V), d(self.ln_weight_K), d(self.ln_bias_K),
+                d(self.ln_weight_V), d(self.ln_bias_V), self.norm_eps, position, H, dh, dp)
+        elif Q is K and K is V:
             q, k, v = ops.projpos_qkv(
                 Q, d(self.weight_Q), d(self.bias_Q), d(self.weight_K), d(self.bias_K), d(self.weight_V), d(self.bias_V),
                 d(self.ln_weight_K), d(self.ln_bias_K), d(self.ln_weight_V), d(self.ln_bias_V), self.norm_eps, position,
@@ -61,8 +67,8 @@ class Sp_GalerkinAttention(_KernelWeights):
             v = ops.projpos_lnorm(V, d(self.weight_V), d(self.bias_V), d(self.ln_weight_V), d(self.ln_bias_V), position,
                                   self.norm_eps, H, dh, dp)
         X = ops.galerkin_attention(q, k, v, merged_heads=True)          # [N, S, H*(d_pos+d_head)]
-        wfc = self._cached('fc', lambda: _linear_kn(self.fc_layer.weight))
-        return ops.linear(X, wfc, d(self.fc_layer.bias), self.dim_hidden, None, residual)
+        wfc = self._cached('fc', lambda: _linear_tc(self.fc_layer.weight))
+        return ops.linear_tc(X, wfc, d(self.fc_layer.bias), None, residual)
 
 
 class Sp_EncoderLayer(torch.nn.Module):

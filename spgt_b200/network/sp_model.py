@@ -5,7 +5,7 @@ import torch
 from torch import Tensor
 
 from .. import ops
-from .layer import FeedForward, _KernelWeights, _linear_kn
+from .layer import FeedForward, _KernelWeights, _linear_kn, _linear_tc
 from .model import DownScaler2D, UpScaler2D
 from .sp_layer import Sp_EncoderLayer, Sp_SpectralConv2D
 
@@ -42,9 +42,13 @@ class Sp_DecoderRegressor(_KernelWeights):
         for layer in self.layers:
             X = layer(X)
         f = self.ffn_layer
-        w1 = self._cached('w1', lambda: _linear_kn(f.layer1.weight))
         w2 = self._cached('w2', lambda: f.layer2.weight.detach().reshape(-1).contiguous())
         b2 = self._cached('b2', lambda: float(f.layer2.bias.detach().reshape(-1)[0]))
+        if f.layer1.out_features == 128:
+            w1 = self._cached('w1tc', lambda: _linear_tc(f.layer1.weight))
+            return ops.decoder_head_tc(X, w1, f.layer1.bias.detach(), w2, b2, scale, shift, dirichlet, self.activation,
+                                       scale_map, shift_map)
+        w1 = self._cached('w1', lambda: _linear_kn(f.layer1.weight))
         return ops.decoder_head(X, w1, f.layer1.bias.detach(), w2, b2, scale, shift, dirichlet, self.activation,
                                 scale_map, shift_map)
 
@@ -55,12 +59,12 @@ class Sp_DecoderRegressor(_KernelWeights):
     def _fc_split(self, X, grid):
         """spatial_fc_layer(concat(X, grid)) = X @ Wx + grid @ Wg + b without materialising the concatenation."""
         wx, wg = self._split_fc()
-        uw = ops.linear(X, wx, None, self.spatial_fc_layer.out_features, None)
+        uw = ops.linear_tc(X, wx, None, None)
         return ops.upsample_grid(uw, grid, wg, self.spatial_fc_layer.bias.detach(), X.shape[1], X.shape[2])
 
     def _split_fc(self):
         w = self.spatial_fc_layer.weight
-        wx = self._cached('wx', lambda: _linear_kn(w[:, :self.in_dim]))
+        wx = self._cached('wx', lambda: _linear_tc(w[:, :self.in_dim]))
         wg = self._cached('wg', lambda: w.detach()[:, self.in_dim:].t().contiguous())
         return wx, wg
 
@@ -69,7 +73,7 @@ class Sp_DecoderRegressor(_KernelWeights):
         Linear are both linear maps, so Linear(concat(resize(U), grid)) = resize(U @ Wx) + grid @ Wg + b: the
         in_dim-channel full-resolution tensor is never formed."""
         wx, wg = self._split_fc()
-        uw = ops.linear(U, wx, None, self.spatial_fc_layer.out_features, None)
+        uw = ops.linear_tc(U, wx, None, None)
         X = ops.upsample_grid(uw, grid, wg, self.spatial_fc_layer.bias.detach(), grid.shape[1], grid.shape[2])
         return self._spectral_and_head(X, scale, shift, dirichlet, scale_map, shift_map)
 

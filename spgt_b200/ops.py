@@ -258,6 +258,17 @@ def bilinear(x: Tensor, Ho: int, Wo: int, act=None) -> Tensor:
     return y
 
 
+def bilinear_concat3(x1: Tensor, x2: Tensor, x3: Tensor, c1: int, c2: int, c3: int, Ho: int, Wo: int, act=None) -> Tensor:
+    """act(bilinear(concat(x1[..., :c1], x2[..., :c2], x3[..., :c3]))) -> [B, Ho, Wo, c1+c2+c3]."""
+    _chk(x1, 'x1'); _chk(x2, 'x2'); _chk(x3, 'x3')
+    B, Hi, Wi, _ = x1.shape
+    y = torch.empty(B, Ho, Wo, c1 + c2 + c3, device=x1.device, dtype=x1.dtype)
+    with torch.cuda.device(x1.device):
+        _call('spgt_bilinear_concat3_fwd', x1.data_ptr(), x2.data_ptr(), x3.data_ptr(), x1.shape[3], x2.shape[3], x3.shape[3],
+              c1, c2, c3, y.data_ptr(), B, Hi, Wi, Ho, Wo, act_code(act), _stream())
+    return y
+
+
 def conv0_down(node: Tensor, w9: Tensor, bias: Tensor, Ho: int, Wo: int, act) -> Tensor:
     """node [B,Hi,Wi] (one channel), w9 [9, Cout] -> act(bilinear(act(conv3x3)))  [B,Ho,Wo,Cout]."""
     _chk(node, 'node'); _chk(w9, 'weight'); _chk(bias, 'bias')
@@ -291,6 +302,77 @@ def decoder_head(x: Tensor, w1_kn: Tensor, b1: Tensor, w2: Tensor, b2: float, sc
         _call('spgt_decoder_head_fwd', x.data_ptr(), w1_kn.data_ptr(), b1.data_ptr(), w2.data_ptr(), float(b2), float(scale),
                                         float(shift), _p(scale_map), _p(shift_map), int(dirichlet), out.data_ptr(), B, Hh, Ww, K, w1_kn.shape[1],
                                         act_code(act), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# tcgen05 / TMEM variants of the dense layers
+# ---------------------------------------------------------------------------------------------------------
+class TcWeight:
+    """A [K, N] weight prepared for the tcgen05 kernels (tf32 hi/lo planes, K-major, padded)."""
+
+    def __init__(self, w_kn: Tensor):
+        _chk(w_kn, 'weight')
+        self.K, self.N = w_kn.shape
+        n = int(lib.spgt_tc_weight_bytes(self.K, self.N))
+        self.buf = torch.empty(n, dtype=torch.uint8, device=w_kn.device)
+        with torch.cuda.device(w_kn.device):
+            _call('spgt_tc_weight_prepare', w_kn.data_ptr(), w_kn.shape[1], self.K, self.N, self.buf.data_ptr(), n, _stream())
+
+    def data_ptr(self) -> int:
+        return self.buf.data_ptr()
+
+
+def tc_status() -> int:
+    return int(lib.spgt_tc_status())
+
+
+def linear_tc(x: Tensor, w: TcWeight, bias: Optional[Tensor], act=None, residual: Optional[Tensor] = None) -> Tensor:
+    _chk(x, 'x')
+    K = x.shape[-1]
+    if K != w.K:
+        raise ValueError('x last dim must equal the prepared weight K')
+    rows = x.numel() // K
+    out = torch.empty(*x.shape[:-1], w.N, device=x.device, dtype=x.dtype)
+    if residual is not None:
+        _chk(residual, 'residual')
+    with torch.cuda.device(x.device):
+        _call('spgt_linear_tc_fwd', x.data_ptr(), K, w.data_ptr(), _p(bias), _p(residual), w.N, out.data_ptr(), w.N,
+              rows, K, w.N, act_code(act), _stream())
+    return out
+
+
+def conv3x3_tc(x: Tensor, cin_off: int, Cin: int, w: TcWeight, bias: Tensor, y: Tensor, cout_off: int, Cout: int, act) -> Tensor:
+    _chk(x, 'x'); _chk(y, 'y'); _chk(bias, 'bias')
+    B, Hh, Ww, cp = x.shape
+    if w.K != 9 * Cin or w.N != Cout:
+        raise ValueError('prepared weight does not match [9*Cin, Cout]')
+    with torch.cuda.device(x.device):
+        _call('spgt_conv3x3_tc_fwd', x.data_ptr(), cp, cin_off, Cin, w.data_ptr(), bias.data_ptr(), y.data_ptr(), y.shape[3],
+              cout_off, Cout, B, Hh, Ww, act_code(act), _stream())
+    return y
+
+
+def projpos_qkv_tc(x, wqkv: TcWeight, bq, bk, bv, lnwk, lnbk, lnwv, lnbv, eps, position, num_head, dim_head, dim_position):
+    _chk(x, 'x'); _chk(position, 'position')
+    B, S, D = x.shape
+    q, k, v = (torch.empty(B, num_head, dim_position + dim_head, S, device=x.device, dtype=x.dtype) for _ in range(3))
+    with torch.cuda.device(x.device):
+        _call('spgt_projpos_qkv_tc_fwd', x.data_ptr(), wqkv.data_ptr(), _p(bq), _p(bk), _p(bv), lnwk.data_ptr(), lnbk.data_ptr(),
+              lnwv.data_ptr(), lnbv.data_ptr(), float(eps), position.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+              B, S, D, num_head, dim_head, dim_position, _stream())
+    return q, k, v
+
+
+def decoder_head_tc(x: Tensor, w1: TcWeight, b1: Tensor, w2: Tensor, b2: float, scale: float, shift: float, dirichlet: bool,
+                    act, scale_map: Optional[Tensor] = None, shift_map: Optional[Tensor] = None) -> Tensor:
+    _chk(x, 'x'); _chk(b1, 'b1'); _chk(w2, 'w2')
+    B, Hh, Ww, K = x.shape
+    out = torch.empty(B, Hh, Ww, 1, device=x.device, dtype=x.dtype)
+    with torch.cuda.device(x.device):
+        _call('spgt_decoder_head_tc_fwd', x.data_ptr(), w1.data_ptr(), b1.data_ptr(), w2.data_ptr(), float(b2), float(scale),
+              float(shift), _p(scale_map), _p(shift_map), int(dirichlet), out.data_ptr(), B, Hh, Ww, K, w1.N,
+              act_code(act), _stream())
     return out
 
 
