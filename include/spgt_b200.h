@@ -172,7 +172,7 @@ int spgt_decoder_head_fwd(const float* x, const float* w1, const float* b1, cons
 size_t spgt_tc_weight_bytes(int K, int N);
 int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, void* out, size_t out_bytes, spgt_stream_t stream);
 /* 0 if no tensor-core kernel ever gave up on a bounded wait, else the code of the first one that did
- * (1 producer, 2 accumulator-free, 3 operands-ready, 4 accumulator-ready).  Synchronises the device. */
+ * (1 stage-free, 2 accumulator-free, 3 operands-ready, 4 accumulator-ready, 5 tile-landed).  Synchronises the device. */
 int spgt_tc_status(void);
 
 /* As spgt_linear_fwd with wprep = spgt_tc_weight_prepare(w, ...). */

@@ -45,45 +45,68 @@ bilinear_kernel(const float4* __restrict__ x, float4* __restrict__ y, int Hi, in
     }
 }
 
-// y[b,yo,xo,c] = act( lerp over the 4 taps of act(conv3x3(node)[tap] + bias[c]) ).  One thread per (pixel, channel):
-// the 4x4 input patch of a pixel is shared by all channel-threads of the warp (broadcast loads), each thread keeps
-// its 9 weights in registers.  A block walks PIX consecutive output pixels.
-constexpr int C0_PIX = 8;
+// y[b,yo,xo,c] = act( lerp over the 4 taps of act(conv3x3(node)[tap] + bias[c]) ).
+// A block handles C0_PIX consecutive output pixels: the 4x4 input patch around each pixel's taps (zero padded
+// outside the image) and the four lerp weights are staged once in shared memory, then thread c evaluates the
+// convolution of channel c at the taps whose weight is non-zero (for exact 2:1 down-scaling that is one tap).
+constexpr int C0_PIX = 16;
 __global__ void __launch_bounds__(128)
 conv0_down_kernel(const float* __restrict__ node, const float* __restrict__ w, const float* __restrict__ bias,
                   float* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int Cout, int act, int64_t npix) {
+    __shared__ float patch[C0_PIX][16];
+    __shared__ float wt[C0_PIX][4];
+    const int64_t p0 = (int64_t)blockIdx.x * C0_PIX;
+    for (int i = threadIdx.x; i < C0_PIX * 16; i += blockDim.x) {
+        const int pi = i >> 4, e = i & 15;
+        const int64_t p = p0 + pi;
+        float v = 0.0f;
+        if (p < npix) {
+            const int xo = (int)(p % Wo);
+            const int yo = (int)((p / Wo) % Ho);
+            const int64_t b = p / ((int64_t)Wo * Ho);
+            const Tap ty = make_tap(yo, Hi, Ho), tx = make_tap(xo, Wi, Wo);
+            const int yy = ty.i0 - 1 + (e >> 2), xx = tx.i0 - 1 + (e & 3);
+            if (yy >= 0 && yy < Hi && xx >= 0 && xx < Wi) v = __ldg(node + (b * Hi + yy) * (int64_t)Wi + xx);
+            if (e < 4) {
+                // a clamped second tap (i1 == i0) reads the same pixel: fold its weight into the first tap
+                const float wy0 = ty.i1 == ty.i0 ? ty.w0 + ty.w1 : ty.w0, wy1 = ty.i1 == ty.i0 ? 0.0f : ty.w1;
+                const float wx0 = tx.i1 == tx.i0 ? tx.w0 + tx.w1 : tx.w0, wx1 = tx.i1 == tx.i0 ? 0.0f : tx.w1;
+                wt[pi][e] = ((e >> 1) ? wy1 : wy0) * ((e & 1) ? wx1 : wx0);
+            }
+        }
+        patch[pi][e] = v;
+    }
+    __syncthreads();
     for (int c = threadIdx.x; c < Cout; c += blockDim.x) {
         float wk[9];
 #pragma unroll
         for (int k = 0; k < 9; ++k) wk[k] = __ldg(w + k * Cout + c);
         const float bc = __ldg(bias + c);
+#pragma unroll 2
         for (int pi = 0; pi < C0_PIX; ++pi) {
-            const int64_t p = (int64_t)blockIdx.x * C0_PIX + pi;
+            const int64_t p = p0 + pi;
             if (p >= npix) break;
-            const int xo = (int)(p % Wo);
-            const int yo = (int)((p / Wo) % Ho);
-            const int64_t b = p / ((int64_t)Wo * Ho);
-            const Tap ty = make_tap(yo, Hi, Ho), tx = make_tap(xo, Wi, Wo);
-            const float* img = node + b * (int64_t)Hi * Wi;
-            float conv[2][2];
+            float pv[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 r = *reinterpret_cast<const float4*>(&patch[pi][4 * q]);
+                pv[4 * q] = r.x; pv[4 * q + 1] = r.y; pv[4 * q + 2] = r.z; pv[4 * q + 3] = r.w;
+            }
+            float o = 0.0f;
 #pragma unroll
             for (int a = 0; a < 2; ++a)
 #pragma unroll
                 for (int d = 0; d < 2; ++d) {
-                    const int cy = a ? ty.i1 : ty.i0, cx = d ? tx.i1 : tx.i0;
-                    float s = bc;
+                    const float wgt = wt[pi][a * 2 + d];
+                    if (wgt != 0.0f) {
+                        float s = bc;
 #pragma unroll
-                    for (int ky = 0; ky < 3; ++ky)
+                        for (int ky = 0; ky < 3; ++ky)
 #pragma unroll
-                        for (int kx = 0; kx < 3; ++kx) {
-                            const int yy = cy + ky - 1, xx = cx + kx - 1;
-                            const float v = (yy >= 0 && yy < Hi && xx >= 0 && xx < Wi) ? __ldg(img + (int64_t)yy * Wi + xx) : 0.0f;
-                            s = fmaf(v, wk[ky * 3 + kx], s);
-                        }
-                    conv[a][d] = apply_act(s, act);
+                            for (int kx = 0; kx < 3; ++kx) s = fmaf(pv[(a + ky) * 4 + d + kx], wk[ky * 3 + kx], s);
+                        o = fmaf(apply_act(s, act), wgt, o);
+                    }
                 }
-            const float o = conv[0][0] * (ty.w0 * tx.w0) + conv[0][1] * (ty.w0 * tx.w1) + conv[1][0] * (ty.w1 * tx.w0) +
-                            conv[1][1] * (ty.w1 * tx.w1);
             y[p * Cout + c] = apply_act(o, act);
         }
     }

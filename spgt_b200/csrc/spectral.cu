@@ -190,6 +190,7 @@ spectral_fwd_x_kernel(const float* __restrict__ Y1, const float* __restrict__ ta
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float zr[4] = {0, 0, 0, 0}, zi[4] = {0, 0, 0, 0};
     const float* yb = Y1 + b * (int64_t)r * T.J * SP_C + lane;
+#pragma unroll 8
     for (int x = 0; x < r; ++x) {
         const float yr = __ldg(yb + ((int64_t)x * T.J + ky) * SP_C);
         const float yi = __ldg(yb + ((int64_t)x * T.J + m + ky) * SP_C);

@@ -2,12 +2,13 @@
 //   C[rows, N] = A[rows, K] * W[K, N],   A*W ~= A_lo*W_hi + A_hi*W_lo + A_hi*W_hi   (fp32-level accuracy).
 //
 // Persistent, warp-specialised kernel, one CTA per SM:
-//   warps 0-3  producers : cp.async the raw fp32 A tile (dense rows or implicit-GEMM 3x3 gather) and the
-//                          pre-split W_hi / W_lo tiles into 128B-swizzled K-major shared memory, then split
-//                          their own A chunks in place into hi (tf32, round-to-nearest) and lo (x - hi);
-//   warp  4    MMA       : one elected lane issues tcgen05.mma.kind::tf32 (128 x BN x 8) three times per k-step,
+//   warps 0-3  loaders   : cp.async the raw fp32 A tile (dense rows or implicit-GEMM 3x3 gather) into 128B-swizzled
+//                          K-major shared memory (completion tracked by an mbarrier); one thread bulk-copies the
+//                          pre-split, pre-swizzled W_hi | W_lo image of the k-block;
+//   warps 4-7  splitters : split the landed A tile in place into hi (tf32, round-to-nearest) and lo (x - hi);
+//   warp  8    MMA       : one elected lane issues tcgen05.mma.kind::tf32 (128 x BN x 8) three times per k-step,
 //                          tcgen05.commit releases the smem stage / publishes the accumulator;
-//   warps 5-12 epilogue  : tcgen05.ld the 128 x BN fp32 accumulator (one row per thread, two warps per TMEM lane
+//   warps 9-16 epilogue  : tcgen05.ld the 128 x BN fp32 accumulator (one row per thread, two warps per TMEM lane
 //                          quarter splitting the columns) and run the fused epilogue while the MMA warp already
 //                          works on the next tile (TMEM double buffer).
 // All waits are bounded mbarrier polls: on expiry the kernel records an error code, stops waiting and returns.
@@ -15,11 +16,18 @@
 
 namespace spgt {
 
-constexpr int TC_BM = 128, TC_BK = 32, TC_STAGES = 3;
-constexpr int TC_PROD_THREADS = 128, TC_MMA_WARP = 4, TC_EPI_WARP0 = 5, TC_EPI_WARPS = 8, TC_THREADS = 32 * (5 + TC_EPI_WARPS);
+constexpr int TC_BM = 128, TC_BK = 32;
+constexpr int TC_PROD_THREADS = 128, TC_MMA_WARP = 8, TC_EPI_WARP0 = 9, TC_EPI_WARPS = 8, TC_THREADS = 32 * (9 + TC_EPI_WARPS);
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
 
 __device__ int g_tc_status = 0;          // 0 = ok; otherwise the code of the first wait that gave up
+
+#ifdef SPGT_TC_TRACE                      // developer build only: per-tile timestamps of CTA 0 (see spgt_tc_trace_read)
+__device__ long long g_tc_trace[64 * 16];
+#define TC_TRACE(tile_i, slot) do { if (blockIdx.x == 0 && (tile_i) < 64) g_tc_trace[(tile_i) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TC_TRACE(tile_i, slot) do { } while (0)
+#endif
 
 // ---- mbarrier / tcgen05 primitives -------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -93,7 +101,7 @@ __host__ __device__ constexpr uint32_t tc_idesc(int bn) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
 }
 // byte offset of 16-byte chunk `c` (0..7) of row `r` inside a swizzled tile
-__device__ __forceinline__ uint32_t tc_swz(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
+__host__ __device__ __forceinline__ uint32_t tc_swz(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
 
 // ---- A-operand loaders (producer side; 128 threads, thread -> chunk (t & 7) of rows (t >> 3) + 16 i) ---------
 struct TcDense {
@@ -157,36 +165,38 @@ template <int BN> struct TcSmem {
     static constexpr int A_BYTES = TC_BM * TC_BK * 4;           // 16 KB
     static constexpr int B_BYTES = BN * TC_BK * 4;
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;     // A_hi(raw), A_lo, B_hi, B_lo
-    static constexpr int STAGING_BYTES = 2 * 128 * 4;                 // partial row sums exchanged between epilogue warp pairs
-    static constexpr int BAR_BYTES = 128;
-    static constexpr size_t BYTES = 1024 /*alignment slack*/ + (size_t)TC_STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
+    static constexpr int STAGES = (BN > 64) ? 3 : 4;
+    static constexpr int STAGING_BYTES = (2 * 128 + 256) * 4;         // partial row sums of epilogue warp pairs + b1 | w2 of the head
+    static constexpr int BAR_BYTES = 192;
+    static constexpr size_t BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
 };
 
 enum { EPI_LINEAR = 0, EPI_PROJ = 1, EPI_HEAD = 2 };
 
 template <int BN, class Loader, int EPI, class EpiParams>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restrict__ w_lo, int kpad, int rows, int n_tiles,
-               int m_tiles, EpiParams ep) {
+tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_tiles, EpiParams ep) {
     using L = TcSmem<BN>;
+    constexpr int ST = L::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // 1024-aligned for the 128B swizzle
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t stage0 = smem_base;
-    const uint32_t bars = smem_base + TC_STAGES * L::STAGE_BYTES + L::STAGING_BYTES;
-    // barrier slots (8 bytes each): full[3], empty[3], acc_full[2], acc_empty[2]; then tmem ptr, abort flag
+    const uint32_t bars = smem_base + ST * L::STAGE_BYTES + L::STAGING_BYTES;
+    // barrier slots (8 bytes each): full[4], empty[4], raw[4], acc_full[2], acc_empty[2]; then tmem ptr, abort flag
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (3 + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (6 + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (8 + b); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_STAGES * L::STAGE_BYTES + L::STAGING_BYTES + 80);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_STAGES * L::STAGE_BYTES + L::STAGING_BYTES + 96);
+    auto empty_bar = [&](int s) { return bars + 8u * (4 + s); };
+    auto raw_bar = [&](int s) { return bars + 8u * (8 + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (12 + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (14 + b); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + ST * L::STAGE_BYTES + L::STAGING_BYTES + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + ST * L::STAGE_BYTES + L::STAGING_BYTES + 144);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int TMEM_COLS = (2 * BN <= 64) ? 64 : (2 * BN <= 128 ? 128 : 256);
 
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full_bar(s), TC_PROD_THREADS); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(full_bar(s), TC_PROD_THREADS + 1); mbar_init(empty_bar(s), 1); mbar_init(raw_bar(s), TC_PROD_THREADS); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 32 * TC_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -194,6 +204,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
     if (warp == TC_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if constexpr (EPI == EPI_HEAD) {
+        float* cst = reinterpret_cast<float*>(smem + ST * L::STAGE_BYTES) + 256;
+        for (int i = tid; i < 256; i += TC_THREADS) cst[i] = i < 128 ? __ldg(ep.b1 + i) : __ldg(ep.w2 + i - 128);
     }
     tc_fence_before();
     __syncthreads();
@@ -204,44 +218,28 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
     const int total_tiles = m_tiles * n_tiles;
 
     if (warp < 4) {
-        // ------------------------------------------ producers ------------------------------------------
-        // Per pipeline slot `it`: (a) split the A chunks this thread loaded LAG slots ago and publish that stage,
-        // (b) wait until the MMA warp has drained stage it % STAGES, (c) issue this slot's loads.  Doing (a) before
-        // (b) lets the split of slot it-LAG overlap the MMAs of slot it-STAGES.
+        // ------------------------------------------ loaders ------------------------------------------
         const int t = tid;
         uint32_t it = 0;
-        constexpr int LAG = TC_STAGES - 1;
         uint32_t aoff[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) aoff[i] = tc_swz((t >> 3) + 16 * i, t & 7);
-        auto convert = [&](uint32_t j) {            // split this thread's own A chunks of pipeline slot j
-            const uint32_t s = j % TC_STAGES;
-            uint8_t* a_hi = smem + s * L::STAGE_BYTES;
-            uint8_t* a_lo = a_hi + L::A_BYTES;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float4 v = *reinterpret_cast<float4*>(a_hi + aoff[i]);
-                uint32_t h[4], l[4];
-                split_tf32(v.x, h[0], l[0]); split_tf32(v.y, h[1], l[1]); split_tf32(v.z, h[2], l[2]); split_tf32(v.w, h[3], l[3]);
-                *reinterpret_cast<uint4*>(a_hi + aoff[i]) = make_uint4(h[0], h[1], h[2], h[3]);
-                *reinterpret_cast<uint4*>(a_lo + aoff[i]) = make_uint4(l[0], l[1], l[2], l[3]);
-            }
-            fence_proxy_async();                     // generic-proxy writes -> visible to the tensor core
-            mbar_arrive(full_bar(s));
-        };
         bool alive = true;
         for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
             const int row0 = (tile / n_tiles) * TC_BM;
-            const int n0 = (tile % n_tiles) * BN;
             ld.init(row0, t);
-            const float* bh = w_hi + (int64_t)(n0 + (t >> 3)) * kpad + (t & 7) * 4;
-            const float* bl = w_lo + (int64_t)(n0 + (t >> 3)) * kpad + (t & 7) * 4;
+            if (t == 0) TC_TRACE(it / KB, 0);
+            const float* wtile = wimg + (int64_t)(tile % n_tiles) * KB * (2 * L::B_BYTES / 4);
             for (int kb = 0; kb < KB; ++kb, ++it) {
-                if (it >= LAG) { cp_async_wait<LAG - 1>(); convert(it - LAG); }
-                const uint32_t s = it % TC_STAGES, ph = (it / TC_STAGES) & 1;
+                const uint32_t s = it % ST, ph = (it / ST) & 1;
                 if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 1)) { alive = false; break; }
                 const uint32_t a_hi = stage0 + s * L::STAGE_BYTES;
-                const uint32_t b_hi = a_hi + 2 * L::A_BYTES, b_lo = b_hi + L::B_BYTES;
+                if (t == 0) {      // the pre-swizzled W_hi | W_lo image of this (column tile, k-block): one bulk copy
+                    const uint32_t bytes = 2 * L::B_BYTES;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(s)), "r"(bytes) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(a_hi + 2 * L::A_BYTES), "l"(wtile + (int64_t)kb * (2 * L::B_BYTES / 4)), "r"(bytes), "r"(full_bar(s)) : "memory");
+                }
                 ld.set_k(kb * TC_BK, t);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -250,21 +248,42 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
                     const int n = ok ? 16 : 0;
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_hi + aoff[i]), "l"(p), "r"(n) : "memory");
                 }
-#pragma unroll
-                for (int i = 0; i < BN / 16; ++i) {                     // BN rows x 8 chunks, 16 rows per pass
-                    const int64_t g = (int64_t)(16 * i) * kpad + kb * TC_BK;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_hi + aoff[i]), "l"(bh + g) : "memory");
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_lo + aoff[i]), "l"(bl + g) : "memory");
-                }
-                cp_async_commit();
+                // arrive on raw[s] once every cp.async issued so far by this thread has landed
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_bar(s)) : "memory");
             }
+            if (t == 0) TC_TRACE((it - 1) / KB, 1);
         }
-        if (alive) {                                   // drain the last LAG slots
-            if (it >= 2) { cp_async_wait<1>(); convert(it - 2); }
-            cp_async_wait<0>();
-            if (it >= 1) convert(it - 1);
-        } else {
-            cp_async_wait<0>();
+        cp_async_wait_all();
+    } else if (warp < 8) {
+        // ------------------------------------------ splitters ------------------------------------------
+        const int t = tid - 128;
+        uint32_t it = 0;
+        uint32_t aoff[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) aoff[i] = tc_swz((t >> 3) + 16 * i, t & 7);
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+                const uint32_t s = it % ST, ph = (it / ST) & 1;
+                if (!mbar_wait(raw_bar(s), ph, abort_flag, 5)) { alive = false; break; }
+                if (t == 0 && kb == 0) TC_TRACE(it / KB, 2);
+                uint8_t* a_hi = smem + s * L::STAGE_BYTES;
+                uint8_t* a_lo = a_hi + L::A_BYTES;
+                float4 v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = *reinterpret_cast<float4*>(a_hi + aoff[i]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    uint32_t h[4], l[4];
+                    split_tf32(v[i].x, h[0], l[0]); split_tf32(v[i].y, h[1], l[1]);
+                    split_tf32(v[i].z, h[2], l[2]); split_tf32(v[i].w, h[3], l[3]);
+                    *reinterpret_cast<uint4*>(a_hi + aoff[i]) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(a_lo + aoff[i]) = make_uint4(l[0], l[1], l[2], l[3]);
+                }
+                fence_proxy_async();                     // generic-proxy writes -> visible to the tensor core
+                mbar_arrive(full_bar(s));
+                if (t == 0 && kb == KB - 1) TC_TRACE(it / KB, 3);
+            }
         }
     } else if (warp == TC_MMA_WARP) {
         // ------------------------------------------ MMA issuer ------------------------------------------
@@ -273,12 +292,15 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
         bool alive = true;
         for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++ti) {
             const uint32_t buf = ti & 1, aph = (ti >> 1) & 1;
+            if (lane == 0) TC_TRACE(ti, 4);
             if (!mbar_wait(acce_bar(buf), aph ^ 1, abort_flag, 2)) { alive = false; break; }
+            if (lane == 0) TC_TRACE(ti, 5);
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * BN;
             for (int kb = 0; kb < KB; ++kb, ++it) {
-                const uint32_t s = it % TC_STAGES, ph = (it / TC_STAGES) & 1;
+                const uint32_t s = it % ST, ph = (it / ST) & 1;
                 if (!mbar_wait(full_bar(s), ph, abort_flag, 3)) { alive = false; break; }
+                if (lane == 0 && kb == 0) TC_TRACE(ti, 6);
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t a_hi = stage0 + s * L::STAGE_BYTES;
@@ -296,6 +318,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
                 __syncwarp();
             }
             if (alive && lane == 0) tc_commit(accf_bar(buf));
+            if (lane == 0) TC_TRACE(ti, 7);
             __syncwarp();
         }
     } else {
@@ -307,7 +330,9 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
         bool alive = true;
         for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++ti) {
             const uint32_t buf = ti & 1, aph = (ti >> 1) & 1;
+            if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 8);
             if (!mbar_wait(accf_bar(buf), aph, abort_flag, 4)) { alive = false; break; }
+            if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 9);
             tc_fence_after();
             const int mt = tile / n_tiles, nt = tile % n_tiles;
             const int row = mt * TC_BM + r_in_tile;
@@ -326,6 +351,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
                     else { tc_ld16(taddr + c0, v);
 #pragma unroll
                         for (int j = 16; j < 32; ++j) v[j] = 0.0f; }
+                    if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 11 + (ch >> 1) * 2);
                     if (row < rows) {
                         const int colb = nt * BN + c0;
                         float* yp = e.y + (int64_t)row * e.ldc + colb;
@@ -356,6 +382,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
                             }
                         }
                     }
+                    if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 12 + (ch >> 1) * 2);
                 }
             } else if constexpr (EPI == EPI_PROJ) {
                 const TcProjEpi& e = ep;
@@ -398,15 +425,28 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
                 }
             } else {
                 const TcHeadEpi& e = ep;
-                float* part = reinterpret_cast<float*>(smem + TC_STAGES * L::STAGE_BYTES);   // [2][128] partial row sums
+                float* part = reinterpret_cast<float*>(smem + ST * L::STAGE_BYTES);   // [2][128] partial row sums
+                const float4* cb = reinterpret_cast<const float4*>(part + 256);              // b1[128] then w2[128]
                 float acc = 0.0f;
 #pragma unroll 1
                 for (int ch = half; ch < BN / 32; ch += 2) {
                     const int c0 = ch * 32;
                     float v[32];
                     tc_ld32(taddr + c0, v);
+                    auto dot = [&](auto actf) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) acc += apply_act(v[j] + __ldg(e.b1 + c0 + j), e.act) * __ldg(e.w2 + c0 + j);
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 b = cb[(c0 >> 2) + j4], w = cb[32 + (c0 >> 2) + j4];
+                            acc = fmaf(actf(v[4 * j4] + b.x), w.x, acc);
+                            acc = fmaf(actf(v[4 * j4 + 1] + b.y), w.y, acc);
+                            acc = fmaf(actf(v[4 * j4 + 2] + b.z), w.z, acc);
+                            acc = fmaf(actf(v[4 * j4 + 3] + b.w), w.w, acc);
+                        }
+                    };
+                    if (e.act == SPGT_ACT_SILU) dot([](float x) { return silu_f(x); });
+                    else if (e.act == SPGT_ACT_RELU) dot([](float x) { return fmaxf(x, 0.0f); });
+                    else if (e.act == SPGT_ACT_SILU2) dot([](float x) { return silu_f(silu_f(x)); });
+                    else dot([](float x) { return x; });
                 }
                 if (half == 1) part[(ti & 1) * 128 + r_in_tile] = acc;
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");   // epilogue warps only
@@ -425,6 +465,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
             }
             tc_fence_before();
             mbar_arrive(acce_bar(buf));
+            if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 10);
         }
     }
     // teardown: everyone meets, then the allocating warp frees the tensor memory
@@ -436,10 +477,12 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ w_hi, const float* __restric
     }
 }
 
-// ---- weight preparation: [K][ldw] row-major fp32 -> hi / lo tf32 planes [Npad][Kpad], K-major, zero padded ------
-__global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, int K, int N, int kpad, int npad,
-                                         float* __restrict__ hi, float* __restrict__ lo) {
+// ---- weight preparation: [K][ldw] row-major fp32 -> per (column tile, k-block) the exact shared-memory image the
+// kernel needs: W_hi then W_lo, each [bn rows (n)][32 k] K-major with the 128-byte swizzle applied, zero padded.
+__global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, int K, int N, int kpad, int npad, int bn,
+                                         float* __restrict__ img) {
     const int64_t total = (int64_t)npad * kpad;
+    const int KB = kpad / TC_BK;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int n = (int)(i / kpad), k = (int)(i % kpad);
         const float v = (n < N && k < K) ? __ldg(w + (int64_t)k * ldw + n) : 0.0f;
@@ -447,16 +490,18 @@ __global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, i
         split_tf32(v, h, l);
         uint32_t l2;
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l2) : "f"(__uint_as_float(l)));
-        hi[i] = __uint_as_float(h);
-        lo[i] = __uint_as_float(l2);
+        const int nt = n / bn, r = n % bn, kb = k / TC_BK, kk = k % TC_BK;
+        const int64_t blk = ((int64_t)nt * KB + kb) * (2 * bn * TC_BK);
+        const int off = (int)(tc_swz(r, kk >> 2) >> 2) + (kk & 3);
+        img[blk + off] = __uint_as_float(h);
+        img[blk + bn * TC_BK + off] = __uint_as_float(l2);
     }
 }
 
 static int tc_bn_for(int N) { return N <= 32 ? 32 : (N <= 48 ? 48 : (N <= 64 ? 64 : 128)); }
 
 template <int BN, class Loader, int EPI, class EpiParams>
-static int tc_launch(Loader ld, const float* w_hi, const float* w_lo, int kpad, int rows, int n_tiles, const EpiParams& ep,
-                     cudaStream_t st) {
+static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_tiles, const EpiParams& ep, cudaStream_t st) {
     static bool done = false;
     auto kern = tc_gemm_kernel<BN, Loader, EPI, EpiParams>;
     if (!done) {
@@ -466,21 +511,19 @@ static int tc_launch(Loader ld, const float* w_hi, const float* w_lo, int kpad, 
     const int m_tiles = ceil_div(rows, TC_BM);
     const int64_t tiles = (int64_t)m_tiles * n_tiles;
     const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
-    kern<<<grid, TC_THREADS, TcSmem<BN>::BYTES, st>>>(ld, w_hi, w_lo, kpad, rows, n_tiles, m_tiles, ep);
+    kern<<<grid, TC_THREADS, TcSmem<BN>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_tiles, ep);
     return launch_status();
 }
 
 template <class Loader>
 static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int rows, const TcLinearEpi& ep, cudaStream_t st) {
     const int bn = tc_bn_for(N), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
-    const float* hi = wprep;
-    const float* lo = wprep + (size_t)npad * kpad;
     const int n_tiles = npad / bn;
     switch (bn) {
-        case 32: return tc_launch<32, Loader, EPI_LINEAR, TcLinearEpi>(ld, hi, lo, kpad, rows, n_tiles, ep, st);
-        case 48: return tc_launch<48, Loader, EPI_LINEAR, TcLinearEpi>(ld, hi, lo, kpad, rows, n_tiles, ep, st);
-        case 64: return tc_launch<64, Loader, EPI_LINEAR, TcLinearEpi>(ld, hi, lo, kpad, rows, n_tiles, ep, st);
-        default: return tc_launch<128, Loader, EPI_LINEAR, TcLinearEpi>(ld, hi, lo, kpad, rows, n_tiles, ep, st);
+        case 32: return tc_launch<32, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+        case 48: return tc_launch<48, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+        case 64: return tc_launch<64, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+        default: return tc_launch<128, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     }
 }
 
@@ -501,11 +544,16 @@ extern "C" int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, 
     if (out_bytes < spgt_tc_weight_bytes(K, N)) return SPGT_ERR_WORKSPACE;
     if (!aligned16(out)) return SPGT_ERR_ALIGN;
     const int bn = tc_bn_for(N), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
-    float* hi = (float*)out;
-    tc_weight_prepare_kernel<<<ceil_div(npad * kpad, 256), 256, 0, (cudaStream_t)stream>>>(w_kn, ldw, K, N, kpad, npad, hi,
-                                                                                         hi + (size_t)npad * kpad);
+    tc_weight_prepare_kernel<<<ceil_div(npad * kpad, 256), 256, 0, (cudaStream_t)stream>>>(w_kn, ldw, K, N, kpad, npad, bn,
+                                                                                         (float*)out);
     return launch_status();
 }
+
+#ifdef SPGT_TC_TRACE
+extern "C" int spgt_tc_trace_read(long long* host_out) {   // 64 tiles x 16 slots of clock64() values of CTA 0
+    return cudaMemcpyFromSymbol(host_out, g_tc_trace, sizeof(long long) * 64 * 16) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
+}
+#endif
 
 extern "C" int spgt_tc_status(void) {
     int v = 0;
@@ -557,9 +605,8 @@ extern "C" int spgt_projpos_qkv_tc_fwd(const float* x, const void* wprep_qkv, co
     ep.bias[0] = bq; ep.bias[1] = bk; ep.bias[2] = bv;
     ep.lnw[1] = lnwk; ep.lnb[1] = lnbk; ep.lnw[2] = lnwv; ep.lnb[2] = lnbv;
     ep.out[0] = q; ep.out[1] = k; ep.out[2] = v; ep.pos = pos; ep.eps = eps; ep.S = S; ep.H = H; ep.d_pos = d_pos;
-    const float* hi = (const float*)wprep_qkv;          // prepared from the [128, 384] concatenation of Wq | Wk | Wv
-    const float* lo = hi + (size_t)384 * 128;
-    return tc_launch<128, TcDense, EPI_PROJ, TcProjEpi>(ld, hi, lo, 128, (int)rows64, 3, ep, (cudaStream_t)stream);
+    // wprep_qkv is prepared from the [128, 384] concatenation of Wq | Wk | Wv: three column tiles of 128
+    return tc_launch<128, TcDense, EPI_PROJ, TcProjEpi>(ld, (const float*)wprep_qkv, 128, (int)rows64, 3, ep, (cudaStream_t)stream);
 }
 
 extern "C" int spgt_decoder_head_tc_fwd(const float* x, const void* w1prep, const float* b1, const float* w2, float b2,
@@ -575,7 +622,5 @@ extern "C" int spgt_decoder_head_tc_fwd(const float* x, const void* w1prep, cons
     ld.x = x; ld.lda = K; ld.rows = (int)rows64; ld.K = K;
     TcHeadEpi ep{b1, w2, b2, scale, shift, scale_map, shift_map, dirichlet, Hh, Ww, act, out};
     const int kpad = ceil_div(K, TC_BK) * TC_BK;
-    const float* hi = (const float*)w1prep;
-    return tc_launch<128, TcDense, EPI_HEAD, TcHeadEpi>(ld, hi, hi + (size_t)128 * kpad, kpad, (int)rows64, 1, ep,
-                                                       (cudaStream_t)stream);
+    return tc_launch<128, TcDense, EPI_HEAD, TcHeadEpi>(ld, (const float*)w1prep, kpad, (int)rows64, 1, ep, (cudaStream_t)stream);
 }
