@@ -1,32 +1,41 @@
-// Dense contractions on the 5th-generation tensor cores (tcgen05, accumulators in TMEM) with 3xTF32:
+// Dense contractions on the 5th-generation tensor cores (tcgen05) with 3xTF32:
 //   C[rows, N] = A[rows, K] * W[K, N],   A*W ~= A_lo*W_hi + A_hi*W_lo + A_hi*W_hi   (fp32-level accuracy).
 //
-// Persistent, warp-specialised kernel, one CTA per SM:
-//   warps 0-3  loaders   : cp.async the raw fp32 A tile (dense rows or implicit-GEMM 3x3 gather) into 128B-swizzled
-//                          K-major shared memory (completion tracked by an mbarrier); one thread bulk-copies the
-//                          pre-split, pre-swizzled W_hi | W_lo image of the k-block;
-//   warps 4-7  splitters : split the landed A tile in place into hi (tf32, round-to-nearest) and lo (x - hi);
-//   warp  8    MMA       : one elected lane issues tcgen05.mma.kind::tf32 (128 x BN x 8) three times per k-step,
-//                          tcgen05.commit releases the smem stage / publishes the accumulator;
-//   warps 9-16 epilogue  : tcgen05.ld the 128 x BN fp32 accumulator (one row per thread, two warps per TMEM lane
-//                          quarter splitting the columns) and run the fused epilogue while the MMA warp already
-//                          works on the next tile (TMEM double buffer).
+// Persistent, warp-specialised kernel, one CTA (576 threads) per SM.  A 128 x 128 x 8 tf32 MMA with both operands
+// in shared memory already consumes the whole shared-memory bandwidth of an SM, and 3xTF32 reads every operand
+// twice, so the operands are kept off that path:
+//   * A (activations) is an MMA operand in TENSOR MEMORY: loader warps cp.async the raw fp32 tile (dense rows, or
+//     the implicit-GEMM gather of a 3x3 convolution) with fully coalesced 16-byte copies into a 128B-swizzled
+//     staging ring; splitter threads own one row each, read it back conflict-free, split it into tf32 hi / lo and
+//     write both into TMEM with tcgen05.st.  (Loading one row per thread straight from global memory was tried:
+//     its 32 lines per load instruction saturate the L1 miss path and slow every other memory access of the SM.)
+//   * W is prepared once (split, transposed to K-major, 128B-swizzled tile images) and arrives by one
+//     cp.async.bulk per k-block; when a whole column tile of W fits the ring it stays resident for the kernel.
+//   * Accumulators live in TMEM.  MT = 1: one 128-row tile with double-buffered accumulators (the epilogue of a
+//     tile overlaps the MMAs of the next).  MT = 2: two 128-row tiles share every W stage (halves the L2 traffic of
+//     W for long-K problems such as the 3x3 convolutions).
+//   * Row-major epilogues stage each thread's row in padded shared memory and leave through cp.async.bulk stores
+//     (full 128-byte lines); the projection epilogue (LayerNorm + head-major transposed store) and the decoder
+//     head (row dot product) store directly, one row per thread.
+//   warps 0-3 A loaders, 4-7 A splitters, 8 W loader, 9 MMA issuer (one elected lane), 10-17 epilogue.
 // All waits are bounded mbarrier polls: on expiry the kernel records an error code, stops waiting and returns.
 #include "common.cuh"
 
 namespace spgt {
 
 constexpr int TC_BM = 128, TC_BK = 32;
-constexpr int TC_PROD_THREADS = 128, TC_MMA_WARP = 8, TC_EPI_WARP0 = 9, TC_EPI_WARPS = 8, TC_THREADS = 32 * (9 + TC_EPI_WARPS);
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
+constexpr int TC_BLOAD_WARP = 8, TC_MMA_WARP = 9, TC_EPI_WARP0 = 10, TC_EPI_WARPS = 8;
+constexpr int TC_THREADS = 32 * (TC_EPI_WARP0 + TC_EPI_WARPS);
+constexpr int TC_SLOT_BYTES = 144;            // per-epilogue-thread staging row: 32 floats + 16 bytes (bank skew)
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 
 __device__ int g_tc_status = 0;          // 0 = ok; otherwise the code of the first wait that gave up
 
-#ifdef SPGT_TC_TRACE                      // developer build only: per-tile timestamps of CTA 0 (see spgt_tc_trace_read)
-__device__ long long g_tc_trace[64 * 16];
-#define TC_TRACE(tile_i, slot) do { if (blockIdx.x == 0 && (tile_i) < 64) g_tc_trace[(tile_i) * 16 + (slot)] = clock64(); } while (0)
+#ifdef SPGT_TC_TRACE                      // developer build only: per-unit timestamps of CTA 0 (see spgt_tc_trace_read)
+__device__ long long g_tc_trace[64 * 32];
+#define TC_TRACE(unit_i, slot) do { if (blockIdx.x == 0 && (unit_i) < 64) g_tc_trace[(unit_i) * 32 + (slot)] = clock64(); } while (0)
 #else
-#define TC_TRACE(tile_i, slot) do { } while (0)
+#define TC_TRACE(unit_i, slot) do { } while (0)
 #endif
 
 // ---- mbarrier / tcgen05 primitives -------------------------------------------------------------------------
@@ -40,9 +49,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(100000u) : "memory");     // suspend-time hint (ns): sleep, do not spin
     return ok;
 }
 // Bounded wait.  Returns false (and latches *abort_flag) when the limit is reached or another thread gave up.
@@ -61,13 +70,13 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc], M = 128, N from the instruction descriptor, K = 8 (tf32)
-__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem desc], M = 128, N from the instruction descriptor, K = 8 (tf32)
+__device__ __forceinline__ void tc_mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t* u = reinterpret_cast<uint32_t*>(v);
@@ -81,7 +90,7 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
         : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
     uint32_t* u = reinterpret_cast<uint32_t*>(v);
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -90,6 +99,14 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
         : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// Store 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&u)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]),
+          "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile with 128-byte rows, SWIZZLE_128B: 8-row groups are 1024 B apart (SBO), LBO unused (1),
 // descriptor version 1 (sm_100), layout type 2.  The tile base must be 1024-byte aligned.
@@ -102,53 +119,57 @@ __host__ __device__ constexpr uint32_t tc_idesc(int bn) {
 }
 // byte offset of 16-byte chunk `c` (0..7) of row `r` inside a swizzled tile
 __host__ __device__ __forceinline__ uint32_t tc_swz(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
+__host__ __device__ constexpr int tc_cols_per_thread(int bn, int mt) { return mt == 1 ? bn / 2 : bn; }
 
-// ---- A-operand loaders (producer side; 128 threads, thread -> chunk (t & 7) of rows (t >> 3) + 16 i) ---------
+// ---- A-operand loaders.  A loader thread copies 16-byte chunk (t & 7) of rows (t >> 3) + 16 i of every tile:
+// per-row state is computed once per work unit, per-k-block state once per k-block.
 struct TcDense {
     const float* x; int lda; int rows; int K;
-    const float* rp[8]; bool rok[8]; int kc; bool kok;
-    __device__ void init(int row0, int t) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int row = row0 + (t >> 3) + 16 * i;
-            rok[i] = row < rows;
-            rp[i] = x + (int64_t)(rok[i] ? row : 0) * lda;
-        }
+    struct Row { const float* p; bool ok; };
+    struct Kst { int kc; bool ok; };
+    __device__ __forceinline__ Row row_state(int row) const {
+        Row r; r.ok = row < rows; r.p = x + (int64_t)(r.ok ? row : 0) * lda; return r;
     }
-    __device__ void set_k(int k0, int t) { kc = k0 + (t & 7) * 4; kok = kc < K; if (!kok) kc = 0; }
-    __device__ const float* ptr(int i, bool& ok) const { ok = rok[i] && kok; return rp[i] + kc; }
+    __device__ __forceinline__ Kst k_state(int kb, int chunk) const {
+        Kst k; k.kc = kb * TC_BK + chunk * 4; k.ok = k.kc < K; if (!k.ok) k.kc = 0; return k;
+    }
+    __device__ __forceinline__ const float* ptr(const Row& r, const Kst& k, bool& ok) const { ok = r.ok && k.ok; return r.p + k.kc; }
 };
-struct TcConv {          // 3x3, padding 1, NHWC; K = 9 * Cin with Cin % 4 == 0
+struct TcConv {          // 3x3, padding 1, NHWC; k = tap * Cin + c with Cin % 4 == 0
     const float* x; int cin_pitch, cin_off, Cin, Hh, Ww; int rows; int K;
-    const float* rp[8]; int py[8], px[8]; int dy, dx, coff; bool kok;
-    __device__ void init(int row0, int t) {
+    struct Row { const float* p; uint32_t mask; };     // bit tap of mask: the tap's source pixel lies inside the image
+    struct Kst { int off; int tap; };
+    __device__ __forceinline__ Row row_state(int row) const {
+        Row r; r.mask = 0; r.p = x;
+        if (row < rows) {
+            const int b = row / (Hh * Ww);
+            const int rem = row - b * Hh * Ww;
+            const int py = rem / Ww, px = rem - py * Ww;
+            r.p = x + (int64_t)row * cin_pitch + cin_off;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int row = row0 + (t >> 3) + 16 * i;
-            if (row < rows) {
-                const int b = row / (Hh * Ww);
-                const int rem = row - b * Hh * Ww;
-                py[i] = rem / Ww; px[i] = rem - py[i] * Ww;
-                rp[i] = x + (int64_t)row * cin_pitch + cin_off;
-            } else { py[i] = -(1 << 20); px[i] = 0; rp[i] = x; }
+            for (int tap = 0; tap < 9; ++tap) {
+                const int yy = py + tap / 3 - 1, xx = px + tap % 3 - 1;
+                if (yy >= 0 && yy < Hh && xx >= 0 && xx < Ww) r.mask |= 1u << tap;
+            }
         }
+        return r;
     }
-    __device__ void set_k(int k0, int t) {
-        const int k = k0 + (t & 7) * 4;
-        kok = k < K;
-        const int tap = kok ? k / Cin : 4;
-        const int c = kok ? k - tap * Cin : 0;
-        dy = tap / 3 - 1; dx = tap % 3 - 1;
-        coff = (dy * Ww + dx) * cin_pitch + c;
+    __device__ __forceinline__ Kst k_state(int kb, int chunk) const {
+        Kst k;
+        const int kk = kb * TC_BK + chunk * 4;
+        k.tap = kk / Cin;                               // >= 9 in the zero padding of K: no mask bit is set there
+        const int c = kk - k.tap * Cin;
+        const int dy = k.tap / 3 - 1, dx = k.tap - (k.tap / 3) * 3 - 1;
+        k.off = (dy * Ww + dx) * cin_pitch + c;
+        return k;
     }
-    __device__ const float* ptr(int i, bool& ok) const {
-        const int yy = py[i] + dy, xx = px[i] + dx;
-        ok = kok && yy >= 0 && yy < Hh && xx >= 0 && xx < Ww;
-        return ok ? rp[i] + coff : x;
+    __device__ __forceinline__ const float* ptr(const Row& r, const Kst& k, bool& ok) const {
+        ok = (r.mask >> k.tap) & 1u;
+        return ok ? r.p + k.off : x;
     }
 };
 
-// ---- epilogues (epilogue side; thread = one row of the 128-row tile, columns arrive 32 at a time) -----------
+// ---- epilogue parameter blocks ------------------------------------------------------------------------------
 struct TcLinearEpi {
     const float* bias; const float* residual; int ldr; float* y; int ldc; int N; int act;
 };
@@ -160,229 +181,302 @@ struct TcHeadEpi {
     const float* b1; const float* w2; float b2, scale, shift; const float* scale_map; const float* shift_map;
     int dirichlet, Hh, Ww, act; float* out;
 };
-
-template <int BN> struct TcSmem {
-    static constexpr int A_BYTES = TC_BM * TC_BK * 4;           // 16 KB
-    static constexpr int B_BYTES = BN * TC_BK * 4;
-    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;     // A_hi(raw), A_lo, B_hi, B_lo
-    static constexpr int STAGES = (BN > 64) ? 3 : 4;
-    static constexpr int STAGING_BYTES = (2 * 128 + 256) * 4;         // partial row sums of epilogue warp pairs + b1 | w2 of the head
-    static constexpr int BAR_BYTES = 192;
-    static constexpr size_t BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
-};
-
 enum { EPI_LINEAR = 0, EPI_PROJ = 1, EPI_HEAD = 2 };
 
-template <int BN, class Loader, int EPI, class EpiParams>
+template <int BN, int MT> struct TcCfg {
+    static constexpr int NBUF = (MT == 1) ? 2 : 1;                  // accumulator buffers
+    static constexpr int ACC_COLS = NBUF * MT * BN;
+    static constexpr int SA = (MT == 1) ? 4 : 2;                    // A stages in TMEM, 64 columns (hi|lo) per tile
+    static_assert(ACC_COLS + SA * MT * 64 <= 512, "tensor memory budget");
+    static constexpr int B_BYTES = 2 * BN * TC_BK * 4;              // W_hi | W_lo image of one k-block
+    static constexpr int SB = (BN == 128) ? (MT == 1 ? 4 : 3) : 6;  // W stages in shared memory
+    static constexpr int RAW_BYTES = MT * TC_BM * TC_BK * 4;        // raw fp32 A tile(s) of one k-block
+    static constexpr int SR = (MT == 1) ? 3 : 2;                    // raw A stages in shared memory
+    static constexpr int STAGING_BYTES = 32 * TC_EPI_WARPS * TC_SLOT_BYTES;
+    static constexpr int CONST_BYTES = 2048;                        // per-CTA epilogue constants (bias, LayerNorm affine, head vectors)
+    static constexpr int BAR_BYTES = 320;
+    static constexpr size_t BYTES = 1024 + (size_t)SB * B_BYTES + SR * RAW_BYTES + STAGING_BYTES + CONST_BYTES + BAR_BYTES;
+};
+
+template <int BN, int MT, class Loader, int EPI, class EpiParams>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_tiles, EpiParams ep) {
-    using L = TcSmem<BN>;
-    constexpr int ST = L::STAGES;
+tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_units, EpiParams ep) {
+    using C = TcCfg<BN, MT>;
+    constexpr int SA = C::SA, SB = C::SB, NBUF = C::NBUF, SR = C::SR;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // 1024-aligned for the 128B swizzle
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t stage0 = smem_base;
-    const uint32_t bars = smem_base + ST * L::STAGE_BYTES + L::STAGING_BYTES;
-    // barrier slots (8 bytes each): full[4], empty[4], raw[4], acc_full[2], acc_empty[2]; then tmem ptr, abort flag
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (4 + s); };
-    auto raw_bar = [&](int s) { return bars + 8u * (8 + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (12 + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (14 + b); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + ST * L::STAGE_BYTES + L::STAGING_BYTES + 128);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + ST * L::STAGE_BYTES + L::STAGING_BYTES + 144);
+    uint8_t* raw = smem + SB * C::B_BYTES;                                      // raw A ring (1024-aligned stages)
+    uint8_t* staging = raw + SR * C::RAW_BYTES;
+    float* consts = reinterpret_cast<float*>(staging + C::STAGING_BYTES);
+    uint8_t* bar_mem = staging + C::STAGING_BYTES + C::CONST_BYTES;
+    const uint32_t bars = smem_u32(bar_mem);
+    // barrier slots (8 bytes each)
+    auto a_full = [&](int s) { return bars + 8u * s; };                 // [4]
+    auto a_empty = [&](int s) { return bars + 8u * (4 + s); };          // [4]
+    auto b_full = [&](int s) { return bars + 8u * (8 + s); };           // [6]
+    auto b_empty = [&](int s) { return bars + 8u * (14 + s); };         // [6]
+    auto acc_full = [&](int b) { return bars + 8u * (20 + b); };        // [2]
+    auto acc_empty = [&](int b) { return bars + 8u * (22 + b); };       // [2]
+    auto raw_full = [&](int s) { return bars + 8u * (24 + s); };        // [3]
+    auto raw_empty = [&](int s) { return bars + 8u * (27 + s); };       // [3]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 256);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 264);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    constexpr int TMEM_COLS = (2 * BN <= 64) ? 64 : (2 * BN <= 128 ? 128 : 256);
+    const int KB = kpad / TC_BK;
+    const bool resident = KB <= SB;          // the whole column tile of W stays in shared memory
 
     if (tid == 0) {
-        for (int s = 0; s < ST; ++s) { mbar_init(full_bar(s), TC_PROD_THREADS + 1); mbar_init(empty_bar(s), 1); mbar_init(raw_bar(s), TC_PROD_THREADS); }
-        for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 32 * TC_EPI_WARPS); }
+        for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 1); }
+        for (int s = 0; s < SR; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
+        for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 32 * TC_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TC_MMA_WARP) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // Epilogue constants of this CTA's column tile go to shared memory once: a global load issued from the epilogue
+    // queues behind the producers' traffic and costs microseconds of latency per use.
     if constexpr (EPI == EPI_HEAD) {
-        float* cst = reinterpret_cast<float*>(smem + ST * L::STAGE_BYTES) + 256;
-        for (int i = tid; i < 256; i += TC_THREADS) cst[i] = i < 128 ? __ldg(ep.b1 + i) : __ldg(ep.w2 + i - 128);
+        for (int i = tid; i < 256; i += TC_THREADS) consts[i] = i < 128 ? __ldg(ep.b1 + i) : __ldg(ep.w2 + i - 128);
+    } else if constexpr (EPI == EPI_LINEAR) {
+        const int ntc = blockIdx.x % n_tiles;
+        for (int i = tid; i < BN; i += TC_THREADS) {
+            const int col = ntc * BN + i;
+            consts[i] = (ep.bias != nullptr && col < ep.N) ? __ldg(ep.bias + col) : 0.0f;
+        }
+    } else {
+        const int p = blockIdx.x % n_tiles;
+        for (int i = tid; i < 128; i += TC_THREADS) {
+            consts[i] = ep.bias[p] ? __ldg(ep.bias[p] + i) : 0.0f;
+            consts[128 + i] = ep.lnw[p] ? __ldg(ep.lnw[p] + i) : 1.0f;
+            consts[256 + i] = ep.lnb[p] ? __ldg(ep.lnb[p] + i) : 0.0f;
+        }
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a = tmem_base + C::ACC_COLS;
 
-    const int KB = kpad / TC_BK;
-    const int total_tiles = m_tiles * n_tiles;
+    // Work distribution: this CTA keeps one column tile (so a resident W is loaded once) and strides over row units.
+    const int ctas_per_nt = gridDim.x / n_tiles;
+    const int nt = blockIdx.x % n_tiles;
+    const int u0 = blockIdx.x / n_tiles;
+    const int n_my_units = (u0 < m_units) ? (m_units - u0 + ctas_per_nt - 1) / ctas_per_nt : 0;
+    const float* wtile = wimg + (int64_t)nt * KB * (C::B_BYTES / 4);
 
     if (warp < 4) {
-        // ------------------------------------------ loaders ------------------------------------------
+        // ------------------------------------------ A loaders ------------------------------------------
         const int t = tid;
-        uint32_t it = 0;
         uint32_t aoff[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) aoff[i] = tc_swz((t >> 3) + 16 * i, t & 7);
+        const uint32_t raw_s = smem_u32(raw);
+        int64_t slot = 0;
         bool alive = true;
-        for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-            const int row0 = (tile / n_tiles) * TC_BM;
-            ld.init(row0, t);
-            if (t == 0) TC_TRACE(it / KB, 0);
-            const float* wtile = wimg + (int64_t)(tile % n_tiles) * KB * (2 * L::B_BYTES / 4);
-            for (int kb = 0; kb < KB; ++kb, ++it) {
-                const uint32_t s = it % ST, ph = (it / ST) & 1;
-                if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 1)) { alive = false; break; }
-                const uint32_t a_hi = stage0 + s * L::STAGE_BYTES;
-                if (t == 0) {      // the pre-swizzled W_hi | W_lo image of this (column tile, k-block): one bulk copy
-                    const uint32_t bytes = 2 * L::B_BYTES;
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(s)), "r"(bytes) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(a_hi + 2 * L::A_BYTES), "l"(wtile + (int64_t)kb * (2 * L::B_BYTES / 4)), "r"(bytes), "r"(full_bar(s)) : "memory");
-                }
-                ld.set_k(kb * TC_BK, t);
+        for (int ui = 0; ui < n_my_units && alive; ++ui) {
+            const int row0 = (u0 + ui * ctas_per_nt) * MT * TC_BM + (t >> 3);
+            typename Loader::Row rs[MT][8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    bool ok;
-                    const float* p = ld.ptr(i, ok);
-                    const int n = ok ? 16 : 0;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_hi + aoff[i]), "l"(p), "r"(n) : "memory");
-                }
-                // arrive on raw[s] once every cp.async issued so far by this thread has landed
-                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_bar(s)) : "memory");
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) rs[m][i] = ld.row_state(row0 + m * TC_BM + 16 * i);
+            for (int kb = 0; kb < KB; ++kb, ++slot) {
+                const uint32_t sr = (uint32_t)(slot % SR), ph = (uint32_t)((slot / SR) & 1);
+                if (!mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1)) { alive = false; break; }
+                const typename Loader::Kst ks = ld.k_state(kb, t & 7);
+                const uint32_t dst = raw_s + sr * C::RAW_BYTES;
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        bool ok;
+                        const float* p = ld.ptr(rs[m][i], ks, ok);
+                        const int n = ok ? 16 : 0;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + m * (TC_BM * TC_BK * 4) + aoff[i]), "l"(p), "r"(n) : "memory");
+                    }
+                // arrive on raw_full[sr] once every cp.async issued so far by this thread has landed
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_full(sr)) : "memory");
             }
-            if (t == 0) TC_TRACE((it - 1) / KB, 1);
         }
         cp_async_wait_all();
     } else if (warp < 8) {
-        // ------------------------------------------ splitters ------------------------------------------
-        const int t = tid - 128;
-        uint32_t it = 0;
-        uint32_t aoff[8];
+        // ------------------------------------------ A splitters ------------------------------------------
+        const int q = warp & 3;                                  // TMEM lane quarter of this warp
+        const int r = q * 32 + lane;                             // the row (TMEM lane) owned by this thread
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        uint32_t roff[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) aoff[i] = tc_swz((t >> 3) + 16 * i, t & 7);
-        bool alive = true;
-        for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-            for (int kb = 0; kb < KB; ++kb, ++it) {
-                const uint32_t s = it % ST, ph = (it / ST) & 1;
-                if (!mbar_wait(raw_bar(s), ph, abort_flag, 5)) { alive = false; break; }
-                if (t == 0 && kb == 0) TC_TRACE(it / KB, 2);
-                uint8_t* a_hi = smem + s * L::STAGE_BYTES;
-                uint8_t* a_lo = a_hi + L::A_BYTES;
+        for (int c = 0; c < 8; ++c) roff[c] = tc_swz(r, c);
+        const int64_t total = (int64_t)n_my_units * KB;
+        for (int64_t slot = 0; slot < total; ++slot) {
+            const uint32_t sr = (uint32_t)(slot % SR), pr = (uint32_t)((slot / SR) & 1);
+            const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
+            if (!mbar_wait(raw_full(sr), pr, abort_flag, 5)) break;
+            if (!mbar_wait(a_empty(sa), pa ^ 1, abort_flag, 8)) break;
+            tc_fence_after();
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const uint8_t* src = raw + sr * C::RAW_BYTES + m * (TC_BM * TC_BK * 4);
                 float4 v[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = *reinterpret_cast<float4*>(a_hi + aoff[i]);
+                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(src + roff[c]);
+                const uint32_t a_hi = tmem_a + lane_addr + (sa * MT + m) * 64;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    uint32_t h[4], l[4];
-                    split_tf32(v[i].x, h[0], l[0]); split_tf32(v[i].y, h[1], l[1]);
-                    split_tf32(v[i].z, h[2], l[2]); split_tf32(v[i].w, h[3], l[3]);
-                    *reinterpret_cast<uint4*>(a_hi + aoff[i]) = make_uint4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<uint4*>(a_lo + aoff[i]) = make_uint4(l[0], l[1], l[2], l[3]);
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 w = v[4 * h + j];
+                        split_tf32(w.x, hi[4 * j], lo[4 * j]); split_tf32(w.y, hi[4 * j + 1], lo[4 * j + 1]);
+                        split_tf32(w.z, hi[4 * j + 2], lo[4 * j + 2]); split_tf32(w.w, hi[4 * j + 3], lo[4 * j + 3]);
+                    }
+                    tc_st16(a_hi + 16 * h, hi);
+                    tc_st16(a_hi + 32 + 16 * h, lo);
                 }
-                fence_proxy_async();                     // generic-proxy writes -> visible to the tensor core
-                mbar_arrive(full_bar(s));
-                if (t == 0 && kb == KB - 1) TC_TRACE(it / KB, 3);
+            }
+            mbar_arrive(raw_empty(sr));                         // the raw stage has been read
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(a_full(sa));
+        }
+    } else if (warp == TC_BLOAD_WARP) {
+        // ------------------------------------------ W loader ------------------------------------------
+        if (lane == 0 && n_my_units > 0) {
+            const uint32_t bytes = C::B_BYTES;
+            const int64_t total = resident ? KB : (int64_t)n_my_units * KB;
+            for (int64_t slot = 0; slot < total; ++slot) {
+                const uint32_t sb = (uint32_t)(slot % SB), ph = (uint32_t)((slot / SB) & 1);
+                if (!mbar_wait(b_empty(sb), ph ^ 1, abort_flag, 6)) break;
+                const int kb = (int)(slot % KB);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(sb)), "r"(bytes) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(smem_base + sb * C::B_BYTES), "l"(wtile + (int64_t)kb * (C::B_BYTES / 4)), "r"(bytes), "r"(b_full(sb)) : "memory");
             }
         }
     } else if (warp == TC_MMA_WARP) {
         // ------------------------------------------ MMA issuer ------------------------------------------
         constexpr uint32_t idesc = tc_idesc(BN);
-        uint32_t it = 0, ti = 0;
+        int64_t slot = 0;
         bool alive = true;
-        for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++ti) {
-            const uint32_t buf = ti & 1, aph = (ti >> 1) & 1;
-            if (lane == 0) TC_TRACE(ti, 4);
-            if (!mbar_wait(acce_bar(buf), aph ^ 1, abort_flag, 2)) { alive = false; break; }
-            if (lane == 0) TC_TRACE(ti, 5);
+        for (int ui = 0; ui < n_my_units && alive; ++ui) {
+            const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
+            if (lane == 0) TC_TRACE(ui, 4);
+            if (!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2)) { alive = false; break; }
+            if (lane == 0) TC_TRACE(ui, 5);
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + buf * BN;
-            for (int kb = 0; kb < KB; ++kb, ++it) {
-                const uint32_t s = it % ST, ph = (it / ST) & 1;
-                if (!mbar_wait(full_bar(s), ph, abort_flag, 3)) { alive = false; break; }
-                if (lane == 0 && kb == 0) TC_TRACE(ti, 6);
+            for (int kb = 0; kb < KB; ++kb, ++slot) {
+                const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
+                const uint32_t sb = resident ? (uint32_t)kb : (uint32_t)(slot % SB);
+                const uint32_t pb = resident ? 0u : (uint32_t)((slot / SB) & 1);
+                if (!mbar_wait(a_full(sa), pa, abort_flag, 3)) { alive = false; break; }
+                if (!resident || ui == 0) {
+                    if (!mbar_wait(b_full(sb), pb, abort_flag, 7)) { alive = false; break; }
+                }
+                if (lane == 0 && kb == 0) TC_TRACE(ui, 6);
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a_hi = stage0 + s * L::STAGE_BYTES;
-                    const uint64_t dah = tc_smem_desc(a_hi), dal = tc_smem_desc(a_hi + L::A_BYTES);
-                    const uint64_t dbh = tc_smem_desc(a_hi + 2 * L::A_BYTES), dbl = tc_smem_desc(a_hi + 2 * L::A_BYTES + L::B_BYTES);
+                    const uint32_t b_hi = smem_base + sb * C::B_BYTES;
+                    const uint64_t dbh = tc_smem_desc(b_hi), dbl = tc_smem_desc(b_hi + C::B_BYTES / 2);
 #pragma unroll
                     for (int k8 = 0; k8 < TC_BK / 8; ++k8) {
                         const uint64_t adv = (uint64_t)(k8 * 2);          // 32 bytes per k-step, in 16-byte units
-                        tc_mma_tf32(d_tmem, dal + adv, dbh + adv, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
-                        tc_mma_tf32(d_tmem, dah + adv, dbl + adv, idesc, 1u);
-                        tc_mma_tf32(d_tmem, dah + adv, dbh + adv, idesc, 1u);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const uint32_t d = tmem_base + (buf * MT + mt) * BN;
+                            const uint32_t ah = tmem_a + (sa * MT + mt) * 64 + k8 * 8, al = ah + 32;
+                            const uint32_t accum = (kb > 0 || k8 > 0) ? 1u : 0u;
+                            tc_mma_tf32_ts(d, al, dbh + adv, idesc, accum);
+                            tc_mma_tf32_ts(d, ah, dbl + adv, idesc, 1u);
+                            tc_mma_tf32_ts(d, ah, dbh + adv, idesc, 1u);
+                        }
                     }
-                    tc_commit(empty_bar(s));           // stage reusable once these MMAs have read it
+                    tc_commit(a_empty(sa));            // A stage reusable once these MMAs have read it
+                    if (!resident) tc_commit(b_empty(sb));
                 }
                 __syncwarp();
             }
-            if (alive && lane == 0) tc_commit(accf_bar(buf));
-            if (lane == 0) TC_TRACE(ti, 7);
+            if (alive && lane == 0) tc_commit(acc_full(buf));
+            if (lane == 0) TC_TRACE(ui, 7);
             __syncwarp();
         }
     } else {
         // ------------------------------------------ epilogue ------------------------------------------
-        const int q = warp & 3;                        // TMEM lane quarter this warp may access
-        const int half = (warp - TC_EPI_WARP0) >> 2;   // which half of the column chunks this warp of the pair takes
+        const int q = warp & 3;                                   // TMEM lane quarter this warp may access
+        const int half = (warp - TC_EPI_WARP0) >> 2;              // 0 or 1
         const int r_in_tile = q * 32 + lane;
-        uint32_t ti = 0;
+        const int mt_e = (MT == 1) ? 0 : half;                    // M-tile served by this thread
+        constexpr int CPT = tc_cols_per_thread(BN, MT);           // columns served by this thread
+        const int col_lo = (MT == 1) ? half * CPT : 0;
+        const int epi_idx = (warp - TC_EPI_WARP0) * 32 + lane;
+        float* slot_ptr = reinterpret_cast<float*>(staging + epi_idx * TC_SLOT_BYTES);
         bool alive = true;
-        for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++ti) {
-            const uint32_t buf = ti & 1, aph = (ti >> 1) & 1;
-            if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 8);
-            if (!mbar_wait(accf_bar(buf), aph, abort_flag, 4)) { alive = false; break; }
-            if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 9);
+        for (int ui = 0; ui < n_my_units && alive; ++ui) {
+            const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
+            if (epi_idx == 0) TC_TRACE(ui, 8);
+            if (!mbar_wait(acc_full(buf), aph, abort_flag, 4)) { alive = false; break; }
+            if (epi_idx == 0) TC_TRACE(ui, 9);
             tc_fence_after();
-            const int mt = tile / n_tiles, nt = tile % n_tiles;
-            const int row = mt * TC_BM + r_in_tile;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            const int unit = u0 + ui * ctas_per_nt;
+            const int row = (unit * MT + mt_e) * TC_BM + r_in_tile;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (buf * MT + mt_e) * BN;
 
             if constexpr (EPI == EPI_LINEAR) {
                 const TcLinearEpi& e = ep;
-                const bool vec = ((e.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(e.y) & 15) == 0) &&
-                                 (e.residual == nullptr || (((e.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(e.residual) & 15) == 0)));
-                constexpr int NCH = (BN + 31) / 32;
+                constexpr int PASS = CPT > 32 ? 32 : CPT;        // columns per staging pass
+                constexpr int LPR = PASS / 4;                    // lanes per row in the store phase (float4 each)
+                constexpr int RPI = 32 / LPR;                    // rows per store instruction
+                const uint8_t* warp_stage = staging + (warp - TC_EPI_WARP0) * 32 * TC_SLOT_BYTES;
+                const int tile_row0 = (unit * MT + mt_e) * TC_BM + q * 32;
 #pragma unroll 1
-                for (int ch = half; ch < NCH; ch += 2) {
-                    const int c0 = ch * 32;
-                    float v[32];
-                    if (BN - c0 >= 32) { tc_ld32(taddr + c0, v); }
-                    else { tc_ld16(taddr + c0, v);
+                for (int c0 = col_lo; c0 < col_lo + CPT; c0 += PASS) {
+                    // phase 1: each thread finishes its own row (bias, activation) into its padded staging slot
+#pragma unroll 1
+                    for (int cc = 0; cc < PASS; cc += 16) {
+                        float v[16];
+                        tc_ld16(taddr + c0 + cc, v);
+                        if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 16 + cc / 16);
+                        const int colb = nt * BN + c0 + cc;
 #pragma unroll
-                        for (int j = 16; j < 32; ++j) v[j] = 0.0f; }
-                    if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 11 + (ch >> 1) * 2);
-                    if (row < rows) {
-                        const int colb = nt * BN + c0;
-                        float* yp = e.y + (int64_t)row * e.ldc + colb;
-                        const float* rp = e.residual ? e.residual + (int64_t)row * e.ldr + colb : nullptr;
-#pragma unroll
-                        for (int j4 = 0; j4 < 8; ++j4) {
+                        for (int j4 = 0; j4 < 4; ++j4) {
                             const int col = colb + 4 * j4;
-                            if (c0 + 4 * j4 >= BN || col >= e.N) continue;
-                            if (vec && col + 3 < e.N) {
-                                float4 b = e.bias ? __ldg(reinterpret_cast<const float4*>(e.bias + col)) : make_float4(0, 0, 0, 0);
-                                float4 o;
-                                o.x = apply_act(v[4 * j4] + b.x, e.act); o.y = apply_act(v[4 * j4 + 1] + b.y, e.act);
-                                o.z = apply_act(v[4 * j4 + 2] + b.z, e.act); o.w = apply_act(v[4 * j4 + 3] + b.w, e.act);
-                                if (rp) {
-                                    const float4 r = __ldg(reinterpret_cast<const float4*>(rp + 4 * j4));
+                            float4 o = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+                            if (col < e.N) {
+                                const float4 b = *reinterpret_cast<const float4*>(consts + c0 + cc + 4 * j4);
+                                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                                o.x = apply_act(o.x, e.act); o.y = apply_act(o.y, e.act);
+                                o.z = apply_act(o.z, e.act); o.w = apply_act(o.w, e.act);
+                            }
+                            *reinterpret_cast<float4*>(slot_ptr + cc + 4 * j4) = o;
+                        }
+                        if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 20 + cc / 16);
+                    }
+                    __syncwarp();
+                    if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 12);
+                    // phase 2: the warp writes its 32 rows with full-line coalesced float4 stores (+ residual)
+                    const int col = nt * BN + c0 + (lane % LPR) * 4;
+                    if (col < e.N) {
+#pragma unroll 4
+                        for (int i = 0; i < 32 / RPI; ++i) {
+                            const int rr = i * RPI + lane / LPR;
+                            const int orow = tile_row0 + rr;
+                            if (orow < rows) {
+                                float4 o = *reinterpret_cast<const float4*>(warp_stage + rr * TC_SLOT_BYTES + (lane % LPR) * 16);
+                                if (e.residual) {
+                                    const float4 r = __ldg(reinterpret_cast<const float4*>(e.residual + (int64_t)orow * e.ldr + col));
                                     o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
                                 }
-                                *reinterpret_cast<float4*>(yp + 4 * j4) = o;
-                            } else {
-#pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    if (col + k < e.N) {
-                                        float o = apply_act(v[4 * j4 + k] + (e.bias ? __ldg(e.bias + col + k) : 0.0f), e.act);
-                                        if (rp) o += __ldg(rp + 4 * j4 + k);
-                                        yp[4 * j4 + k] = o;
-                                    }
-                                }
+                                *reinterpret_cast<float4*>(e.y + (int64_t)orow * e.ldc + col) = o;
                             }
                         }
                     }
-                    if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 12 + (ch >> 1) * 2);
+                    __syncwarp();
+                    if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 13);
                 }
             } else if constexpr (EPI == EPI_PROJ) {
                 const TcProjEpi& e = ep;
@@ -391,17 +485,13 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 const bool rok = row < rows;
                 const int b = rok ? row / e.S : 0, s_ = rok ? row - b * e.S : 0;
                 float* out = e.out[p];
-                const float* bias = e.bias[p];
                 const float* lnw = e.lnw[p];
-                const float* lnb = e.lnb[p];
 #pragma unroll 1
                 for (int hd = half; hd < 4; hd += 2) {           // one head = 32 columns = one TMEM load
                     float v[32];
                     tc_ld32(taddr + hd * 32, v);
-                    if (bias) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] += __ldg(bias + hd * 32 + j);
-                    }
+                    for (int j = 0; j < 32; ++j) v[j] += consts[hd * 32 + j];
                     if (lnw != nullptr) {
                         float s = 0.0f;
 #pragma unroll
@@ -413,7 +503,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                         const float inv = 1.0f / sqrtf(qq * (1.0f / 32.0f) + e.eps);
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            v[j] = (v[j] - mu) * inv * __ldg(lnw + hd * 32 + j) + __ldg(lnb + hd * 32 + j);
+                            v[j] = (v[j] - mu) * inv * consts[128 + hd * 32 + j] + consts[256 + hd * 32 + j];
                     }
                     if (rok) {
                         float* o = out + (((int64_t)b * e.H + hd) * dpk + e.d_pos) * e.S + s_;
@@ -425,8 +515,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 }
             } else {
                 const TcHeadEpi& e = ep;
-                float* part = reinterpret_cast<float*>(smem + ST * L::STAGE_BYTES);   // [2][128] partial row sums
-                const float4* cb = reinterpret_cast<const float4*>(part + 256);              // b1[128] then w2[128]
+                float* part = reinterpret_cast<float*>(staging);                 // [2][128] partial row sums
+                const float4* cb = reinterpret_cast<const float4*>(consts);      // b1[128] then w2[128]
                 float acc = 0.0f;
 #pragma unroll 1
                 for (int ch = half; ch < BN / 32; ch += 2) {
@@ -448,10 +538,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     else if (e.act == SPGT_ACT_SILU2) dot([](float x) { return silu_f(silu_f(x)); });
                     else dot([](float x) { return x; });
                 }
-                if (half == 1) part[(ti & 1) * 128 + r_in_tile] = acc;
+                if (half == 1) part[(ui & 1) * 128 + r_in_tile] = acc;
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");   // epilogue warps only
                 if (half == 0 && row < rows) {
-                    acc += part[(ti & 1) * 128 + r_in_tile];
+                    acc += part[(ui & 1) * 128 + r_in_tile];
                     const int rem = row % (e.Hh * e.Ww);
                     const float sc = e.scale_map ? __ldg(e.scale_map + rem) : e.scale;
                     const float sh = e.shift_map ? __ldg(e.shift_map + rem) : e.shift;
@@ -464,8 +554,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 }
             }
             tc_fence_before();
-            mbar_arrive(acce_bar(buf));
-            if (tid == TC_EPI_WARP0 * 32) TC_TRACE(ti, 10);
+            mbar_arrive(acc_empty(buf));
+            if (epi_idx == 0) TC_TRACE(ui, 10);
         }
     }
     // teardown: everyone meets, then the allocating warp frees the tensor memory
@@ -473,7 +563,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     __syncthreads();
     if (warp == TC_MMA_WARP) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
 }
 
@@ -498,32 +588,34 @@ __global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, i
     }
 }
 
-static int tc_bn_for(int N) { return N <= 32 ? 32 : (N <= 48 ? 48 : (N <= 64 ? 64 : 128)); }
+static int tc_bn_for(int N) { return N <= 32 ? 32 : (N <= 64 ? 64 : 128); }
 
-template <int BN, class Loader, int EPI, class EpiParams>
+template <int BN, int MT, class Loader, int EPI, class EpiParams>
 static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_tiles, const EpiParams& ep, cudaStream_t st) {
     static bool done = false;
-    auto kern = tc_gemm_kernel<BN, Loader, EPI, EpiParams>;
+    auto kern = tc_gemm_kernel<BN, MT, Loader, EPI, EpiParams>;
     if (!done) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem<BN>::BYTES) != cudaSuccess) return launch_status();
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcCfg<BN, MT>::BYTES) != cudaSuccess) return launch_status();
         done = true;
     }
-    const int m_tiles = ceil_div(rows, TC_BM);
-    const int64_t tiles = (int64_t)m_tiles * n_tiles;
-    const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
-    kern<<<grid, TC_THREADS, TcSmem<BN>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_tiles, ep);
+    const int m_units = ceil_div(rows, TC_BM * MT);
+    int per_nt = num_sms() / n_tiles;                 // CTAs per column tile
+    if (per_nt < 1) per_nt = 1;
+    if (per_nt > m_units) per_nt = m_units;
+    const int grid = per_nt * n_tiles;
+    kern<<<grid, TC_THREADS, TcCfg<BN, MT>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
     return launch_status();
 }
 
 template <class Loader>
-static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int rows, const TcLinearEpi& ep, cudaStream_t st) {
+static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int rows, const TcLinearEpi& ep, bool long_k, cudaStream_t st) {
     const int bn = tc_bn_for(N), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
     const int n_tiles = npad / bn;
+    if (long_k && bn == 128) return tc_launch<128, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     switch (bn) {
-        case 32: return tc_launch<32, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
-        case 48: return tc_launch<48, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
-        case 64: return tc_launch<64, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
-        default: return tc_launch<128, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+        case 32: return tc_launch<32, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+        case 64: return tc_launch<64, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+        default: return tc_launch<128, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     }
 }
 
@@ -550,8 +642,8 @@ extern "C" int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, 
 }
 
 #ifdef SPGT_TC_TRACE
-extern "C" int spgt_tc_trace_read(long long* host_out) {   // 64 tiles x 16 slots of clock64() values of CTA 0
-    return cudaMemcpyFromSymbol(host_out, g_tc_trace, sizeof(long long) * 64 * 16) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
+extern "C" int spgt_tc_trace_read(long long* host_out) {   // 64 units x 16 slots of clock64() values of CTA 0
+    return cudaMemcpyFromSymbol(host_out, g_tc_trace, sizeof(long long) * 64 * 32) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
 }
 #endif
 
@@ -565,12 +657,13 @@ extern "C" int spgt_linear_tc_fwd(const float* x, int lda, const void* wprep, co
                                   int ldr, float* y, int ldc, int rows, int K, int N, int act, spgt_stream_t stream) {
     if (!x || !wprep || !y) return SPGT_ERR_NULL;
     if (rows <= 0 || K <= 0 || N <= 0 || lda < K || ldc < N || (residual && ldr < N)) return SPGT_ERR_SHAPE;
-    if ((lda & 3) || (K & 3) || act < 0 || act > 3) return SPGT_ERR_SHAPE;
-    if (!aligned16(x) || !aligned16(wprep) || !aligned16(y)) return SPGT_ERR_ALIGN;
+    if ((lda & 3) || (K & 3) || (N & 3) || (ldc & 3) || (residual && (ldr & 3)) || act < 0 || act > 3) return SPGT_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(wprep) || !aligned16(y) || (residual && !aligned16(residual)) || (bias && !aligned16(bias)))
+        return SPGT_ERR_ALIGN;
     TcDense ld;
     ld.x = x; ld.lda = lda; ld.rows = rows; ld.K = K;
     TcLinearEpi ep{bias, residual, ldr, y, ldc, N, act};
-    return tc_dispatch_linear(ld, (const float*)wprep, K, N, rows, ep, (cudaStream_t)stream);
+    return tc_dispatch_linear(ld, (const float*)wprep, K, N, rows, ep, K > 256, (cudaStream_t)stream);
 }
 
 extern "C" int spgt_conv3x3_tc_fwd(const float* x, int cin_pitch, int cin_off, int Cin, const void* wprep, const float* bias,
@@ -579,14 +672,14 @@ extern "C" int spgt_conv3x3_tc_fwd(const float* x, int cin_pitch, int cin_off, i
     if (!x || !wprep || !y) return SPGT_ERR_NULL;
     if (B <= 0 || Hh <= 0 || Ww <= 0 || Cin <= 0 || Cout <= 0 || cin_off < 0 || cout_off < 0) return SPGT_ERR_SHAPE;
     if (cin_off + Cin > cin_pitch || cout_off + Cout > cout_pitch || act < 0 || act > 3) return SPGT_ERR_SHAPE;
-    if ((Cin & 3) || (cin_off & 3) || (cin_pitch & 3)) return SPGT_ERR_SHAPE;
+    if ((Cin & 3) || (cin_off & 3) || (cin_pitch & 3) || (Cout & 3) || (cout_off & 3) || (cout_pitch & 3)) return SPGT_ERR_SHAPE;
     const int64_t rows64 = (int64_t)B * Hh * Ww;
     if (rows64 > 0x7fffffffLL / 4 || rows64 * cin_pitch > 0x7fffffffLL * 4) return SPGT_ERR_SHAPE;
-    if (!aligned16(x) || !aligned16(wprep) || !aligned16(y)) return SPGT_ERR_ALIGN;
+    if (!aligned16(x) || !aligned16(wprep) || !aligned16(y) || (bias && !aligned16(bias))) return SPGT_ERR_ALIGN;
     TcConv ld;
     ld.x = x; ld.cin_pitch = cin_pitch; ld.cin_off = cin_off; ld.Cin = Cin; ld.Hh = Hh; ld.Ww = Ww; ld.rows = (int)rows64; ld.K = 9 * Cin;
     TcLinearEpi ep{bias, nullptr, 0, y + cout_off, cout_pitch, Cout, act};
-    return tc_dispatch_linear(ld, (const float*)wprep, 9 * Cin, Cout, (int)rows64, ep, (cudaStream_t)stream);
+    return tc_dispatch_linear(ld, (const float*)wprep, 9 * Cin, Cout, (int)rows64, ep, true, (cudaStream_t)stream);
 }
 
 extern "C" int spgt_projpos_qkv_tc_fwd(const float* x, const void* wprep_qkv, const float* bq, const float* bk, const float* bv,
@@ -606,7 +699,7 @@ extern "C" int spgt_projpos_qkv_tc_fwd(const float* x, const void* wprep_qkv, co
     ep.lnw[1] = lnwk; ep.lnb[1] = lnbk; ep.lnw[2] = lnwv; ep.lnb[2] = lnbv;
     ep.out[0] = q; ep.out[1] = k; ep.out[2] = v; ep.pos = pos; ep.eps = eps; ep.S = S; ep.H = H; ep.d_pos = d_pos;
     // wprep_qkv is prepared from the [128, 384] concatenation of Wq | Wk | Wv: three column tiles of 128
-    return tc_launch<128, TcDense, EPI_PROJ, TcProjEpi>(ld, (const float*)wprep_qkv, 128, (int)rows64, 3, ep, (cudaStream_t)stream);
+    return tc_launch<128, 1, TcDense, EPI_PROJ, TcProjEpi>(ld, (const float*)wprep_qkv, 128, (int)rows64, 3, ep, (cudaStream_t)stream);
 }
 
 extern "C" int spgt_decoder_head_tc_fwd(const float* x, const void* w1prep, const float* b1, const float* w2, float b2,
@@ -622,5 +715,5 @@ extern "C" int spgt_decoder_head_tc_fwd(const float* x, const void* w1prep, cons
     ld.x = x; ld.lda = K; ld.rows = (int)rows64; ld.K = K;
     TcHeadEpi ep{b1, w2, b2, scale, shift, scale_map, shift_map, dirichlet, Hh, Ww, act, out};
     const int kpad = ceil_div(K, TC_BK) * TC_BK;
-    return tc_launch<128, TcDense, EPI_HEAD, TcHeadEpi>(ld, (const float*)w1prep, kpad, (int)rows64, 1, ep, (cudaStream_t)stream);
+    return tc_launch<128, 1, TcDense, EPI_HEAD, TcHeadEpi>(ld, (const float*)w1prep, kpad, (int)rows64, 1, ep, (cudaStream_t)stream);
 }
