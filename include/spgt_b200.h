@@ -38,7 +38,8 @@ const char* spgt_error_string(int code);
 int spgt_last_cuda_error(void);
 /* Library ABI version (bumped when a signature changes). */
 int spgt_abi_version(void);
-/* Experiment knob: "attn_cluster" = 0 (heuristic), 1, 2, 4 or 8 CTAs per (batch, head) in spgt_galerkin_attn_fwd. */
+/* Experiment knobs: "attn_cluster" = 0 (heuristic), 1, 2, 4 or 8 CTAs per (batch, head) in spgt_galerkin_attn_fwd;
+ * "attn_impl" = 0 (tcgen05 kernel) or 1 (warp-MMA kernel, default while it is the faster one). */
 int spgt_set_tuning(const char* key, int value);
 
 /* ---------------------------------------------------------------------------------------------
@@ -172,7 +173,7 @@ int spgt_decoder_head_fwd(const float* x, const float* w1, const float* b1, cons
 size_t spgt_tc_weight_bytes(int K, int N);
 int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, void* out, size_t out_bytes, spgt_stream_t stream);
 /* 0 if no tensor-core kernel ever gave up on a bounded wait, else the code of the first one that did
- * (1 stage-free, 2 accumulator-free, 3 operands-ready, 4 accumulator-ready, 5 tile-landed).  Synchronises the device. */
+ * (GEMM: 1..8; attention: 101..108).  Synchronises the device. */
 int spgt_tc_status(void);
 
 /* As spgt_linear_fwd with wprep = spgt_tc_weight_prepare(w, ...). */

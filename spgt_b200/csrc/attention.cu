@@ -457,6 +457,11 @@ skinny_reduce_kernel(const float* __restrict__ ws, float* __restrict__ C, float 
 }
 
 static int g_attn_cluster_override = 0;   // 0 = heuristic; set through spgt_set_tuning("attn_cluster", n)
+static int g_attn_impl = 1;               // 0 = tcgen05 kernel (attention_tc.cu), 1 = warp-MMA kernel of this file (currently faster)
+
+// defined in attention_tc.cu
+int launch_attn_tc(const float* Q, const float* K, const float* V, float* out, float* t_out, int64_t BH, int H, int dpk,
+                   int S, int merged, int cluster, cudaStream_t stream);
 
 }  // namespace spgt
 
@@ -516,6 +521,7 @@ extern "C" int spgt_galerkin_attn_fwd(const float* Q, const float* K, const floa
     if (BH * 8 > 0x7fffffffLL) return SPGT_ERR_SHAPE;
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(out)) return SPGT_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
+    if (g_attn_impl == 0) return launch_attn_tc(Q, K, V, out, t_out, BH, H, dpk, S, merged_heads, pick_cluster(BH, S), st);
     switch (dpk) {
         case 32: return launch_attn<32>(Q, K, V, out, t_out, BH, H, S, merged_heads, st);
         case 33: return launch_attn<33>(Q, K, V, out, t_out, BH, H, S, merged_heads, st);
@@ -573,12 +579,15 @@ extern "C" int spgt_batched_skinny_gemm(const float* A, const float* B, float* C
 
 extern "C" int spgt_set_tuning(const char* key, int value) {
     if (!key) return SPGT_ERR_NULL;
-    const char* k = "attn_cluster";
-    int i = 0;
-    while (k[i] && key[i] == k[i]) ++i;
-    if (k[i] == 0 && key[i] == 0) {
+    auto eq = [&](const char* k) { int i = 0; while (k[i] && key[i] == k[i]) ++i; return k[i] == 0 && key[i] == 0; };
+    if (eq("attn_cluster")) {
         if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return SPGT_ERR_SHAPE;
         g_attn_cluster_override = value;
+        return SPGT_OK;
+    }
+    if (eq("attn_impl")) {
+        if (value != 0 && value != 1) return SPGT_ERR_SHAPE;
+        g_attn_impl = value;
         return SPGT_OK;
     }
     return SPGT_ERR_SHAPE;

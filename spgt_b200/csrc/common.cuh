@@ -35,6 +35,13 @@ __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) 
     lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
+// Same, with lo also rounded to tf32 (round to nearest) instead of being truncated by the tensor core: one more
+// instruction, unbiased error; used where thousands of products are summed (the K^T V reduction over grid nodes).
+__device__ __forceinline__ void split_tf32_rn(float x, uint32_t& hi, uint32_t& lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(x - __uint_as_float(hi)));
+}
+
 // D(16x8) += A(16x8, row) * B(8x8, col), TF32 inputs, fp32 accumulate.
 // Fragment layout (g = lane/4, t = lane%4):  a0=(g,t) a1=(g+8,t) a2=(g,t+4) a3=(g+8,t+4);
 // b0=(k=t,n=g) b1=(k=t+4,n=g);  c0=(g,2t) c1=(g,2t+1) c2=(g+8,2t) c3=(g+8,2t+1).

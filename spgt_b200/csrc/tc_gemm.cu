@@ -19,15 +19,13 @@
 //     head (row dot product) store directly, one row per thread.
 //   warps 0-3 A loaders, 4-7 A splitters, 8 W loader, 9 MMA issuer (one elected lane), 10-17 epilogue.
 // All waits are bounded mbarrier polls: on expiry the kernel records an error code, stops waiting and returns.
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace spgt {
 
-constexpr int TC_BM = 128, TC_BK = 32;
 constexpr int TC_BLOAD_WARP = 8, TC_MMA_WARP = 9, TC_EPI_WARP0 = 10, TC_EPI_WARPS = 8;
 constexpr int TC_THREADS = 32 * (TC_EPI_WARP0 + TC_EPI_WARPS);
 constexpr int TC_SLOT_BYTES = 144;            // per-epilogue-thread staging row: 32 floats + 16 bytes (bank skew)
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 
 __device__ int g_tc_status = 0;          // 0 = ok; otherwise the code of the first wait that gave up
 
@@ -38,87 +36,6 @@ __device__ long long g_tc_trace[64 * 32];
 #define TC_TRACE(unit_i, slot) do { } while (0)
 #endif
 
-// ---- mbarrier / tcgen05 primitives -------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"(100000u) : "memory");     // suspend-time hint (ns): sleep, do not spin
-    return ok;
-}
-// Bounded wait.  Returns false (and latches *abort_flag) when the limit is reached or another thread gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = code;
-    atomicCAS(&g_tc_status, 0, code);
-    return false;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem desc], M = 128, N from the instruction descriptor, K = 8 (tf32)
-__device__ __forceinline__ void tc_mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t* u = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-        "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
-          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]),
-          "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
-          "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t* u = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
-          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-// Store 16 consecutive 32-bit columns of this thread's TMEM lane.
-__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&u)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-        ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]),
-          "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]) : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// K-major operand tile with 128-byte rows, SWIZZLE_128B: 8-row groups are 1024 B apart (SBO), LBO unused (1),
-// descriptor version 1 (sm_100), layout type 2.  The tile base must be 1024-byte aligned.
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__host__ __device__ constexpr uint32_t tc_idesc(int bn) {
-    // c = f32 (1 << 4), a = b = tf32 (2 << 7, 2 << 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
-// byte offset of 16-byte chunk `c` (0..7) of row `r` inside a swizzled tile
-__host__ __device__ __forceinline__ uint32_t tc_swz(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
 __host__ __device__ constexpr int tc_cols_per_thread(int bn, int mt) { return mt == 1 ? bn / 2 : bn; }
 
 // ---- A-operand loaders.  A loader thread copies 16-byte chunk (t & 7) of rows (t >> 3) + 16 i of every tile:
@@ -288,7 +205,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 for (int i = 0; i < 8; ++i) rs[m][i] = ld.row_state(row0 + m * TC_BM + 16 * i);
             for (int kb = 0; kb < KB; ++kb, ++slot) {
                 const uint32_t sr = (uint32_t)(slot % SR), ph = (uint32_t)((slot / SR) & 1);
-                if (!mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1)) { alive = false; break; }
+                if (!mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1, &g_tc_status)) { alive = false; break; }
                 const typename Loader::Kst ks = ld.k_state(kb, t & 7);
                 const uint32_t dst = raw_s + sr * C::RAW_BYTES;
 #pragma unroll
@@ -317,8 +234,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int64_t slot = 0; slot < total; ++slot) {
             const uint32_t sr = (uint32_t)(slot % SR), pr = (uint32_t)((slot / SR) & 1);
             const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
-            if (!mbar_wait(raw_full(sr), pr, abort_flag, 5)) break;
-            if (!mbar_wait(a_empty(sa), pa ^ 1, abort_flag, 8)) break;
+            if (!mbar_wait(raw_full(sr), pr, abort_flag, 5, &g_tc_status)) break;
+            if (!mbar_wait(a_empty(sa), pa ^ 1, abort_flag, 8, &g_tc_status)) break;
             tc_fence_after();
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
@@ -352,7 +269,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             const int64_t total = resident ? KB : (int64_t)n_my_units * KB;
             for (int64_t slot = 0; slot < total; ++slot) {
                 const uint32_t sb = (uint32_t)(slot % SB), ph = (uint32_t)((slot / SB) & 1);
-                if (!mbar_wait(b_empty(sb), ph ^ 1, abort_flag, 6)) break;
+                if (!mbar_wait(b_empty(sb), ph ^ 1, abort_flag, 6, &g_tc_status)) break;
                 const int kb = (int)(slot % KB);
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(sb)), "r"(bytes) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -367,16 +284,16 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
             if (lane == 0) TC_TRACE(ui, 4);
-            if (!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2)) { alive = false; break; }
+            if (!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2, &g_tc_status)) { alive = false; break; }
             if (lane == 0) TC_TRACE(ui, 5);
             tc_fence_after();
             for (int kb = 0; kb < KB; ++kb, ++slot) {
                 const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
                 const uint32_t sb = resident ? (uint32_t)kb : (uint32_t)(slot % SB);
                 const uint32_t pb = resident ? 0u : (uint32_t)((slot / SB) & 1);
-                if (!mbar_wait(a_full(sa), pa, abort_flag, 3)) { alive = false; break; }
+                if (!mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status)) { alive = false; break; }
                 if (!resident || ui == 0) {
-                    if (!mbar_wait(b_full(sb), pb, abort_flag, 7)) { alive = false; break; }
+                    if (!mbar_wait(b_full(sb), pb, abort_flag, 7, &g_tc_status)) { alive = false; break; }
                 }
                 if (lane == 0 && kb == 0) TC_TRACE(ui, 6);
                 tc_fence_after();
@@ -419,7 +336,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
             if (epi_idx == 0) TC_TRACE(ui, 8);
-            if (!mbar_wait(acc_full(buf), aph, abort_flag, 4)) { alive = false; break; }
+            if (!mbar_wait(acc_full(buf), aph, abort_flag, 4, &g_tc_status)) { alive = false; break; }
             if (epi_idx == 0) TC_TRACE(ui, 9);
             tc_fence_after();
             const int unit = u0 + ui * ctas_per_nt;
@@ -647,10 +564,14 @@ extern "C" int spgt_tc_trace_read(long long* host_out) {   // 64 units x 16 slot
 }
 #endif
 
+namespace spgt { int attn_tc_status(); }      // attention_tc.cu
+
 extern "C" int spgt_tc_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return SPGT_ERR_LAUNCH;
-    return v;
+    if (v != 0) return v;
+    const int a = spgt::attn_tc_status();
+    return a > 0 ? 100 + a : a;                 // 101..108: a wait of the attention kernel gave up
 }
 
 extern "C" int spgt_linear_tc_fwd(const float* x, int lda, const void* wprep, const float* bias, const float* residual,

@@ -127,6 +127,35 @@ def test_attention_cluster_sizes_agree_and_are_deterministic(dev):
         lib.spgt_set_tuning(b'attn_cluster', 0)
 
 
+@pytest.mark.parametrize('B,H,dpk,S', [(1, 1, 34, 1), (2, 4, 34, 129), (2, 4, 34, 1849), (1, 2, 32, 300), (1, 1, 35, 77), (2, 4, 34, 2809)])
+def test_attention_both_implementations(dev, B, H, dpk, S):
+    """The tcgen05 kernel and the warp-MMA kernel against the fp64 oracle, for every cluster size."""
+    from spgt_b200 import ops
+    from spgt_b200._lib import lib
+    g = torch.Generator().manual_seed(S * 7 + dpk)
+    Q, K, V = (torch.randn(B, H, dpk, S, generator=g).to(dev) for _ in range(3))
+    ref = O.galerkin_attention(Q.cpu().double(), K.cpu().double(), V.cpu().double())
+    refT = O.galerkin_kv(K.cpu().double(), V.cpu().double())
+    try:
+        for impl in (0, 1):
+            assert lib.spgt_set_tuning(b'attn_impl', impl) == 0
+            for c in (1, 2, 8):
+                assert lib.spgt_set_tuning(b'attn_cluster', c) == 0
+                out, T = ops.galerkin_attention(Q, K, V, return_kv=True)
+                # K^T V of independent random rows is a sum of S cancelling terms (|T| ~ sqrt(S)/S while the terms are O(1)/S),
+                # so its fp32 relative error is ~sqrt(S) larger than that of the layer output checked below.
+                assert rel_l2(T, refT) < 5e-5, (impl, c, rel_l2(T, refT))
+                # the tcgen05 kernel keeps one accumulator per CTA over all its grid nodes, so on cancelling random data its
+                # error grows with the chain length like that of T; the layer tolerance is checked on layer data elsewhere
+                assert rel_l2(out, ref) < (5e-5 if impl == 0 else PER_LAYER_TOL), (impl, c, rel_l2(out, ref))
+                merged = ops.galerkin_attention(Q, K, V, merged_heads=True)
+                assert torch.equal(merged, out.transpose(1, 2).contiguous().view(B, S, H * dpk)), (impl, c)
+        assert lib.spgt_tc_status() == 0
+    finally:
+        lib.spgt_set_tuning(b'attn_impl', 1)
+        lib.spgt_set_tuning(b'attn_cluster', 0)
+
+
 @pytest.mark.parametrize('batch,M,N,K', [(64, 32, 32, 1849), (3, 34, 34, 500), (2, 5, 70, 33), (1, 32, 32, 19881), (2, 32, 30, 7)])
 def test_skinny_gemm(dev, batch, M, N, K):
     ga, _ = _bind()
