@@ -24,6 +24,7 @@ extern "C" {
 #define SPGT_ERR_ALIGN (-3)       /* a base pointer is not 16-byte aligned */
 #define SPGT_ERR_WORKSPACE (-4)   /* workspace missing or smaller than the *_workspace_bytes() answer */
 #define SPGT_ERR_LAUNCH (-5)      /* the CUDA runtime refused the launch; see spgt_last_cuda_error() */
+#define SPGT_ERR_TOO_LARGE (-6)   /* the problem exceeds the fixed scratch of a *_noalloc entry point */
 
 #define SPGT_ACT_NONE 0
 #define SPGT_ACT_RELU 1
@@ -88,6 +89,21 @@ int spgt_galerkin_attn_fwd(const float* Q, const float* K, const float* V, float
 size_t spgt_skinny_gemm_workspace_bytes(int M, int N, int K, int batch);
 int spgt_batched_skinny_gemm(const float* A, const float* B, float* C, float alpha, int M, int N, int K, int batch,
                              void* workspace, size_t workspace_bytes, spgt_stream_t stream);
+
+/* The same product for callers that can neither pass a workspace nor allocate one (plugin callbacks, real-time
+ * loops, hosts whose device allocator is out of reach at call time).  No counterpart in the reference, whose
+ * binding allocates its split-K buffer through torch on every call.  The partial tiles live in a fixed
+ * 8 MiB array inside the library image (one per device); the call allocates nothing.
+ *  - Limit: spgt_skinny_gemm_workspace_bytes(M,N,K,batch) must not exceed spgt_skinny_gemm_noalloc_max_bytes();
+ *    otherwise SPGT_ERR_TOO_LARGE is returned and nothing is launched.
+ *  - The first call on each device (that device current) looks up the array's device address; make it before any
+ *    stream capture.  Later calls only launch kernels.
+ *  - Nothing has to be zeroed: every partial tile that is read is written earlier in the same call.
+ *  - One array per device: calls that may overlap on a device (different streams) race; keep them on one stream
+ *    or order them with events. */
+size_t spgt_skinny_gemm_noalloc_max_bytes(void);
+int spgt_batched_skinny_gemm_noalloc(const float* A, const float* B, float* C, float alpha, int M, int N, int K,
+                                     int batch, spgt_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Data-movement ops (reference: extension/bind/datamove.{py,cu}, extension/native/datamove.cu)

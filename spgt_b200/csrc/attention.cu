@@ -577,6 +577,70 @@ extern "C" int spgt_batched_skinny_gemm(const float* A, const float* B, float* C
     return launch_status();
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Batched skinny GEMM for callers that cannot hand over a workspace and must not allocate.
+//
+// Who needs this: a host that drives the library from inside a plugin callback, a real-time loop or a memory
+// pool it does not own often has no way to obtain device memory at call time (its allocator may take a lock, may
+// synchronise the device, or may simply be out of reach from the calling layer), and no place to keep a buffer
+// between calls.  spgt_batched_skinny_gemm() asks such a caller for a workspace it cannot provide.  The entry
+// point below has the same arithmetic, but takes its split-K partial tiles from a fixed array that is part of
+// the loaded library image on every device.  It never calls cudaMalloc, cudaFree or any other allocating routine.
+//
+// Limit: the partial tiles must fit SPGT_SKINNY_NOALLOC_BYTES (8 MiB).  Larger problems are refused with
+// SPGT_ERR_TOO_LARGE; nothing is launched in that case.  spgt_skinny_gemm_workspace_bytes() gives the size a
+// problem needs, spgt_skinny_gemm_noalloc_max_bytes() the limit.
+//
+// Set-up: the first call on a device (with that device current) looks up the device address of the array once
+// and caches it.  That lookup is a runtime query, so make one call on every device you use before you start
+// capturing a stream; later calls only launch the two kernels.
+//
+// Initial contents: nothing has to start at zero.  Pass 1 writes every element of every partial tile that pass 2
+// reads, in the same call, so stale contents of an earlier call are never observed and no clearing kernel runs.
+//
+// Concurrency: there is one array per device.  Two calls whose kernels can overlap on the same device (different
+// streams, or different host threads on different streams) would write the same partial tiles and race; issue
+// the calls of one device on one stream, or order them with events.
+// ------------------------------------------------------------------------------------------------------------
+constexpr size_t SKINNY_NOALLOC_FLOATS = (size_t)2 * 1024 * 1024;                 // 8 MiB
+static __device__ __align__(256) float g_skinny_noalloc_scratch[SKINNY_NOALLOC_FLOATS];
+
+constexpr int SKINNY_MAX_DEVICES = 64;
+static float* g_skinny_noalloc_ptr[SKINNY_MAX_DEVICES] = {};   // device address of the array, per device; 0 = not looked up
+
+extern "C" size_t spgt_skinny_gemm_noalloc_max_bytes(void) { return SKINNY_NOALLOC_FLOATS * sizeof(float); }
+
+extern "C" int spgt_batched_skinny_gemm_noalloc(const float* A, const float* B, float* C, float alpha, int M, int N,
+                                                int K, int batch, spgt_stream_t stream) {
+    if (!A || !B || !C) return SPGT_ERR_NULL;
+    if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return SPGT_ERR_SHAPE;
+    if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return SPGT_ERR_ALIGN;
+    const int tiles_n = ceil_div(N, 32), tiles = ceil_div(M, 32) * tiles_n;
+    const int splits = skinny_splits(M, N, K, batch);
+    const int64_t blocks = (int64_t)tiles * splits * batch;
+    if (blocks > 0x7fffffffLL) return SPGT_ERR_SHAPE;
+    if ((size_t)blocks * 1024 > SKINNY_NOALLOC_FLOATS) return SPGT_ERR_TOO_LARGE;
+
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return launch_status();
+    if (dev < 0 || dev >= SKINNY_MAX_DEVICES) return SPGT_ERR_SHAPE;
+    float* scratch = g_skinny_noalloc_ptr[dev];
+    const size_t smem = (size_t)SK_WARPS * SK_WARP_FLOATS * sizeof(float);
+    if (!scratch) {   // once per device: address of this device's copy of the array, and the kernel's shared-memory opt-in
+        cudaError_t e = cudaGetSymbolAddress((void**)&scratch, g_skinny_noalloc_scratch);
+        if (e != cudaSuccess || !scratch) { g_last_cuda_error = (int)e; (void)cudaGetLastError(); return SPGT_ERR_LAUNCH; }
+        e = cudaFuncSetAttribute(skinny_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { g_last_cuda_error = (int)e; (void)cudaGetLastError(); return SPGT_ERR_LAUNCH; }
+        g_skinny_noalloc_ptr[dev] = scratch;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    const int vecB = (N % 4 == 0) ? 1 : 0;
+    skinny_splitk_kernel<<<(unsigned)blocks, SK_WARPS * 32, smem, st>>>(A, B, scratch, M, N, K, tiles_n, tiles, splits, vecB);
+    if (int e = launch_status()) return e;
+    skinny_reduce_kernel<<<(unsigned)((int64_t)tiles * batch), 256, 0, st>>>(scratch, C, alpha, M, N, tiles_n, tiles, splits);
+    return launch_status();
+}
+
 extern "C" int spgt_set_tuning(const char* key, int value) {
     if (!key) return SPGT_ERR_NULL;
     auto eq = [&](const char* k) { int i = 0; while (k[i] && key[i] == k[i]) ++i; return k[i] == 0 && key[i] == 0; };
