@@ -14,7 +14,7 @@
 //            memory (deterministic, no global scratch), scaled by 1/S and written as the B operand of phase B.
 //   phase B  128 threads own one grid node each: 34 coalesced loads of Q, split, tcgen05.st into TMEM (A operand);
 //            the accumulator rows go back through shared memory and leave as coalesced stores.
-// warps 0-3 loaders / Q producers, 4-7 converters / epilogue, 8 MMA issuer.  Two CTAs fit per SM (256 TMEM columns,
+// warps 0-3 loaders / Q producers, 4-7 converters / epilogue, 8-9 MMA issuers.  Two CTAs fit per SM (256 TMEM columns,
 // ~102 KB shared memory each).  Every wait is a bounded mbarrier poll that records an error code on expiry.
 #include "tc_common.cuh"
 
@@ -23,13 +23,16 @@ namespace spgt {
 __device__ int g_attn_status = 0;
 
 #ifdef SPGT_TC_TRACE
-__device__ long long g_attn_trace[16];
-#define AT_TRACE(slot) do { if (blockIdx.x == 0) g_attn_trace[slot] = clock64(); } while (0)
+__device__ long long g_attn_trace[16 + 10 * 2048];
+__device__ __forceinline__ long long at_gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ int at_smid() { int t; asm volatile("mov.u32 %0, %%smid;" : "=r"(t)); return t; }
+#define AT_TRACE(slot) do { if (blockIdx.x == 0) g_attn_trace[slot] = clock64(); \
+    if (blockIdx.x < 2048) { g_attn_trace[16 + 10 * blockIdx.x + ((slot) & 7)] = at_gtime(); if ((slot) == 0) g_attn_trace[16 + 10 * blockIdx.x + 8] = at_smid(); } } while (0)
 #else
 #define AT_TRACE(slot) do { } while (0)
 #endif
 
-constexpr int AT_THREADS = 288;
+constexpr int AT_THREADS = 320;                 // warps 0-3 loaders, 4-7 converters, 8-9 MMA issuers
 constexpr int AT_NP = 48;                       // N (and B-tile rows) padded to a multiple of 16
 constexpr int AT_SUB = 32;                      // columns per phase-A stage
 constexpr int AT_ST = 3;                        // phase-A stages
@@ -43,7 +46,7 @@ constexpr int AT_TP = 36;                       // pitch of the dpk x dpk partia
 constexpr int AT_BAR_OFF = AT_TC_OFF + AT_TP * AT_TP * 4;
 constexpr int AT_SMEM_BYTES = 1024 + AT_BAR_OFF + 256;
 constexpr int AT_TMEM_COLS = 256;
-constexpr int AT_A1_COL = 48;                   // phase A: accumulator at [0,48), A stages (64 cols each) from here
+constexpr int AT_A1_COL = 96;                   // phase A: two accumulators at [0,48) and [48,96), two A stages (64 cols each) from here
 constexpr int AT_A2_COL = 96;                   // phase B: accumulators at [0,48) and [48,96), A stages (80 cols) from here
 
 template <int D>
@@ -61,7 +64,8 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     auto raw_full = [&](int s) { return bars + 8u * s; };            // [3] loaders -> converters
     auto raw_empty = [&](int s) { return bars + 8u * (3 + s); };     // [3] MMA commit -> loaders
     auto ab_full = [&](int s) { return bars + 8u * (6 + s); };       // [3] converters -> MMA
-    const uint32_t t_done = bars + 8u * 9;                           //     MMA commit -> T readout
+    const uint32_t t_done = bars + 8u * 9;                           //     MMA commits -> T readout
+    auto a_empty = [&](int s) { return bars + 8u * (18 + s); };      // [2] MMA commits -> converters (tensor-memory A stages)
     auto a2_full = [&](int s) { return bars + 8u * (10 + s); };      // [2] Q producers -> MMA
     auto a2_empty = [&](int s) { return bars + 8u * (12 + s); };     // [2] MMA commit -> Q producers
     auto d_full = [&](int b) { return bars + 8u * (14 + b); };       // [2] MMA commit -> epilogue
@@ -83,8 +87,9 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     const int nmine = sub_end - sub_begin;
 
     if (tid == 0) {
-        for (int s = 0; s < AT_ST; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 1); mbar_init(ab_full(s), 128); }
-        mbar_init(t_done, 1);
+        for (int s = 0; s < AT_ST; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 2); mbar_init(ab_full(s), 128); }
+        mbar_init(t_done, 2);
+        for (int s = 0; s < 2; ++s) mbar_init(a_empty(s), 2);
         for (int s = 0; s < 2; ++s) { mbar_init(a2_full(s), 128); mbar_init(a2_empty(s), 1); mbar_init(d_full(s), 1); mbar_init(d_empty(s), 128); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -143,11 +148,12 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 *reinterpret_cast<uint4*>(vhi + off) = make_uint4(h[0], h[1], h[2], h[3]);
                 *reinterpret_cast<uint4*>(vlo + off) = make_uint4(l[0], l[1], l[2], l[3]);
             }
-            // K: one row per thread into tensor memory (the TMEM stage is free: the loaders already waited for the
-            // MMAs that used it).  Lanes beyond dpk move rows whose accumulator entries are never read.
+            // K: one row per thread into tensor memory, two stages there (freed by the MMAs two sub-tiles back).
+            // Lanes beyond dpk move rows whose accumulator entries are never read.
             if (k_warp) {
+                if (!mbar_wait(a_empty(it & 1), (uint32_t)(((it >> 1) & 1) ^ 1), abort_flag, 9, &g_attn_status)) break;
                 tc_fence_after();
-                const uint32_t a_hi = tmem_base + lane_addr + AT_A1_COL + st * 64;
+                const uint32_t a_hi = tmem_base + lane_addr + AT_A1_COL + (it & 1) * 64;
 #pragma unroll
                 for (int h2 = 0; h2 < 2; ++h2) {
                     uint32_t hi[16], lo[16];
@@ -167,6 +173,11 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             mbar_arrive(ab_full(st));
         }
     } else {
+        // Two issuing warps (one thread issues an MMA only about every 54 cycles; a 128 x 48 x 8 MMA takes 24): warp 8
+        // multiplies k-steps 0-1 of every sub-tile into the accumulator at column 0, warp 9 k-steps 2-3 into the one at
+        // column 48; the two partial sums are added when T is read out.
+        const int iw = warp - 8;
+        const uint32_t d = tmem_base + (uint32_t)(iw * AT_NP);
         for (int it = 0; it < nmine; ++it) {
             const uint32_t st = (uint32_t)(it % AT_ST), ph = (uint32_t)((it / AT_ST) & 1);
             if (!mbar_wait(ab_full(st), ph, abort_flag, 3, &g_attn_status)) break;
@@ -175,14 +186,16 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 const uint32_t vhi = smem_base + st * AT_RAW_STAGE + AT_TILE;
                 const uint64_t dbh = tc_smem_desc(vhi), dbl = tc_smem_desc(vhi + AT_TILE);
 #pragma unroll
-                for (int k8 = 0; k8 < 4; ++k8) {
-                    const uint32_t ah = tmem_base + AT_A1_COL + st * 64 + k8 * 8, al = ah + 32;
+                for (int kk = 0; kk < 2; ++kk) {
+                    const int k8 = 2 * iw + kk;
+                    const uint32_t ah = tmem_base + AT_A1_COL + (it & 1) * 64 + k8 * 8, al = ah + 32;
                     const uint64_t adv = (uint64_t)(k8 * 2);
-                    tc_mma_tf32_ts(tmem_base, al, dbh + adv, idesc, (it > 0 || k8 > 0) ? 1u : 0u);
-                    tc_mma_tf32_ts(tmem_base, ah, dbl + adv, idesc, 1u);
-                    tc_mma_tf32_ts(tmem_base, ah, dbh + adv, idesc, 1u);
+                    tc_mma_tf32_ts(d, al, dbh + adv, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_tf32_ts(d, ah, dbl + adv, idesc, 1u);
+                    tc_mma_tf32_ts(d, ah, dbh + adv, idesc, 1u);
                 }
                 tc_commit(raw_empty(st));
+                tc_commit(a_empty(it & 1));
                 if (it == nmine - 1) tc_commit(t_done);
             }
             __syncwarp();
@@ -191,7 +204,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
 
     if (tid == 0) AT_TRACE(1);      // loaders done issuing
     if (tid == 128) AT_TRACE(2);    // converters done
-    if (tid == 256) AT_TRACE(3);    // MMA issued
+    if (tid == 256) AT_TRACE(3);    // MMAs issued
     // ============================== reduce T over the cluster ==============================
     if (warp >= 4 && warp < 8) {
         const int q = warp & 3;
@@ -201,8 +214,15 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             if (nmine > 0) have = mbar_wait(t_done, 0, abort_flag, 4, &g_attn_status);
             tc_fence_after();
             if (have) {
+                float v2[32], w2[16];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16), v);
                 tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + 32, w);
+                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + AT_NP, v2);
+                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + AT_NP + 32, w2);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += v2[j];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) w[j] += w2[j];
             }
             const int row = q * 32 + lane;
             if (row < D) {
@@ -318,7 +338,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             }
             __syncwarp();
         }
-    } else {
+    } else if (warp == 8) {
         for (int it = 0; it < ntile; ++it) {
             const uint32_t sa = (uint32_t)(it & 1), ph = (uint32_t)((it >> 1) & 1);
             if (!mbar_wait(d_empty(sa), ph ^ 1, abort_flag, 7, &g_attn_status)) break;
@@ -391,7 +411,7 @@ int launch_attn_tc(const float* Q, const float* K, const float* V, float* out, f
 
 #ifdef SPGT_TC_TRACE
 extern "C" int spgt_attn_trace_read(long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(long long) * 16) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
+    return cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(long long) * (16 + 10 * 2048)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
 }
 #endif
 

@@ -276,6 +276,175 @@ spectral_inv_x_kernel(const float* __restrict__ Or, const float* __restrict__ Oi
 }
 
 // ------------------------------------------------------------------------------------------------------------
+// S2a and S2c on the tensor cores (3xTF32 warp MMA), one CTA per (ky, b), for r <= SP_XMAX.
+//
+// S2a as a real GEMM:  R[q'][n] = sum_x Gt[q'][x] * Y[x][n],  q' < 2J (rows 0..J-1 = Re G, J..2J-1 = Im G),
+//                      n < 64 (0..31 = Re Y1 = Y1[.., ky, c], 32..63 = Im Y1 = Y1[.., m + ky, c]);
+//                      Zr[q][c] = R[q][c] - R[J+q][32+c],  Zi[q][c] = R[q][32+c] + R[J+q][c].
+// S2c as a real GEMM:  P[x][n] = sum_k Gt[k][x] * Bm[k][n],  k < 2J,
+//                      Bm[q] = (Or[q] | Oi[q]),  Bm[J+q] = (Oi[q] | -Or[q]);  n < 32 -> P[.., ky, :], else P[.., m + ky, :].
+// Both stage the whole G table ([2J][r], zero padded) and their Y1 / O block in shared memory, then every warp
+// owns a slice of the output (S2a: 16 columns, S2c: every fourth 16-row tile).
+// ------------------------------------------------------------------------------------------------------------
+constexpr int SP_XMAX = 256;      // largest r the staged kernels accept (shared-memory budget)
+constexpr int SP_YP = 72;         // pitch of the [x][64] / [k][64] B operands, == 8 (mod 32)
+
+__host__ __device__ inline int sp_round_pitch(int n, int rem) {   // smallest p >= n with p % 32 == rem
+    int p = (n + 31) / 32 * 32 + rem;
+    if (p - 32 >= n) p -= 32;
+    return p;
+}
+
+__global__ void __launch_bounds__(128)
+spectral_fwd_x_mma_kernel(const float* __restrict__ Y1, const float* __restrict__ tab, float* __restrict__ Zr,
+                          float* __restrict__ Zi, int r, int m) {
+    extern __shared__ __align__(16) float smem[];
+    const SpecTables T = spec_tables(r, m);
+    const int J = T.J, M2 = 2 * J, MT = (M2 + 15) / 16;
+    const int r8 = (r + 7) / 8 * 8;
+    const int GP = sp_round_pitch(r8, 4);                    // G pitch == 4 (mod 32): A fragments conflict-free
+    float* gs = smem;                                        // [16*MT][GP]
+    float* ys = smem + 16 * MT * GP;                         // [r8][SP_YP]; later R [16*MT][SP_YP]
+    const int ky = blockIdx.x; const int64_t b = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    // Y block: 16 float4 per x (8 from the real row, 8 from the imaginary row)
+    const float* yb = Y1 + b * (int64_t)r * J * SP_C;
+    for (int i = tid; i < r8 * 16; i += 128) {
+        const int x = i >> 4, c4 = i & 15;
+        const bool ok = x < r;
+        const float* src = yb + ((int64_t)(ok ? x : 0) * J + (c4 < 8 ? ky : m + ky)) * SP_C + (c4 & 7) * 4;
+        cp_async_zfill<16>(ys + x * SP_YP + c4 * 4, src, ok);
+    }
+    cp_async_commit();
+    for (int i = tid; i < 16 * MT * GP; i += 128) {
+        const int q = i / GP, x = i % GP;
+        gs[i] = (q < M2 && x < r) ? __ldg(tab + T.gr + q * r + x) : 0.0f;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    float acc[4][2][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
+    const int n0 = warp * 16;
+    for (int k0 = 0; k0 < r8; k0 += 8) {
+        uint32_t bhi[2][2], blo[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float* p = ys + (k0 + t) * SP_YP + n0 + 8 * j + g;
+            split_tf32(p[0], bhi[j][0], blo[j][0]);
+            split_tf32(p[4 * SP_YP], bhi[j][1], blo[j][1]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (i < MT) {
+                const float* p = gs + (16 * i + g) * GP + k0 + t;
+                uint32_t ahi[4], alo[4];
+                split_tf32(p[0], ahi[0], alo[0]);
+                split_tf32(p[8 * GP], ahi[1], alo[1]);
+                split_tf32(p[4], ahi[2], alo[2]);
+                split_tf32(p[8 * GP + 4], ahi[3], alo[3]);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    mma_tf32(acc[i][j], alo, bhi[j]);
+                    mma_tf32(acc[i][j], ahi, blo[j]);
+                    mma_tf32(acc[i][j], ahi, bhi[j]);
+                }
+            }
+        }
+    }
+    __syncthreads();                                         // everyone is done reading ys
+    float* rs = ys;                                          // R [16*MT][SP_YP]
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (i < MT) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int row = 16 * i + g, col = n0 + 8 * j + 2 * t;
+                *reinterpret_cast<float2*>(rs + row * SP_YP + col) = make_float2(acc[i][j][0], acc[i][j][1]);
+                *reinterpret_cast<float2*>(rs + (row + 8) * SP_YP + col) = make_float2(acc[i][j][2], acc[i][j][3]);
+            }
+        }
+    __syncthreads();
+    for (int e = tid; e < J * SP_C; e += 128) {
+        const int q = e >> 5, c = e & 31;
+        const int64_t o = ((b * J + q) * m + ky) * SP_C + c;
+        Zr[o] = rs[q * SP_YP + c] - rs[(J + q) * SP_YP + 32 + c];
+        Zi[o] = rs[q * SP_YP + 32 + c] + rs[(J + q) * SP_YP + c];
+    }
+}
+
+__global__ void __launch_bounds__(128)
+spectral_inv_x_mma_kernel(const float* __restrict__ Or, const float* __restrict__ Oi, const float* __restrict__ tab,
+                          float* __restrict__ P, int r, int m) {
+    extern __shared__ __align__(16) float smem[];
+    const SpecTables T = spec_tables(r, m);
+    const int J = T.J, M2 = 2 * J, K8 = (M2 + 7) / 8 * 8;
+    const int r16 = (r + 15) / 16 * 16;
+    const int GP = sp_round_pitch(r16, 8);                   // G pitch == 8 (mod 32): transposed A fragments conflict-free
+    float* gs = smem;                                        // [K8][GP]
+    float* bs = smem + K8 * GP;                              // [K8][SP_YP]
+    const int ky = blockIdx.x; const int64_t b = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    for (int i = tid; i < K8 * GP; i += 128) {
+        const int q = i / GP, x = i % GP;
+        gs[i] = (q < M2 && x < r) ? __ldg(tab + T.gr + q * r + x) : 0.0f;
+    }
+    for (int i = tid; i < K8 * 64; i += 128) {
+        const int k = i >> 6, n = i & 63;
+        float v = 0.0f;
+        if (k < M2) {
+            const int q = k < J ? k : k - J;
+            const int64_t o = ((b * J + q) * m + ky) * SP_C + (n & 31);
+            if (k < J) v = n < 32 ? __ldg(Or + o) : __ldg(Oi + o);
+            else v = n < 32 ? __ldg(Oi + o) : -__ldg(Or + o);
+        }
+        bs[k * SP_YP + n] = v;
+    }
+    __syncthreads();
+    float* pb = P + (b * r) * (int64_t)J * SP_C;
+    for (int mt = warp; mt < r16 / 16; mt += 4) {
+        float acc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
+        const int x0 = mt * 16;
+        for (int k0 = 0; k0 < K8; k0 += 8) {
+            uint32_t ahi[4], alo[4];
+            const float* pa = gs + (k0 + t) * GP + x0 + g;   // A[x][k] = G[k][x]
+            split_tf32(pa[0], ahi[0], alo[0]);
+            split_tf32(pa[8], ahi[1], alo[1]);
+            split_tf32(pa[4 * GP], ahi[2], alo[2]);
+            split_tf32(pa[4 * GP + 8], ahi[3], alo[3]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float* p = bs + (k0 + t) * SP_YP + 8 * j + g;
+                uint32_t bhi[2], blo[2];
+                split_tf32(p[0], bhi[0], blo[0]);
+                split_tf32(p[4 * SP_YP], bhi[1], blo[1]);
+                mma_tf32(acc[j], alo, bhi);
+                mma_tf32(acc[j], ahi, blo);
+                mma_tf32(acc[j], ahi, bhi);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int jrow = (j < 4 ? ky : m + ky), c = (8 * j + 2 * t) & 31;
+            const int xa = x0 + g, xb = x0 + g + 8;
+            if (xa < r) *reinterpret_cast<float2*>(pb + ((int64_t)xa * J + jrow) * SP_C + c) = make_float2(acc[j][0], acc[j][1]);
+            if (xb < r) *reinterpret_cast<float2*>(pb + ((int64_t)xb * J + jrow) * SP_C + c) = make_float2(acc[j][2], acc[j][3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------
 // S3: per (b,x) row and chunk of 32 y:  out[y][o] = act( F3[y][:] * P[:, o] + X[y][:] * Wr[:, o] + br[o] ).
 // M = y, N = o (32), K = JP + 32.  One warp per row at a time; X chunks (and the row's P block) are streamed
 // through a private double buffer.
@@ -531,14 +700,29 @@ extern "C" int spgt_spectral_conv2d_fwd(const float* x, const float* wr, const f
     if (e) return e;
     const size_t gsmem = (size_t)2 * J * r * sizeof(float);
     if (gsmem > 200 * 1024) return SPGT_ERR_SHAPE;
-    static size_t cfg_a = 0, cfg_c = 0;
-    if ((e = set_smem_once(spectral_fwd_x_kernel, gsmem, cfg_a))) return e;
-    if ((e = set_smem_once(spectral_inv_x_kernel, gsmem, cfg_c))) return e;
-    spectral_fwd_x_kernel<<<dim3(m, B), 256, gsmem, st>>>(Y1, tab, Zr, Zi, r, m);
+    static size_t cfg_a = 0, cfg_c = 0, cfg_am = 0, cfg_cm = 0;
+    const bool staged = r <= SP_XMAX;                       // tensor-core S2a / S2c with everything staged in shared memory
+    if (staged) {
+        const int MT = ceil_div(2 * (int)J, 16), r8 = ceil_div(r, 8) * 8;
+        const size_t smem_a = ((size_t)16 * MT * sp_round_pitch(r8, 4) + (size_t)(r8 > 16 * MT ? r8 : 16 * MT) * SP_YP) * sizeof(float);
+        if ((e = set_smem_once(spectral_fwd_x_mma_kernel, smem_a, cfg_am))) return e;
+        spectral_fwd_x_mma_kernel<<<dim3(m, B), 128, smem_a, st>>>(Y1, tab, Zr, Zi, r, m);
+    } else {
+        if ((e = set_smem_once(spectral_fwd_x_kernel, gsmem, cfg_a))) return e;
+        spectral_fwd_x_kernel<<<dim3(m, B), 256, gsmem, st>>>(Y1, tab, Zr, Zi, r, m);
+    }
     if ((e = launch_status())) return e;
     spectral_mix_kernel<<<(unsigned)(J * m), 256, 0, st>>>(Zr, Zi, fw0, fw1, Or, Oi, B, m);
     if ((e = launch_status())) return e;
-    spectral_inv_x_kernel<<<dim3(m, B), 256, gsmem, st>>>(Or, Oi, tab, P, r, m);
+    if (staged) {
+        const int K8 = ceil_div(2 * (int)J, 8) * 8, r16 = ceil_div(r, 16) * 16;
+        const size_t smem_c = ((size_t)K8 * sp_round_pitch(r16, 8) + (size_t)K8 * SP_YP) * sizeof(float);
+        if ((e = set_smem_once(spectral_inv_x_mma_kernel, smem_c, cfg_cm))) return e;
+        spectral_inv_x_mma_kernel<<<dim3(m, B), 128, smem_c, st>>>(Or, Oi, tab, P, r, m);
+    } else {
+        if ((e = set_smem_once(spectral_inv_x_kernel, gsmem, cfg_c))) return e;
+        spectral_inv_x_kernel<<<dim3(m, B), 256, gsmem, st>>>(Or, Oi, tab, P, r, m);
+    }
     if ((e = launch_status())) return e;
     switch (T.JP / 8) {
         case 1: return launch_inv_y<1>(x, P, wr, br, tab, y, r, m, act, nrows, st);

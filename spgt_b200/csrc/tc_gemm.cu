@@ -17,14 +17,17 @@
 //   * Row-major epilogues stage each thread's row in padded shared memory and leave through cp.async.bulk stores
 //     (full 128-byte lines); the projection epilogue (LayerNorm + head-major transposed store) and the decoder
 //     head (row dot product) store directly, one row per thread.
-//   warps 0-3 A loaders, 4-7 A splitters, 8 W loader, 9 MMA issuer (one elected lane), 10-17 epilogue.
+//   warps 0-3 A loaders, 4-7 A splitters, 8 W loader, 9-10 MMA issuers (one elected lane each), 11-18 epilogue.
 // All waits are bounded mbarrier polls: on expiry the kernel records an error code, stops waiting and returns.
 #include "tc_common.cuh"
 
 namespace spgt {
 
-constexpr int TC_BLOAD_WARP = 8, TC_MMA_WARP = 9, TC_EPI_WARP0 = 10, TC_EPI_WARPS = 8;
-constexpr int TC_THREADS = 32 * (TC_EPI_WARP0 + TC_EPI_WARPS);
+constexpr int TC_BLOAD_WARP = 8, TC_MMA_WARP = 9, TC_EPI_WARPS = 8;
+// MMA-issuing warps: two with two row tiles per unit (one tile each), one otherwise; the epilogue warps follow them
+__host__ __device__ constexpr int tc_mma_warps(int mt) { return mt == 2 ? 2 : 1; }
+__host__ __device__ constexpr int tc_epi_warp0(int mt) { return TC_MMA_WARP + tc_mma_warps(mt); }
+__host__ __device__ constexpr int tc_threads(int mt) { return 32 * (tc_epi_warp0(mt) + TC_EPI_WARPS); }
 constexpr int TC_SLOT_BYTES = 144;            // per-epilogue-thread staging row: 32 floats + 16 bytes (bank skew)
 
 __device__ int g_tc_status = 0;          // 0 = ok; otherwise the code of the first wait that gave up
@@ -101,7 +104,7 @@ struct TcHeadEpi {
 enum { EPI_LINEAR = 0, EPI_PROJ = 1, EPI_HEAD = 2 };
 
 template <int BN, int MT> struct TcCfg {
-    static constexpr int NBUF = (MT == 1) ? 2 : 1;                  // accumulator buffers
+    static constexpr int NBUF = (MT == 1 || BN <= 64) ? 2 : 1;      // accumulator buffers
     static constexpr int ACC_COLS = NBUF * MT * BN;
     static constexpr int SA = (MT == 1) ? 4 : 2;                    // A stages in TMEM, 64 columns (hi|lo) per tile
     static_assert(ACC_COLS + SA * MT * 64 <= 512, "tensor memory budget");
@@ -116,10 +119,12 @@ template <int BN, int MT> struct TcCfg {
 };
 
 template <int BN, int MT, class Loader, int EPI, class EpiParams>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(tc_threads(MT), 1)
 tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_units, EpiParams ep) {
     using C = TcCfg<BN, MT>;
     constexpr int SA = C::SA, SB = C::SB, NBUF = C::NBUF, SR = C::SR;
+    constexpr int NIWARPS = tc_mma_warps(MT);                       // MMA-issuing warps
+    constexpr int TC_THREADS = tc_threads(MT), TC_EPI_WARP0 = tc_epi_warp0(MT);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // 1024-aligned for the 128B swizzle
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -145,10 +150,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     const bool resident = KB <= SB;          // the whole column tile of W stays in shared memory
 
     if (tid == 0) {
-        for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 1); }
+        for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), NIWARPS); }
         for (int s = 0; s < SR; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
-        for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 32 * TC_EPI_WARPS); }
+        for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), NIWARPS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), NIWARPS); mbar_init(acc_empty(b), 32 * TC_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -276,17 +281,28 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                              ::"r"(smem_base + sb * C::B_BYTES), "l"(wtile + (int64_t)kb * (C::B_BYTES / 4)), "r"(bytes), "r"(b_full(sb)) : "memory");
             }
         }
-    } else if (warp == TC_MMA_WARP) {
-        // ------------------------------------------ MMA issuer ------------------------------------------
-        constexpr uint32_t idesc = tc_idesc(BN);
+    } else if (warp < TC_MMA_WARP + NIWARPS) {
+        // ------------------------------------------ MMA issuers ------------------------------------------
+        // One thread issues a tcgen05.mma about every 54 cycles, while a 128 x 64 x 8 tf32 MMA occupies the tensor
+        // pipe for 32 cycles (128 x 128 x 8: 64), so a single issuing thread can starve the pipe.  With two row tiles
+        // per unit (MT == 2) two warps issue concurrently, one tile (its own accumulator) each; both wait on the same
+        // full barriers and the empty / accumulator barriers expect one commit from each.
+        const int iw = warp - TC_MMA_WARP;
+        constexpr int NI = BN;                                              // N of one instruction
+        {
+        constexpr uint32_t idesc = tc_idesc(NI);
+        const uint32_t d_off = (MT == 2) ? (uint32_t)(iw * BN) : (uint32_t)(iw * NI);
+        const uint32_t a_off = (MT == 2) ? (uint32_t)(iw * 64) : 0u;
+        const uint32_t b_off = (MT == 2) ? 0u : (uint32_t)(iw * NI * 128);   // NI rows of 128 bytes
         int64_t slot = 0;
         bool alive = true;
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
-            if (lane == 0) TC_TRACE(ui, 4);
+            if (lane == 0 && iw == 0) TC_TRACE(ui, 4);
             if (!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2, &g_tc_status)) { alive = false; break; }
-            if (lane == 0) TC_TRACE(ui, 5);
+            if (lane == 0 && iw == 0) TC_TRACE(ui, 5);
             tc_fence_after();
+            const uint32_t d = tmem_base + buf * MT * BN + d_off;
             for (int kb = 0; kb < KB; ++kb, ++slot) {
                 const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
                 const uint32_t sb = resident ? (uint32_t)kb : (uint32_t)(slot % SB);
@@ -295,32 +311,30 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 if (!resident || ui == 0) {
                     if (!mbar_wait(b_full(sb), pb, abort_flag, 7, &g_tc_status)) { alive = false; break; }
                 }
-                if (lane == 0 && kb == 0) TC_TRACE(ui, 6);
+                if (lane == 0 && kb == 0 && iw == 0) TC_TRACE(ui, 6);
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t b_hi = smem_base + sb * C::B_BYTES;
+                    const uint32_t b_hi = smem_base + sb * C::B_BYTES + b_off;
                     const uint64_t dbh = tc_smem_desc(b_hi), dbl = tc_smem_desc(b_hi + C::B_BYTES / 2);
+                    const uint32_t ah0 = tmem_a + sa * MT * 64 + a_off;
 #pragma unroll
                     for (int k8 = 0; k8 < TC_BK / 8; ++k8) {
                         const uint64_t adv = (uint64_t)(k8 * 2);          // 32 bytes per k-step, in 16-byte units
-#pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) {
-                            const uint32_t d = tmem_base + (buf * MT + mt) * BN;
-                            const uint32_t ah = tmem_a + (sa * MT + mt) * 64 + k8 * 8, al = ah + 32;
-                            const uint32_t accum = (kb > 0 || k8 > 0) ? 1u : 0u;
-                            tc_mma_tf32_ts(d, al, dbh + adv, idesc, accum);
-                            tc_mma_tf32_ts(d, ah, dbl + adv, idesc, 1u);
-                            tc_mma_tf32_ts(d, ah, dbh + adv, idesc, 1u);
-                        }
+                        const uint32_t ah = ah0 + k8 * 8, al = ah + 32;
+                        const uint32_t accum = (kb > 0 || k8 > 0) ? 1u : 0u;
+                        tc_mma_tf32_ts(d, al, dbh + adv, idesc, accum);
+                        tc_mma_tf32_ts(d, ah, dbl + adv, idesc, 1u);
+                        tc_mma_tf32_ts(d, ah, dbh + adv, idesc, 1u);
                     }
-                    tc_commit(a_empty(sa));            // A stage reusable once these MMAs have read it
+                    tc_commit(a_empty(sa));            // A stage reusable once both issuers' MMAs have read it
                     if (!resident) tc_commit(b_empty(sb));
                 }
                 __syncwarp();
             }
             if (alive && lane == 0) tc_commit(acc_full(buf));
-            if (lane == 0) TC_TRACE(ui, 7);
+            if (lane == 0 && iw == 0) TC_TRACE(ui, 7);
             __syncwarp();
+        }
         }
     } else {
         // ------------------------------------------ epilogue ------------------------------------------
@@ -520,7 +534,7 @@ static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_til
     if (per_nt < 1) per_nt = 1;
     if (per_nt > m_units) per_nt = m_units;
     const int grid = per_nt * n_tiles;
-    kern<<<grid, TC_THREADS, TcCfg<BN, MT>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
+    kern<<<grid, tc_threads(MT), TcCfg<BN, MT>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
     return launch_status();
 }
 
@@ -529,6 +543,7 @@ static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int r
     const int bn = tc_bn_for(N), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
     const int n_tiles = npad / bn;
     if (long_k && bn == 128) return tc_launch<128, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+    if (long_k && bn == 64) return tc_launch<64, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     switch (bn) {
         case 32: return tc_launch<32, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
         case 64: return tc_launch<64, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
