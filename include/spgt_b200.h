@@ -40,7 +40,7 @@ int spgt_last_cuda_error(void);
 /* Library ABI version (bumped when a signature changes). */
 int spgt_abi_version(void);
 /* Experiment knobs: "attn_cluster" = 0 (heuristic), 1, 2, 4 or 8 CTAs per (batch, head) in spgt_galerkin_attn_fwd;
- * "attn_impl" = 0 (tcgen05 kernel) or 1 (warp-MMA kernel, default while it is the faster one). */
+ * "attn_impl" = 0 (tcgen05 kernel, default) or 1 (warp-MMA kernel). */
 int spgt_set_tuning(const char* key, int value);
 
 /* ---------------------------------------------------------------------------------------------

@@ -457,7 +457,7 @@ skinny_reduce_kernel(const float* __restrict__ ws, float* __restrict__ C, float 
 }
 
 static int g_attn_cluster_override = 0;   // 0 = heuristic; set through spgt_set_tuning("attn_cluster", n)
-static int g_attn_impl = 1;               // 0 = tcgen05 kernel (attention_tc.cu), 1 = warp-MMA kernel of this file (currently faster)
+static int g_attn_impl = 0;               // 0 = tcgen05 kernel (attention_tc.cu, default), 1 = warp-MMA kernel of this file
 
 // defined in attention_tc.cu
 int launch_attn_tc(const float* Q, const float* K, const float* V, float* out, float* t_out, int64_t BH, int H, int dpk,

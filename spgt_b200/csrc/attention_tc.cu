@@ -4,18 +4,25 @@
 //   out[s][j] = sum_i Q[i][s] * T[i][j]                 phase B: M = s, N = j, reduction over i (dpk, zero padded to 40)
 //
 // Both contractions are 3xTF32 (x = hi + lo, three MMAs) so the result keeps fp32-level accuracy.  One cluster of
-// 1-8 CTAs works on a (batch, head); each CTA streams its share of the S columns exactly once:
-//   phase A  loader warps cp.async the raw K and V sub-tiles (32 columns) element-wise into 128B-swizzled K-major
-//            shared memory (rows of Q/K/V are only 4-byte aligned, so no wider copy is legal); converter warps split
-//            V in place into the hi / lo B operands and move the K rows - one row per thread - into TENSOR MEMORY as
-//            the hi / lo A operands; one elected lane issues tcgen05.mma (128 x 48 x 8, A from TMEM, B from smem).
-//            Rows / columns beyond dpk only produce accumulator entries that are never read.
+// 1-8 CTAs works on a (batch, head); each CTA streams its share of the S columns exactly once.
+//
+// Loads.  Rows of Q, K and V are only 4-byte aligned (S is arbitrary), and the number of bytes a CTA can keep in
+// flight, not the instruction rate, limits the stream.  Every row piece is therefore fetched as 16-byte cp.async
+// chunks that start at the aligned element at or below the first wanted column; the wanted columns then sit
+// shift(row) = (element index of the row start) mod 4 floats into the shared-memory row, and the readers add that
+// shift.  Piece starts are multiples of 32 columns, so the shift depends on the row only.
+//
+//   phase A  loader warps fill a deep ring of raw K / V sub-tiles (32 columns, 7 stages ~ 70 KB in flight);
+//            converter warps split V into the hi / lo B operands (128B-swizzled K-major tiles, 2 stages) and move
+//            the K rows - one row per thread - into TENSOR MEMORY as the hi / lo A operands; two issuing warps
+//            multiply (128 x 48 x 8, A from TMEM, B from smem), each into its own accumulator.
 //   reduce   the dpk x dpk partial sums of the cluster's CTAs are added in rank order through distributed shared
 //            memory (deterministic, no global scratch), scaled by 1/S and written as the B operand of phase B.
-//   phase B  128 threads own one grid node each: 34 coalesced loads of Q, split, tcgen05.st into TMEM (A operand);
-//            the accumulator rows go back through shared memory and leave as coalesced stores.
+//   phase B  Q tiles (128 grid nodes) are prefetched two tiles ahead into shared memory; 128 threads own one grid
+//            node each: read its column, split, tcgen05.st into TMEM (A operand); the accumulator rows go back
+//            through shared memory and leave as coalesced stores.
 // warps 0-3 loaders / Q producers, 4-7 converters / epilogue, 8-9 MMA issuers.  Two CTAs fit per SM (256 TMEM columns,
-// ~102 KB shared memory each).  Every wait is a bounded mbarrier poll that records an error code on expiry.
+// ~104 KB shared memory each).  Every wait is a bounded mbarrier poll that records an error code on expiry.
 #include "tc_common.cuh"
 
 namespace spgt {
@@ -35,19 +42,41 @@ __device__ __forceinline__ int at_smid() { int t; asm volatile("mov.u32 %0, %%sm
 constexpr int AT_THREADS = 320;                 // warps 0-3 loaders, 4-7 converters, 8-9 MMA issuers
 constexpr int AT_NP = 48;                       // N (and B-tile rows) padded to a multiple of 16
 constexpr int AT_SUB = 32;                      // columns per phase-A stage
-constexpr int AT_ST = 3;                        // phase-A stages
+constexpr int AT_NR = 7;                        // raw K / V stages
+constexpr int AT_RROWS = 36;                    // rows allocated per raw matrix (dpk <= 35)
+constexpr int AT_RP = 36;                       // floats per raw row: 32 wanted + up to 3 of shift, in 16-byte chunks
+constexpr int AT_RAW_MAT = AT_RROWS * AT_RP * 4;
+constexpr int AT_RAW_STAGE = 2 * AT_RAW_MAT;    // K raw | V raw
 constexpr int AT_TILE = AT_NP * 128;            // one K-major operand image: 48 rows x 128 bytes
-constexpr int AT_RAW_STAGE = 3 * AT_TILE;       // K raw | V hi (raw, split in place) | V lo
-constexpr int AT_TB_OFF = AT_ST * AT_RAW_STAGE; // T images: [k-block 0 hi | lo | k-block 1 hi | lo]
-constexpr int AT_OUT_OFF = AT_TB_OFF + 4 * AT_TILE;
-constexpr int AT_OUT_BYTES = 4 * 32 * 36 * 4;
-constexpr int AT_TC_OFF = AT_OUT_OFF + AT_OUT_BYTES;
+constexpr int AT_QP = 132;                      // floats per Q row of a phase-B tile: 128 wanted + shift, 33 chunks
+constexpr int AT_QSTAGE = AT_RROWS * AT_QP * 4;
+constexpr int AT_NQ = 3;                        // Q stages (prefetch distance 2)
+constexpr int AT_OUT_BYTES = 4 * 32 * 36 * 4;   // output staging of the four epilogue warps
+constexpr int AT_RING_A = AT_NR * AT_RAW_STAGE;
+constexpr int AT_RING_B = AT_NQ * AT_QSTAGE + AT_OUT_BYTES;
+constexpr int AT_RING = ((AT_RING_A > AT_RING_B ? AT_RING_A : AT_RING_B) + 1023) / 1024 * 1024;
+constexpr int AT_OP_OFF = AT_RING;              // phase A: 2 x (V hi | V lo); phase B: T images [k-block 0 hi | lo | k-block 1 hi | lo]
+constexpr int AT_TC_OFF = AT_OP_OFF + 4 * AT_TILE;
 constexpr int AT_TP = 36;                       // pitch of the dpk x dpk partial sums
-constexpr int AT_BAR_OFF = AT_TC_OFF + AT_TP * AT_TP * 4;
-constexpr int AT_SMEM_BYTES = 1024 + AT_BAR_OFF + 256;
+constexpr int AT_SH_OFF = AT_TC_OFF + AT_TP * AT_TP * 4;   // shift table, 36 ints
+constexpr int AT_BAR_OFF = AT_SH_OFF + 160;
+constexpr int AT_SMEM_BYTES = 1024 + AT_BAR_OFF + 320;
 constexpr int AT_TMEM_COLS = 256;
 constexpr int AT_A1_COL = 96;                   // phase A: two accumulators at [0,48) and [48,96), two A stages (64 cols each) from here
 constexpr int AT_A2_COL = 96;                   // phase B: accumulators at [0,48) and [48,96), A stages (80 cols) from here
+static_assert(2 * (AT_SMEM_BYTES + 1024) <= 227 * 1024, "two CTAs per SM");
+
+// 16-byte chunk `ch` of row piece (row, col0): global source (aligned) and the number of valid bytes (the rest is zero-filled)
+__device__ __forceinline__ void at_chunk(const float* tensor, int64_t e_row, int S, int col0, int ch, const float*& src, int& bytes) {
+    const int64_t start = ((e_row + col0) & ~(int64_t)3) + 4 * ch;
+    int64_t valid = e_row + S - start;                                   // elements of this row at or after `start`
+    valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
+    src = tensor + (valid > 0 ? start : 0);
+    bytes = (int)valid * 4;
+}
+__device__ __forceinline__ void at_cp16(uint32_t dst, const float* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
 
 template <int D>
 __global__ void __launch_bounds__(AT_THREADS, 2)
@@ -56,30 +85,28 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint8_t* tb = smem + AT_TB_OFF;
-    float* out_stage = reinterpret_cast<float*>(smem + AT_OUT_OFF);
+    uint8_t* opr = smem + AT_OP_OFF;
     float* Tc = reinterpret_cast<float*>(smem + AT_TC_OFF);
+    int* sh_tab = reinterpret_cast<int*>(smem + AT_SH_OFF);
     uint8_t* bar_mem = smem + AT_BAR_OFF;
     const uint32_t bars = smem_u32(bar_mem);
-    auto raw_full = [&](int s) { return bars + 8u * s; };            // [3] loaders -> converters
-    auto raw_empty = [&](int s) { return bars + 8u * (3 + s); };     // [3] MMA commit -> loaders
-    auto ab_full = [&](int s) { return bars + 8u * (6 + s); };       // [3] converters -> MMA
-    const uint32_t t_done = bars + 8u * 9;                           //     MMA commits -> T readout
-    auto a_empty = [&](int s) { return bars + 8u * (18 + s); };      // [2] MMA commits -> converters (tensor-memory A stages)
-    auto a2_full = [&](int s) { return bars + 8u * (10 + s); };      // [2] Q producers -> MMA
-    auto a2_empty = [&](int s) { return bars + 8u * (12 + s); };     // [2] MMA commit -> Q producers
-    auto d_full = [&](int b) { return bars + 8u * (14 + b); };       // [2] MMA commit -> epilogue
-    auto d_empty = [&](int b) { return bars + 8u * (16 + b); };      // [2] epilogue -> MMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 192);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 200);
+    auto raw_full = [&](int s) { return bars + 8u * s; };            // [7] loaders -> converters
+    auto raw_empty = [&](int s) { return bars + 8u * (7 + s); };     // [7] converters -> loaders
+    auto op_full = [&](int s) { return bars + 8u * (14 + s); };      // [2] converters -> MMA issuers
+    auto op_empty = [&](int s) { return bars + 8u * (16 + s); };     // [2] MMA commits -> converters
+    const uint32_t t_done = bars + 8u * 18;                          //     MMA commits -> T readout
+    auto a2_full = [&](int s) { return bars + 8u * (19 + s); };      // [2] Q producers -> MMA
+    auto a2_empty = [&](int s) { return bars + 8u * (21 + s); };     // [2] MMA commit -> Q producers
+    auto d_full = [&](int b) { return bars + 8u * (23 + b); };       // [2] MMA commit -> epilogue
+    auto d_empty = [&](int b) { return bars + 8u * (25 + b); };      // [2] epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 256);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 264);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t C = cluster_nctarank();
     const uint32_t rank = cluster_ctarank();
     const int64_t bh = blockIdx.x / C;
-    const float* Kg = K + bh * (int64_t)D * S;
-    const float* Vg = V + bh * (int64_t)D * S;
-    const float* Qg = Q + bh * (int64_t)D * S;
+    const int64_t e_bh = bh * (int64_t)D * S;                        // element index of this (batch, head) in Q / K / V
 
     const int nsub = (S + AT_SUB - 1) / AT_SUB;
     const int sub_begin = (int)(((int64_t)rank * nsub) / C);
@@ -87,9 +114,9 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     const int nmine = sub_end - sub_begin;
 
     if (tid == 0) {
-        for (int s = 0; s < AT_ST; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 2); mbar_init(ab_full(s), 128); }
+        for (int s = 0; s < AT_NR; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
+        for (int s = 0; s < 2; ++s) { mbar_init(op_full(s), 128); mbar_init(op_empty(s), 2); }
         mbar_init(t_done, 2);
-        for (int s = 0; s < 2; ++s) mbar_init(a_empty(s), 2);
         for (int s = 0; s < 2; ++s) { mbar_init(a2_full(s), 128); mbar_init(a2_empty(s), 1); mbar_init(d_full(s), 1); mbar_init(d_empty(s), 128); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -98,8 +125,9 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(AT_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int i = tid; i < 4 * AT_TILE / 16; i += AT_THREADS)            // K padding of the T images must be zero
-        reinterpret_cast<uint4*>(tb)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < AT_RROWS) sh_tab[tid] = tid < D ? (int)((e_bh + (int64_t)tid * S) & 3) : 0;
+    for (int i = tid; i < 4 * AT_TILE / 16; i += AT_THREADS)            // rows of the V tiles beyond dpk are never written: keep them finite
+        reinterpret_cast<uint4*>(opr)[i] = make_uint4(0u, 0u, 0u, 0u);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -109,21 +137,20 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     if (tid == 0) AT_TRACE(0);
     // ============================== phase A: partial T over my columns ==============================
     if (warp < 4) {
-        const int t = tid;
+        constexpr int NCH = 2 * D * 9;                                   // 16-byte chunks of one stage: K rows then V rows
         for (int it = 0; it < nmine; ++it) {
-            const uint32_t st = (uint32_t)(it % AT_ST), ph = (uint32_t)((it / AT_ST) & 1);
+            const uint32_t st = (uint32_t)(it % AT_NR), ph = (uint32_t)((it / AT_NR) & 1);
             if (!mbar_wait(raw_empty(st), ph ^ 1, abort_flag, 1, &g_attn_status)) break;
             const int s0 = (sub_begin + it) * AT_SUB;
-            const uint32_t kdst = smem_base + st * AT_RAW_STAGE, vdst = kdst + AT_TILE;
-#pragma unroll 3
-            for (int e = t; e < D * AT_SUB; e += 128) {
-                const int row = e >> 5, col = e & 31;
-                const bool ok = s0 + col < S;
-                const int64_t g = (int64_t)row * S + (ok ? s0 + col : 0);
-                const uint32_t off = tc_swz(row, col >> 2) + (uint32_t)(col & 3) * 4u;
-                const int n = ok ? 4 : 0;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(kdst + off), "l"(Kg + g), "r"(n) : "memory");
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(vdst + off), "l"(Vg + g), "r"(n) : "memory");
+            const uint32_t dst0 = smem_base + st * AT_RAW_STAGE;
+#pragma unroll 2
+            for (int idx = tid; idx < NCH; idx += 128) {
+                const int mat = idx >= D * 9 ? 1 : 0;
+                const int j = idx - mat * D * 9;
+                const int row = j / 9, ch = j - 9 * row;
+                const float* src; int bytes;
+                at_chunk(mat ? V : K, e_bh + (int64_t)row * S, S, s0, ch, src, bytes);
+                at_cp16(dst0 + mat * AT_RAW_MAT + row * (AT_RP * 4) + ch * 16, src, bytes);
             }
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_full(st)) : "memory");
         }
@@ -133,44 +160,50 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         const int krow = q * 32 + lane;                                 // K row moved to TMEM by this thread (q < 2)
         const bool k_warp = q * 32 < D;                                 // this warp owns at least one valid K row
+        const int krow_rd = krow < AT_RROWS ? krow : AT_RROWS - 1;      // lanes beyond dpk read an allocated row; their TMEM lanes are never used
+        const int ksh = sh_tab[krow_rd];
+        int vrow[3], vsh[3];
+#pragma unroll
+        for (int n = 0; n < 3; ++n) { vrow[n] = (t >> 3) + 16 * n; vsh[n] = vrow[n] < D ? sh_tab[vrow[n]] : 0; }
         for (int it = 0; it < nmine; ++it) {
-            const uint32_t st = (uint32_t)(it % AT_ST), ph = (uint32_t)((it / AT_ST) & 1);
+            const uint32_t st = (uint32_t)(it % AT_NR), ph = (uint32_t)((it / AT_NR) & 1);
+            const uint32_t so = (uint32_t)(it & 1), po = (uint32_t)((it >> 1) & 1);
             if (!mbar_wait(raw_full(st), ph, abort_flag, 2, &g_attn_status)) break;
-            uint8_t* kraw = smem + st * AT_RAW_STAGE;
-            uint8_t* vhi = kraw + AT_TILE;
+            if (!mbar_wait(op_empty(so), po ^ 1, abort_flag, 9, &g_attn_status)) break;    // MMAs two sub-tiles back are done
+            const float* kraw = reinterpret_cast<const float*>(smem + st * AT_RAW_STAGE);
+            const float* vraw = kraw + AT_RROWS * AT_RP;
+            uint8_t* vhi = opr + so * (2 * AT_TILE);
             uint8_t* vlo = vhi + AT_TILE;
-            // V: split the raw tile in place into the hi / lo B operands
-            for (int e = t; e < D * 8; e += 128) {
-                const uint32_t off = tc_swz(e >> 3, e & 7);
-                const float4 v = *reinterpret_cast<const float4*>(vhi + off);
-                uint32_t h[4], l[4];
-                split_tf32_rn(v.x, h[0], l[0]); split_tf32_rn(v.y, h[1], l[1]); split_tf32_rn(v.z, h[2], l[2]); split_tf32_rn(v.w, h[3], l[3]);
-                *reinterpret_cast<uint4*>(vhi + off) = make_uint4(h[0], h[1], h[2], h[3]);
-                *reinterpret_cast<uint4*>(vlo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+            // V: raw rows -> hi / lo B operands (row = j, 32 k-values = grid nodes, 128B swizzle)
+#pragma unroll
+            for (int n = 0; n < 3; ++n) {
+                if (vrow[n] < D) {
+                    const float* p = vraw + vrow[n] * AT_RP + vsh[n] + 4 * (t & 7);
+                    uint32_t h[4], l[4];
+                    split_tf32_rn(p[0], h[0], l[0]); split_tf32_rn(p[1], h[1], l[1]); split_tf32_rn(p[2], h[2], l[2]); split_tf32_rn(p[3], h[3], l[3]);
+                    const uint32_t off = tc_swz(vrow[n], t & 7);
+                    *reinterpret_cast<uint4*>(vhi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(vlo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                }
             }
-            // K: one row per thread into tensor memory, two stages there (freed by the MMAs two sub-tiles back).
-            // Lanes beyond dpk move rows whose accumulator entries are never read.
+            // K: one row per thread into tensor memory (stage `so`, freed together with the V operands)
             if (k_warp) {
-                if (!mbar_wait(a_empty(it & 1), (uint32_t)(((it >> 1) & 1) ^ 1), abort_flag, 9, &g_attn_status)) break;
                 tc_fence_after();
-                const uint32_t a_hi = tmem_base + lane_addr + AT_A1_COL + (it & 1) * 64;
+                const uint32_t a_hi = tmem_base + lane_addr + AT_A1_COL + so * 64;
+                const float* p = kraw + krow_rd * AT_RP + ksh;
 #pragma unroll
                 for (int h2 = 0; h2 < 2; ++h2) {
                     uint32_t hi[16], lo[16];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float4 w = *reinterpret_cast<const float4*>(kraw + tc_swz(krow, 4 * h2 + j));
-                        split_tf32_rn(w.x, hi[4 * j], lo[4 * j]); split_tf32_rn(w.y, hi[4 * j + 1], lo[4 * j + 1]);
-                        split_tf32_rn(w.z, hi[4 * j + 2], lo[4 * j + 2]); split_tf32_rn(w.w, hi[4 * j + 3], lo[4 * j + 3]);
-                    }
+                    for (int j = 0; j < 16; ++j) split_tf32_rn(p[16 * h2 + j], hi[j], lo[j]);
                     tc_st16(a_hi + 16 * h2, hi);
                     tc_st16(a_hi + 32 + 16 * h2, lo);
                 }
-                tc_wait_st();
-                tc_fence_before();
             }
+            mbar_arrive(raw_empty(st));                                 // this thread has read the raw stage
+            if (k_warp) { tc_wait_st(); tc_fence_before(); }
             fence_proxy_async();
-            mbar_arrive(ab_full(st));
+            mbar_arrive(op_full(so));
         }
     } else {
         // Two issuing warps (one thread issues an MMA only about every 54 cycles; a 128 x 48 x 8 MMA takes 24): warp 8
@@ -179,23 +212,22 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         const int iw = warp - 8;
         const uint32_t d = tmem_base + (uint32_t)(iw * AT_NP);
         for (int it = 0; it < nmine; ++it) {
-            const uint32_t st = (uint32_t)(it % AT_ST), ph = (uint32_t)((it / AT_ST) & 1);
-            if (!mbar_wait(ab_full(st), ph, abort_flag, 3, &g_attn_status)) break;
+            const uint32_t so = (uint32_t)(it & 1), po = (uint32_t)((it >> 1) & 1);
+            if (!mbar_wait(op_full(so), po, abort_flag, 3, &g_attn_status)) break;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t vhi = smem_base + st * AT_RAW_STAGE + AT_TILE;
+                const uint32_t vhi = smem_base + AT_OP_OFF + so * (2 * AT_TILE);
                 const uint64_t dbh = tc_smem_desc(vhi), dbl = tc_smem_desc(vhi + AT_TILE);
 #pragma unroll
                 for (int kk = 0; kk < 2; ++kk) {
                     const int k8 = 2 * iw + kk;
-                    const uint32_t ah = tmem_base + AT_A1_COL + (it & 1) * 64 + k8 * 8, al = ah + 32;
+                    const uint32_t ah = tmem_base + AT_A1_COL + so * 64 + k8 * 8, al = ah + 32;
                     const uint64_t adv = (uint64_t)(k8 * 2);
                     tc_mma_tf32_ts(d, al, dbh + adv, idesc, (it > 0 || kk > 0) ? 1u : 0u);
                     tc_mma_tf32_ts(d, ah, dbl + adv, idesc, 1u);
                     tc_mma_tf32_ts(d, ah, dbh + adv, idesc, 1u);
                 }
-                tc_commit(raw_empty(st));
-                tc_commit(a_empty(it & 1));
+                tc_commit(op_empty(so));
                 if (it == nmine - 1) tc_commit(t_done);
             }
             __syncwarp();
@@ -234,8 +266,11 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         }
     }
     tc_fence_before();
-    cluster_sync_all();        // every CTA's Tc is complete; also a CTA-wide barrier (all threads arrive)
+    cluster_sync_all();        // every CTA's Tc is complete and all MMAs of phase A are done; also a CTA-wide barrier
     tc_fence_after();
+    for (int i = tid; i < 4 * AT_TILE / 16; i += AT_THREADS)            // the T images reuse the V operand ring; their k padding must be zero
+        reinterpret_cast<uint4*>(opr)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
     {
         const float inv_s = 1.0f / (float)S;
         for (int e = tid; e < D * D; e += AT_THREADS) {
@@ -244,14 +279,13 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             for (uint32_t r = 0; r < C; ++r) s += ld_dsmem_f32(Tc + i * AT_TP + j, r);
             s *= inv_s;
             if (t_out != nullptr && rank == 0) t_out[bh * D * D + e] = s;
-            uint32_t hi, lo, lo2;
-            split_tf32(s, hi, lo);
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo2) : "f"(__uint_as_float(lo)));
+            uint32_t hi, lo;
+            split_tf32_rn(s, hi, lo);
             // B operand of phase B: row j (N), k = i; k-block i / 32
-            uint8_t* img = tb + (i >> 5) * (2 * AT_TILE);
+            uint8_t* img = opr + (i >> 5) * (2 * AT_TILE);
             const uint32_t off = tc_swz(j, (i & 31) >> 2) + (uint32_t)(i & 3) * 4u;
             *reinterpret_cast<uint32_t*>(img + off) = hi;
-            *reinterpret_cast<uint32_t*>(img + AT_TILE + off) = lo2;
+            *reinterpret_cast<uint32_t*>(img + AT_TILE + off) = lo;
         }
     }
     fence_proxy_async();
@@ -263,17 +297,39 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     const int col_end = min(sub_end * AT_SUB, S);
     const int ntile = (col_end - col_begin + 127) / 128;
     const int64_t b_idx = bh / H, h_idx = bh % H;
+    float* out_stage = reinterpret_cast<float*>(smem + AT_NQ * AT_QSTAGE);
     if (warp < 4) {
         const int q = warp & 3;
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        auto load_q = [&](int tile) {                                    // 33 chunks per row: 128 wanted columns + shift
+            if (tile < ntile) {
+                const int c0 = col_begin + tile * 128;
+                const uint32_t dst0 = smem_base + (uint32_t)(tile % AT_NQ) * AT_QSTAGE;
+                for (int idx = tid; idx < D * 33; idx += 128) {
+                    const int row = idx / 33, ch = idx - 33 * row;
+                    const float* src; int bytes;
+                    at_chunk(Q, e_bh + (int64_t)row * S, S, c0, ch, src, bytes);
+                    at_cp16(dst0 + row * (AT_QP * 4) + ch * 16, src, bytes);
+                }
+            }
+            cp_async_commit();                                           // one group per tile slot, empty past the end
+        };
+        load_q(0);
+        load_q(1);
+        bool alive = true;                                               // after a failed wait keep meeting the others at the barrier
         for (int it = 0; it < ntile; ++it) {
             const uint32_t sa = (uint32_t)(it & 1), ph = (uint32_t)((it >> 1) & 1);
+            cp_async_wait<1>();                                          // my chunks of tile `it` have landed
+            asm volatile("bar.sync 1, 128;" ::: "memory");              // ... and everyone else's; tile it-1 has been read by all
+            load_q(it + 2);                                              // into the stage tile it-1 used
+            if (!alive) continue;
             const int s = col_begin + it * 128 + tid;
             const bool ok = s < col_end;
+            const float* qs = reinterpret_cast<const float*>(smem + (it % AT_NQ) * AT_QSTAGE) + tid;
             float qv[40];
 #pragma unroll
-            for (int i = 0; i < 40; ++i) qv[i] = (i < D && ok) ? __ldg(Qg + (int64_t)i * S + s) : 0.0f;
-            if (!mbar_wait(a2_empty(sa), ph ^ 1, abort_flag, 5, &g_attn_status)) break;
+            for (int i = 0; i < 40; ++i) qv[i] = (i < D && ok) ? qs[i * AT_QP + sh_tab[i]] : 0.0f;
+            if (!mbar_wait(a2_empty(sa), ph ^ 1, abort_flag, 5, &g_attn_status)) { alive = false; continue; }
             tc_fence_after();
             const uint32_t a_hi = tmem_base + lane_addr + AT_A2_COL + sa * 80, a_lo = a_hi + 40;
 #pragma unroll
@@ -295,6 +351,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             tc_fence_before();
             mbar_arrive(a2_full(sa));
         }
+        cp_async_wait_all();
     } else if (warp < 8) {
         const int q = warp & 3;
         float* os = out_stage + (warp - 4) * 32 * 36;
@@ -348,7 +405,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 const uint32_t d = tmem_base + sa * AT_NP;
 #pragma unroll
                 for (int k8 = 0; k8 < 5; ++k8) {
-                    const uint32_t img = smem_base + AT_TB_OFF + (k8 >> 2) * (2 * AT_TILE);
+                    const uint32_t img = smem_base + AT_OP_OFF + (k8 >> 2) * (2 * AT_TILE);
                     const uint64_t adv = (uint64_t)((k8 & 3) * 2);
                     const uint64_t dbh = tc_smem_desc(img) + adv, dbl = tc_smem_desc(img + AT_TILE) + adv;
                     const uint32_t ah = tmem_base + AT_A2_COL + sa * 80 + k8 * 8, al = ah + 40;

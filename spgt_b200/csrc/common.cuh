@@ -28,18 +28,22 @@ inline int num_sms() {
 template <typename T> __host__ __device__ constexpr T ceil_div(T a, T b) { return (a + b - 1) / b; }
 
 // ---- 3xTF32 ---------------------------------------------------------------------------------------
-// x = hi + lo with hi = tf32(x) (round to nearest) and lo = x - hi (exact in fp32; the tensor core reads its
-// upper 19 bits).  a*b ~= hi_a*hi_b + hi_a*lo_b + lo_a*hi_b recovers fp32-level accuracy from three TF32 MMAs.
+// x = hi + lo with hi = tf32(x) (round to nearest, ties away) and lo = x - hi (exact in fp32; the tensor core reads
+// its upper 19 bits).  a*b ~= hi_a*hi_b + hi_a*lo_b + lo_a*hi_b recovers fp32-level accuracy from three TF32 MMAs.
+// The rounding is done with integer arithmetic on the bit pattern (add half an ulp of tf32 to the magnitude, clear
+// the 13 low mantissa bits): cvt.rna.tf32.f32 gives the same bits but runs on the quarter-rate conversion pipe,
+// which becomes the bottleneck of kernels that split every operand element.
+__device__ __forceinline__ uint32_t tf32_rna_bits(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    hi = tf32_rna_bits(x);
     lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
-// Same, with lo also rounded to tf32 (round to nearest) instead of being truncated by the tensor core: one more
-// instruction, unbiased error; used where thousands of products are summed (the K^T V reduction over grid nodes).
+// Same, with lo also rounded to tf32 (round to nearest) instead of being truncated by the tensor core: two more
+// instructions, unbiased error; used where thousands of products are summed (the K^T V reduction over grid nodes).
 __device__ __forceinline__ void split_tf32_rn(float x, uint32_t& hi, uint32_t& lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(x - __uint_as_float(hi)));
+    hi = tf32_rna_bits(x);
+    lo = tf32_rna_bits(x - __uint_as_float(hi));
 }
 
 // D(16x8) += A(16x8, row) * B(8x8, col), TF32 inputs, fp32 accumulate.

@@ -152,7 +152,7 @@ def test_attention_both_implementations(dev, B, H, dpk, S):
                 assert torch.equal(merged, out.transpose(1, 2).contiguous().view(B, S, H * dpk)), (impl, c)
         assert lib.spgt_tc_status() == 0
     finally:
-        lib.spgt_set_tuning(b'attn_impl', 1)
+        lib.spgt_set_tuning(b'attn_impl', 0)
         lib.spgt_set_tuning(b'attn_cluster', 0)
 
 
