@@ -66,14 +66,7 @@ constexpr int AT_A1_COL = 96;                   // phase A: two accumulators at 
 constexpr int AT_A2_COL = 96;                   // phase B: accumulators at [0,48) and [48,96), A stages (80 cols) from here
 static_assert(2 * (AT_SMEM_BYTES + 1024) <= 227 * 1024, "two CTAs per SM");
 
-// 16-byte chunk `ch` of row piece (row, col0): global source (aligned) and the number of valid bytes (the rest is zero-filled)
-__device__ __forceinline__ void at_chunk(const float* tensor, int64_t e_row, int S, int col0, int ch, const float*& src, int& bytes) {
-    const int64_t start = ((e_row + col0) & ~(int64_t)3) + 4 * ch;
-    int64_t valid = e_row + S - start;                                   // elements of this row at or after `start`
-    valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
-    src = tensor + (valid > 0 ? start : 0);
-    bytes = (int)valid * 4;
-}
+// 16-byte cp.async that reads `bytes` (0, 4, 8, 12 or 16) from the aligned source and zero-fills the rest
 __device__ __forceinline__ void at_cp16(uint32_t dst, const float* src, int bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
@@ -107,6 +100,10 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     const uint32_t rank = cluster_ctarank();
     const int64_t bh = blockIdx.x / C;
     const int64_t e_bh = bh * (int64_t)D * S;                        // element index of this (batch, head) in Q / K / V
+    const int sh_bh = (int)(e_bh & 3);                               // its offset from the 16-byte aligned element below it
+    const float* Kb = K + (e_bh - sh_bh);
+    const float* Vb = V + (e_bh - sh_bh);
+    const float* Qb = Q + (e_bh - sh_bh);
 
     const int nsub = (S + AT_SUB - 1) / AT_SUB;
     const int sub_begin = (int)(((int64_t)rank * nsub) / C);
@@ -125,7 +122,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(AT_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (tid < AT_RROWS) sh_tab[tid] = tid < D ? (int)((e_bh + (int64_t)tid * S) & 3) : 0;
+    if (tid < AT_RROWS) sh_tab[tid] = tid < D ? ((sh_bh + tid * S) & 3) : 0;
     for (int i = tid; i < 4 * AT_TILE / 16; i += AT_THREADS)            // rows of the V tiles beyond dpk are never written: keep them finite
         reinterpret_cast<uint4*>(opr)[i] = make_uint4(0u, 0u, 0u, 0u);
     tc_fence_before();
@@ -137,20 +134,37 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     if (tid == 0) AT_TRACE(0);
     // ============================== phase A: partial T over my columns ==============================
     if (warp < 4) {
+        // The chunks a thread copies are the same for every sub-tile: (matrix, row, chunk) of index tid + 128 n.
         constexpr int NCH = 2 * D * 9;                                   // 16-byte chunks of one stage: K rows then V rows
+        constexpr int NPT = (NCH + 127) / 128;
+        const float* cbase[NPT];                                         // aligned source of the chunk for sub-tile column 0
+        int crem[NPT];                                                   // elements from there to the end of the row
+        uint32_t cdst[NPT];                                              // destination offset inside a raw stage
+#pragma unroll
+        for (int n = 0; n < NPT; ++n) {
+            const int idx = tid + 128 * n;
+            const bool in = idx < NCH;
+            const int mat = idx >= D * 9 ? 1 : 0;
+            const int j = in ? idx - mat * D * 9 : 0;
+            const int row = j / 9, ch = j - 9 * row;
+            const int e_row = sh_bh + row * S;
+            const int start = (e_row & ~3) + 4 * ch;
+            cbase[n] = (mat ? Vb : Kb) + start;
+            crem[n] = in ? e_row + S - start : 0;
+            cdst[n] = (uint32_t)(mat * AT_RAW_MAT + row * (AT_RP * 4) + ch * 16);
+        }
         for (int it = 0; it < nmine; ++it) {
             const uint32_t st = (uint32_t)(it % AT_NR), ph = (uint32_t)((it / AT_NR) & 1);
             if (!mbar_wait(raw_empty(st), ph ^ 1, abort_flag, 1, &g_attn_status)) break;
             const int s0 = (sub_begin + it) * AT_SUB;
             const uint32_t dst0 = smem_base + st * AT_RAW_STAGE;
-#pragma unroll 2
-            for (int idx = tid; idx < NCH; idx += 128) {
-                const int mat = idx >= D * 9 ? 1 : 0;
-                const int j = idx - mat * D * 9;
-                const int row = j / 9, ch = j - 9 * row;
-                const float* src; int bytes;
-                at_chunk(mat ? V : K, e_bh + (int64_t)row * S, S, s0, ch, src, bytes);
-                at_cp16(dst0 + mat * AT_RAW_MAT + row * (AT_RP * 4) + ch * 16, src, bytes);
+#pragma unroll
+            for (int n = 0; n < NPT; ++n) {
+                if (tid + 128 * n < NCH) {
+                    int valid = crem[n] - s0;
+                    valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
+                    at_cp16(dst0 + cdst[n], valid > 0 ? cbase[n] + s0 : Kb, valid * 4);
+                }
             }
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_full(st)) : "memory");
         }
@@ -301,19 +315,39 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     if (warp < 4) {
         const int q = warp & 3;
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        auto load_q = [&](int tile) {                                    // 33 chunks per row: 128 wanted columns + shift
+        // Q tile loader.  Thread (w = warp, ch = lane) copies chunk ch of rows w, w + 4, w + 8, ...: rows four apart
+        // have the same shift, so their aligned sources are exactly 4 S floats apart and share the valid-byte count.
+        // The 33rd chunk of every row (needed when the shift is not zero) is copied by threads 0 .. dpk-1.
+        const int e_w = sh_bh + warp * S;
+        const float* qsrc0 = Qb + (e_w & ~3) + 4 * lane;
+        const int qrem0 = S + (e_w & 3) - 4 * lane;                      // elements from chunk `lane` of column 0 to the row end
+        const int e_x = sh_bh + (tid < D ? tid : 0) * S;
+        const float* xsrc0 = Qb + (e_x & ~3) + 128;
+        const int xrem0 = S + (e_x & 3) - 128;
+        auto load_q = [&](int tile) {
             if (tile < ntile) {
                 const int c0 = col_begin + tile * 128;
                 const uint32_t dst0 = smem_base + (uint32_t)(tile % AT_NQ) * AT_QSTAGE;
-                for (int idx = tid; idx < D * 33; idx += 128) {
-                    const int row = idx / 33, ch = idx - 33 * row;
-                    const float* src; int bytes;
-                    at_chunk(Q, e_bh + (int64_t)row * S, S, c0, ch, src, bytes);
-                    at_cp16(dst0 + row * (AT_QP * 4) + ch * 16, src, bytes);
+                int valid = qrem0 - c0;
+                valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
+                const float* src = valid > 0 ? qsrc0 + c0 : Qb;
+                const size_t step = valid > 0 ? (size_t)4 * S : 0;
+                uint32_t dst = dst0 + warp * (AT_QP * 4) + lane * 16;
+#pragma unroll
+                for (int k = 0; k < (D + 3) / 4; ++k) {
+                    if (warp + 4 * k < D) at_cp16(dst, src, valid * 4);
+                    src += step;
+                    dst += 4 * AT_QP * 4;
+                }
+                if (tid < D) {
+                    int vx = xrem0 - c0;
+                    vx = vx < 0 ? 0 : (vx > 4 ? 4 : vx);
+                    at_cp16(dst0 + tid * (AT_QP * 4) + 32 * 16, vx > 0 ? xsrc0 + c0 : Qb, vx * 4);
                 }
             }
             cp_async_commit();                                           // one group per tile slot, empty past the end
         };
+        const int s4 = S & 3;
         load_q(0);
         load_q(1);
         bool alive = true;                                               // after a failed wait keep meeting the others at the barrier
@@ -328,7 +362,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             const float* qs = reinterpret_cast<const float*>(smem + (it % AT_NQ) * AT_QSTAGE) + tid;
             float qv[40];
 #pragma unroll
-            for (int i = 0; i < 40; ++i) qv[i] = (i < D && ok) ? qs[i * AT_QP + sh_tab[i]] : 0.0f;
+            for (int i = 0; i < 40; ++i) qv[i] = (i < D && ok) ? qs[i * AT_QP + ((sh_bh + i * s4) & 3)] : 0.0f;
             if (!mbar_wait(a2_empty(sa), ph ^ 1, abort_flag, 5, &g_attn_status)) { alive = false; continue; }
             tc_fence_after();
             const uint32_t a_hi = tmem_base + lane_addr + AT_A2_COL + sa * 80, a_lo = a_hi + 40;
@@ -336,14 +370,14 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             for (int c = 0; c < 2; ++c) {
                 uint32_t hi[16], lo[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) split_tf32_rn(qv[16 * c + j], hi[j], lo[j]);
+                for (int j = 0; j < 16; ++j) split_tf32(qv[16 * c + j], hi[j], lo[j]);
                 tc_st16(a_hi + 16 * c, hi);
                 tc_st16(a_lo + 16 * c, lo);
             }
             {
                 uint32_t hi[8], lo[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) split_tf32_rn(qv[32 + j], hi[j], lo[j]);
+                for (int j = 0; j < 8; ++j) split_tf32(qv[32 + j], hi[j], lo[j]);
                 tc_st8(a_hi + 32, hi);
                 tc_st8(a_lo + 32, lo);
             }
