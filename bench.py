@@ -28,9 +28,9 @@ import torch.distributed as dist  # noqa: E402
 
 METRIC = 'darcy_gt_inference_samples_per_s_211'
 FINE, SUB_NODE, SUB_ATTN, MODES, SEED = 421, 2, 8, 12, 4
-# DRAM bytes (read + write) of one galerkin_attn_kernel launch at B=64, H=4, S=2809 from the ncu capture
+# DRAM bytes (read + write) of one galerkin_attn_tc_kernel launch at B=64, H=4, S=2809 from the ncu capture
 # summarised in profiles/ (None until a capture of the current kernel exists).
-ATTN_TRAFFIC_BYTES = None
+ATTN_TRAFFIC_BYTES = 346_700_000   # dram read + write per launch from the ncu capture under profiles/ (345.7 - 347.8 MB)
 
 
 def measured_peak():
@@ -349,7 +349,7 @@ def main():
     peak, peak_kind = measured_peak()
     algo_bytes = 4 * B * H * DPK * S * 4                      # read Q, K, V and write out, fp32
     achieved = algo_bytes / (attn_avg_ms * 1e-3) / 1e9 if attn_avg_ms > 0 else None
-    roofline = {'kernel': 'galerkin_attn_kernel', 'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'peak_kind': peak_kind,
+    roofline = {'kernel': 'galerkin_attn_tc_kernel', 'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'peak_kind': peak_kind,
                 'unit': 'GB/s', 'frac': (achieved / peak) if achieved else None, 'traffic': ATTN_TRAFFIC_BYTES,
                 'algorithmic_bytes': algo_bytes, 'avg_launch_ms': attn_avg_ms, 'launches_timed': len(attn_ms)}
 
