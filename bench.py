@@ -111,6 +111,20 @@ def oracle_params(seed: int = SEED):
     return {k: v.detach().clone() for k, v in model.state_dict().items()}
 
 
+WORKLOAD = ('full Darcy Galerkin Transformer forward, fine grid 211x211, attention grid 53x53, 6 encoder '
+            'layers (hidden 128, 4 heads, FFN 256), FNO2d regressor (2 spectral layers, width 32, 12 modes)')
+
+
+def use_all_host_threads() -> int:
+    """The launcher of multi-rank runs exports OMP_NUM_THREADS=1; the CPU legs use every core this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def time_oracle(sample_batch: int, steps: int, warmup: int):
     O, cfg, data = oracle_setup(sample_batch)
     p = oracle_params()
@@ -128,14 +142,15 @@ def time_oracle(sample_batch: int, steps: int, warmup: int):
 def run_reference(args, rank):
     if rank != 0:
         return
-    cores = torch.get_num_threads()
+    cores = use_all_host_threads()
     sample = 8
     sps, per_step = time_oracle(sample, args.steps, args.warmup)
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': sps, 'unit': 'samples/s', 'n_gpus': args.gpus, 'steps': args.steps,
         'warmup': args.warmup, 'ms_per_step': per_step * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
         'dtype': 'f32', 'data': 'synthetic', 'gpu_launches': 0,
-        'config': {'workload': f'full Darcy GT forward 211x211 / 53x53, 6 encoder layers, FNO 12 modes; CPU sample of {sample} of the 64-sample batch per step'},
+        'config': {'workload': WORKLOAD, 'batch_per_gpu': 64, 'global_batch': 64 * args.gpus, 'parallelism': f'dp{args.gpus}', 'seed': SEED,
+                   'cpu_sample': f'{sample} of the 64 samples of a step per timed forward'},
         'cpu_baseline': {'value': sps, 'unit': 'samples/s', 'cores': cores, 'kind': 'port',
                          'sample': f'{sample} samples per step (1/8 of the 64-sample batch), torch CPU fp32, {cores} threads'},
         'e2e': {'value': sps, 'unit': 'samples/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
@@ -364,7 +379,7 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cores = torch.get_num_threads()
+        cores = use_all_host_threads()
         sps, per_step = time_oracle(8, 3, 1)
         cpu = {'value': sps, 'unit': 'samples/s', 'cores': cores, 'kind': 'port',
                'sample': f'8 samples per forward (1/8 of the batch), 3 timed forwards after 1 warm-up, torch CPU fp32, {cores} threads'}
@@ -374,9 +389,7 @@ def main():
             'metric': METRIC, 'value': value, 'unit': 'samples/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': elapsed_ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
             'dtype': 'f32', 'data': 'synthetic',
-            'config': {'workload': 'full Darcy Galerkin Transformer forward, fine grid 211x211, attention grid 53x53, 6 encoder '
-                                   'layers (hidden 128, 4 heads, FFN 256), FNO2d regressor (2 spectral layers, width 32, 12 modes)',
-                       'batch_per_gpu': B, 'global_batch': B * world, 'parallelism': f'dp{world}', 'seed': SEED,
+            'config': {'workload': WORKLOAD, 'batch_per_gpu': B, 'global_batch': B * world, 'parallelism': f'dp{world}', 'seed': SEED,
                        'l2_policy': 'per-step working set (several GB of activations) is far larger than the 126 MB L2'},
             'clocks': clocks.summary(), 'gpu_launches': launches,
             'e2e': {'value': e2e_value, 'unit': 'samples/s', 'h2d_bytes_per_step': nbytes['h2d'], 'd2h_bytes_per_step': nbytes['d2h'],

@@ -35,7 +35,9 @@ __device__ int g_tc_status = 0;          // 0 = ok; otherwise the code of the fi
 #ifdef SPGT_TC_TRACE                      // developer build only: per-unit timestamps of CTA 0 (see spgt_tc_trace_read)
 __device__ long long g_tc_trace[64 * 32];
 #define TC_TRACE(unit_i, slot) do { if (blockIdx.x == 0 && (unit_i) < 64) g_tc_trace[(unit_i) * 32 + (slot)] = clock64(); } while (0)
+#define TC_TADD(unit_i, slot, ...) do { const long long t_ = clock64(); __VA_ARGS__; if (blockIdx.x == 0 && (unit_i) < 64 && (threadIdx.x & 31) == 0) g_tc_trace[(unit_i) * 32 + (slot)] += clock64() - t_; } while (0)
 #else
+#define TC_TADD(unit_i, slot, ...) do { __VA_ARGS__; } while (0)
 #define TC_TRACE(unit_i, slot) do { } while (0)
 #endif
 
@@ -210,7 +212,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 for (int i = 0; i < 8; ++i) rs[m][i] = ld.row_state(row0 + m * TC_BM + 16 * i);
             for (int kb = 0; kb < KB; ++kb, ++slot) {
                 const uint32_t sr = (uint32_t)(slot % SR), ph = (uint32_t)((slot / SR) & 1);
-                if (!mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1, &g_tc_status)) { alive = false; break; }
+                bool okw; TC_TADD(ui, 28, okw = mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1, &g_tc_status));
+                if (!okw) { alive = false; break; }
                 const typename Loader::Kst ks = ld.k_state(kb, t & 7);
                 const uint32_t dst = raw_s + sr * C::RAW_BYTES;
 #pragma unroll
@@ -239,8 +242,11 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int64_t slot = 0; slot < total; ++slot) {
             const uint32_t sr = (uint32_t)(slot % SR), pr = (uint32_t)((slot / SR) & 1);
             const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
-            if (!mbar_wait(raw_full(sr), pr, abort_flag, 5, &g_tc_status)) break;
-            if (!mbar_wait(a_empty(sa), pa ^ 1, abort_flag, 8, &g_tc_status)) break;
+            bool ok1, ok2; const int ui_t = (int)(slot / KB);
+            TC_TADD(ui_t, 26, ok1 = mbar_wait(raw_full(sr), pr, abort_flag, 5, &g_tc_status));
+            if (!ok1) break;
+            TC_TADD(ui_t, 27, ok2 = mbar_wait(a_empty(sa), pa ^ 1, abort_flag, 8, &g_tc_status));
+            if (!ok2) break;
             tc_fence_after();
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
@@ -307,13 +313,16 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
                 const uint32_t sb = resident ? (uint32_t)kb : (uint32_t)(slot % SB);
                 const uint32_t pb = resident ? 0u : (uint32_t)((slot / SB) & 1);
-                if (!mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status)) { alive = false; break; }
+                bool oka, okb = true;
+                TC_TADD(ui, 24 + 5 * iw, oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status));
+                if (!oka) { alive = false; break; }
                 if (!resident || ui == 0) {
-                    if (!mbar_wait(b_full(sb), pb, abort_flag, 7, &g_tc_status)) { alive = false; break; }
+                    TC_TADD(ui, 25 + 5 * iw, okb = mbar_wait(b_full(sb), pb, abort_flag, 7, &g_tc_status));
+                    if (!okb) { alive = false; break; }
                 }
                 if (lane == 0 && kb == 0 && iw == 0) TC_TRACE(ui, 6);
                 tc_fence_after();
-                if (lane == 0) {
+                TC_TADD(ui, 31 - iw, if (lane == 0) {
                     const uint32_t b_hi = smem_base + sb * C::B_BYTES + b_off;
                     const uint64_t dbh = tc_smem_desc(b_hi), dbl = tc_smem_desc(b_hi + C::B_BYTES / 2);
                     const uint32_t ah0 = tmem_a + sa * MT * 64 + a_off;
@@ -328,7 +337,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     }
                     tc_commit(a_empty(sa));            // A stage reusable once both issuers' MMAs have read it
                     if (!resident) tc_commit(b_empty(sb));
-                }
+                });
                 __syncwarp();
             }
             if (alive && lane == 0) tc_commit(acc_full(buf));
@@ -574,6 +583,7 @@ extern "C" int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, 
 }
 
 #ifdef SPGT_TC_TRACE
+extern "C" int spgt_tc_trace_reset(void) { static long long z[64 * 32] = {}; return cudaMemcpyToSymbol(g_tc_trace, z, sizeof(z)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH; }
 extern "C" int spgt_tc_trace_read(long long* host_out) {   // 64 units x 16 slots of clock64() values of CTA 0
     return cudaMemcpyFromSymbol(host_out, g_tc_trace, sizeof(long long) * 64 * 32) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
 }
