@@ -375,6 +375,8 @@ def main():
         tot = sum(sum(v) for v in tm.values())
         for k, v in sorted(tm.items(), key=lambda kv: -sum(kv[1])):
             print(f'{k:34s} calls {len(v):3d}  total {sum(v):8.3f} ms  {100 * sum(v) / tot:5.1f} %', file=sys.stderr)
+            if len(v) > 1:
+                print('    per call (us): ' + ' '.join(f'{1e3 * t:.0f}' for t in v), file=sys.stderr)
         print(f'{"sum":34s} {tot:8.3f} ms', file=sys.stderr)
 
     cpu = None

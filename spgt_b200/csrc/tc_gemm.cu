@@ -111,7 +111,7 @@ template <int BN, int MT> struct TcCfg {
     static constexpr int SA = (MT == 1) ? 4 : 2;                    // A stages in TMEM, 64 columns (hi|lo) per tile
     static_assert(ACC_COLS + SA * MT * 64 <= 512, "tensor memory budget");
     static constexpr int B_BYTES = 2 * BN * TC_BK * 4;              // W_hi | W_lo image of one k-block
-    static constexpr int SB = (BN == 128) ? (MT == 1 ? 4 : 3) : 6;  // W stages in shared memory
+    static constexpr int SB = (BN == 128) ? (MT == 1 ? 4 : 3) : (MT == 1 ? 8 : 6);  // W stages in shared memory
     static constexpr int RAW_BYTES = MT * TC_BM * TC_BK * 4;        // raw fp32 A tile(s) of one k-block
     static constexpr int SR = (MT == 1) ? 3 : 2;                    // raw A stages in shared memory
     static constexpr int STAGING_BYTES = 32 * TC_EPI_WARPS * TC_SLOT_BYTES;
@@ -138,14 +138,15 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     // barrier slots (8 bytes each)
     auto a_full = [&](int s) { return bars + 8u * s; };                 // [4]
     auto a_empty = [&](int s) { return bars + 8u * (4 + s); };          // [4]
-    auto b_full = [&](int s) { return bars + 8u * (8 + s); };           // [6]
-    auto b_empty = [&](int s) { return bars + 8u * (14 + s); };         // [6]
-    auto acc_full = [&](int b) { return bars + 8u * (20 + b); };        // [2]
-    auto acc_empty = [&](int b) { return bars + 8u * (22 + b); };       // [2]
-    auto raw_full = [&](int s) { return bars + 8u * (24 + s); };        // [3]
-    auto raw_empty = [&](int s) { return bars + 8u * (27 + s); };       // [3]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 256);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 264);
+    auto b_full = [&](int s) { return bars + 8u * (8 + s); };           // [8]
+    auto b_empty = [&](int s) { return bars + 8u * (16 + s); };         // [8]
+    auto acc_full = [&](int b) { return bars + 8u * (24 + b); };        // [2]
+    auto acc_empty = [&](int b) { return bars + 8u * (26 + b); };       // [2]
+    auto raw_full = [&](int s) { return bars + 8u * (28 + s); };        // [3]
+    auto raw_empty = [&](int s) { return bars + 8u * (31 + s); };       // [3]
+    static_assert(SA <= 4 && SB <= 8 && SR <= 3 && NBUF <= 2, "barrier slots");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 288);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 296);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int KB = kpad / TC_BK;
@@ -528,7 +529,15 @@ __global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, i
     }
 }
 
-static int tc_bn_for(int N) { return N <= 32 ? 32 : (N <= 64 ? 64 : 128); }
+// Column tile width.  A 128-wide tile keeps W resident in shared memory only up to K = 128; just above that (the
+// 136-wide merged attention heads) two 64-wide column tiles with W resident beat one 128-wide tile that re-streams W
+// for every row tile, the second read of the rows coming from L2.  At K = 256 the doubled row traffic costs more
+// than the W stream (measured: 0.125 vs 0.094 ms for 180k rows).
+static int tc_bn_for(int N, int K) {
+    if (N <= 32) return 32;
+    if (N <= 64) return 64;
+    return (K > 128 && K <= 192) ? 64 : 128;
+}
 
 template <int BN, int MT, class Loader, int EPI, class EpiParams>
 static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_tiles, const EpiParams& ep, cudaStream_t st) {
@@ -549,7 +558,7 @@ static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_til
 
 template <class Loader>
 static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int rows, const TcLinearEpi& ep, bool long_k, cudaStream_t st) {
-    const int bn = tc_bn_for(N), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
+    const int bn = tc_bn_for(N, K), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
     const int n_tiles = npad / bn;
     if (long_k && bn == 128) return tc_launch<128, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     if (long_k && bn == 64) return tc_launch<64, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
@@ -566,7 +575,7 @@ using namespace spgt;
 
 extern "C" size_t spgt_tc_weight_bytes(int K, int N) {
     if (K <= 0 || N <= 0) return 0;
-    const int bn = tc_bn_for(N);
+    const int bn = tc_bn_for(N, K);
     return (size_t)2 * (ceil_div(N, bn) * bn) * (ceil_div(K, TC_BK) * TC_BK) * sizeof(float);
 }
 
@@ -576,7 +585,7 @@ extern "C" int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, 
     if (K <= 0 || N <= 0 || ldw < N) return SPGT_ERR_SHAPE;
     if (out_bytes < spgt_tc_weight_bytes(K, N)) return SPGT_ERR_WORKSPACE;
     if (!aligned16(out)) return SPGT_ERR_ALIGN;
-    const int bn = tc_bn_for(N), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
+    const int bn = tc_bn_for(N, K), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
     tc_weight_prepare_kernel<<<ceil_div(npad * kpad, 256), 256, 0, (cudaStream_t)stream>>>(w_kn, ldw, K, N, kpad, npad, bn,
                                                                                          (float*)out);
     return launch_status();
