@@ -280,6 +280,7 @@ def main():
     ap.add_argument('--impl', default='spgt_b200', choices=['spgt_b200', 'reference'])
     ap.add_argument('--batch', type=int, default=64, help='samples per GPU per step')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-graphs', action='store_true', help='end-to-end leg launches the kernels eagerly instead of replaying CUDA graphs')
     ap.add_argument('--breakdown', action='store_true', help='also print a per-entry-point time table to stderr')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != 'reference' else args.warmup
@@ -348,7 +349,7 @@ def main():
     value = world * B * args.steps / (elapsed_ms * 1e-3)
 
     # ---------------- end to end through the host-facing API ----------------
-    engine = HostInference(model, device)
+    engine = HostInference(model, device, use_graphs=not args.no_graphs)
     outs = [torch.empty(B, cfg['r_node'], cfg['r_node'], 1, dtype=torch.float32, pin_memory=True) for _ in range(2)]
     engine.run([host] * args.warmup, [outs[i & 1] for i in range(args.warmup)])
     barrier()

@@ -15,17 +15,22 @@ class HostInference:
     Each batch is a dict with float32 tensors 'node' [n,r,r,1], 'position' [n,ra,ra,2], 'grid' [n,r,r,2] in pinned
     host memory; the result for each batch is written into a pinned host tensor [n,r,r,1]."""
 
-    def __init__(self, model, device):
+    def __init__(self, model, device, use_graphs: bool = False):
+        """use_graphs: capture the forward of each staging slot into a CUDA graph on its first use (one batch shape)."""
         self.model, self.device = model, torch.device(device)
         self.copy_in, self.copy_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
         self._slots = [{}, {}]
         self._out_host = {}
+        self.use_graphs = use_graphs
+        self._graphs = [None, None]
+        self._slot_out_done = [None, None]
 
     def _stage(self, slot: Dict, batch: Dict[str, torch.Tensor]):
         for k in ('node', 'position', 'grid'):
             t = batch[k]
             if k not in slot or slot[k].shape != t.shape:
                 slot[k] = torch.empty(t.shape, dtype=torch.float32, device=self.device)
+                slot['fresh'] = True                     # a graph captured on the old buffers is stale
             slot[k].copy_(t, non_blocking=True)
 
     def bytes_per_batch(self, batch) -> Dict[str, int]:
@@ -53,7 +58,17 @@ class HostInference:
                             self.copy_in.wait_event(pending[-1][1])     # slot nxt was read by batch i-1: wait for it
                         self._stage(self._slots[nxt], batches[i + 1])
                         ready[nxt] = self.copy_in.record_event()
-                pred = self.model(slot['node'], slot['position'], slot['grid'])
+                if self.use_graphs:
+                    if slot.pop('fresh', False):
+                        self._graphs[i & 1] = None
+                    if self._graphs[i & 1] is None:
+                        compute.synchronize()        # the capture below warms up on a side stream
+                        self._graphs[i & 1] = GraphedForward(self.model, slot['node'], slot['position'], slot['grid'], own_inputs=False)
+                    if self._slot_out_done[i & 1] is not None:
+                        compute.wait_event(self._slot_out_done[i & 1])   # the captured output buffer is still being downloaded
+                    pred = self._graphs[i & 1](slot['node'], slot['position'], slot['grid'])
+                else:
+                    pred = self.model(slot['node'], slot['position'], slot['grid'])
                 done = compute.record_event()
                 host = outputs[i] if outputs is not None else self._host_out(i, pred.shape)
                 with torch.cuda.stream(self.copy_out):
@@ -61,6 +76,7 @@ class HostInference:
                     host.copy_(pred, non_blocking=True)
                     pred.record_stream(self.copy_out)
                     out_done = self.copy_out.record_event()
+                self._slot_out_done[i & 1] = out_done
                 pending.append((host, done, out_done))
                 results.append(host)
             for _, _, out_done in pending:
@@ -72,3 +88,41 @@ class HostInference:
         if key not in self._out_host:
             self._out_host[key] = torch.empty(shape, dtype=torch.float32, pin_memory=True)
         return self._out_host[key]
+
+
+class GraphedForward:
+    """The forward of one (batch, resolution) shape captured once into a CUDA graph and replayed.
+
+    The reference launches every kernel of every batch from Python (engine/darcy_engine.py:33-46).  Here the ~50
+    launches of a forward are recorded once; a replay costs one launch call, which matters for small batches where
+    the GPU finishes a forward faster than the host can issue it.  Inputs are copied into the captured buffers; the
+    returned prediction is the captured output buffer (valid until the next replay)."""
+
+    def __init__(self, model, node: torch.Tensor, position: torch.Tensor, grid: torch.Tensor, warmup: int = 2,
+                 own_inputs: bool = True):
+        """own_inputs=False captures the given tensors themselves as the graph's input buffers (no copy at replay when
+        the caller refills them in place)."""
+        self.model = model
+        if own_inputs:
+            node, position, grid = node.clone(), position.clone(), grid.clone()
+        self.static_in = {'node': node, 'position': position, 'grid': grid}
+        current = torch.cuda.current_stream(node.device)
+        side = torch.cuda.Stream(node.device)
+        side.wait_stream(current)
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(max(1, warmup)):   # weight images, DFT tables and kernel attributes are set up by the first calls
+                model(self.static_in['node'], self.static_in['position'], self.static_in['grid'])
+        current.wait_stream(side)
+        torch.cuda.synchronize(node.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.static_out = model(self.static_in['node'], self.static_in['position'], self.static_in['grid'])
+
+    def __call__(self, node: torch.Tensor, position: torch.Tensor = None, grid: torch.Tensor = None) -> torch.Tensor:
+        for key, t in (('node', node), ('position', position), ('grid', grid)):
+            if t is not None and t.data_ptr() != self.static_in[key].data_ptr():
+                if t.shape != self.static_in[key].shape:
+                    raise ValueError(f'{key}: shape {tuple(t.shape)} differs from the captured {tuple(self.static_in[key].shape)}')
+                self.static_in[key].copy_(t, non_blocking=True)
+        self.graph.replay()
+        return self.static_out

@@ -97,3 +97,72 @@ def test_full_size_model_against_oracle(sub_node, sub_attn, batch):
     for i in range(6):
         assert rel_l2(taps[f'enc{i}'].reshape(-1), ref_taps[f'enc{i}'].reshape(-1)) < (i + 1) * PER_LAYER_TOL, i
     assert rel_l2(out, ref) < MODEL_TOL
+
+
+def _random_model(sub_node, sub_attn, modes, seed):
+    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+    from spgt_b200.config.config_accessor import get_darcy_config
+    from spgt_b200.dataset.darcy_dataset import GaussNormalizer
+    cfg = get_darcy_config(sub_node, sub_attn, num_frequence_mode=modes, clamp_attn=False)
+    cfg['target_normalizer'] = GaussNormalizer()
+    torch.manual_seed(seed)
+    model = Sp_GalerkinTransformer2D(cfg).eval()
+    with torch.no_grad():
+        for n, prm in model.named_parameters():
+            if 'fourier_weight' in n:
+                prm.mul_(30.0)
+    return cfg, model
+
+
+def test_super_resolution_shape_against_oracle():
+    """Full resolution r = 421 (the reference's super-resolution evaluation grid), attention grid 106^2 = 11236 nodes,
+    15 Fourier modes, batch 1, vs the fp32 CPU oracle."""
+    from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
+    cfg, model = _random_model(1, 4, 15, seed=11)
+    data = synthetic_darcy_batch(range(1), 421, 1, 4, seed=11)
+    ocfg = O.default_config(421, 1, 4, 15)
+    assert tuple(ocfg['resolution_size']) == tuple(cfg['resolution_size'])
+    p = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    ref = O.model_forward(data['node'], data['position'], data['grid'], p, ocfg)
+    out = model.cuda()(data['node'].cuda(), data['position'].cuda(), data['grid'].cuda())
+    assert out.shape == (1, 421, 421, 1)
+    assert rel_l2(out, ref) < MODEL_TOL
+
+
+def test_graph_captured_forward_is_bit_identical():
+    """A forward captured into a CUDA graph replays to exactly the eager result, also for new inputs."""
+    from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
+    from spgt_b200.engine.darcy_engine import GraphedForward
+    cfg, model = _random_model(3, 10, 12, seed=5)
+    model = model.cuda()
+    a = {k: v.cuda() for k, v in synthetic_darcy_batch(range(2), 421, 3, 10, seed=5).items()}
+    b = {k: v.cuda() for k, v in synthetic_darcy_batch(range(2, 4), 421, 3, 10, seed=5).items()}
+    with torch.no_grad():
+        eager_a = model(a['node'], a['position'], a['grid']).clone()
+        eager_b = model(b['node'], b['position'], b['grid']).clone()
+        graphed = GraphedForward(model, a['node'], a['position'], a['grid'])
+        assert torch.equal(graphed(a['node']), eager_a)
+        assert torch.equal(graphed(b['node'], b['position'], b['grid']), eager_b)
+        assert torch.equal(graphed(a['node']), eager_a)
+    with pytest.raises(ValueError):
+        graphed(a['node'][:1])
+
+
+def test_host_inference_with_and_without_graphs_agree():
+    """The host-facing loop (pinned batches in, pinned predictions out) gives the same bits eagerly and with replayed graphs."""
+    from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
+    from spgt_b200.engine.darcy_engine import HostInference
+    cfg, model = _random_model(3, 10, 12, seed=6)
+    model = model.cuda()
+    batches = []
+    for i in range(5):
+        d = synthetic_darcy_batch(range(2 * i, 2 * i + 2), 421, 3, 10, seed=6)
+        batches.append({k: d[k].pin_memory() for k in ('node', 'position', 'grid')})
+    with torch.no_grad():
+        eager = [t.clone() for t in HostInference(model, 'cuda:0').run(batches)]
+        graphed = [t.clone() for t in HostInference(model, 'cuda:0', use_graphs=True).run(batches)]
+        direct = model(batches[3]['node'].cuda(), batches[3]['position'].cuda(), batches[3]['grid'].cuda()).cpu()
+    assert len(eager) == len(graphed) == 5
+    for a, b in zip(eager, graphed):
+        assert torch.equal(a, b)
+    assert torch.equal(eager[3], direct)
