@@ -106,6 +106,17 @@ int spgt_batched_skinny_gemm_noalloc(const float* A, const float* B, float* C, f
                                      int batch, spgt_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Validation metric (reference: engine/metric.py:47-67, WeightedL2Loss2D with alpha = 0, beta = 1)
+ * ------------------------------------------------------------------------------------------- */
+
+/* per_sample[n] = sqrt( mean((pred[n] - target[n])^2) / (mean(target[n]^2) + eps) ) over n_per_sample elements of
+ * each of the N samples (dense, sample-major).  The reference reduces these per-sample values with a mean ('L1'),
+ * sqrt of the mean of squares ('L2') or max ('Linf'); that reduction over N numbers is left to the caller.
+ * One block per sample, fixed summation order. */
+int spgt_relative_l2_fwd(const float* pred, const float* target, float* per_sample, int N, int64_t n_per_sample,
+                         float eps, spgt_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Data-movement ops (reference: extension/bind/datamove.{py,cu}, extension/native/datamove.cu)
  * ------------------------------------------------------------------------------------------- */
 

@@ -146,6 +146,17 @@ def galerkin_attention(Q: Tensor, K: Tensor, V: Tensor, merged_heads: bool = Fal
     return (out, T) if return_kv else out
 
 
+def relative_l2(pred: Tensor, target: Tensor, eps: float = 1.0e-10) -> Tensor:
+    """Per-sample relative L2 error of [N, ...] tensors (engine/metric.py:47-67 of the reference): [N]."""
+    pred, target = _chk(pred.contiguous(), 'pred'), _chk(target.contiguous(), 'target')
+    if pred.shape != target.shape:
+        raise ValueError('pred and target must have the same shape')
+    N = pred.shape[0]
+    out = torch.empty(N, dtype=torch.float32, device=pred.device)
+    _call('spgt_relative_l2_fwd', pred.data_ptr(), target.data_ptr(), out.data_ptr(), N, pred.numel() // N, float(eps), _stream())
+    return out
+
+
 def skinny_gemm_workspace_bytes(M: int, N: int, K: int, batch: int) -> int:
     return int(lib.spgt_skinny_gemm_workspace_bytes(M, N, K, batch))
 

@@ -277,3 +277,23 @@ def test_error_codes_do_not_launch(dev):
     assert lib.spgt_galerkin_attn_fwd(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), None, 1, 1, 40, 8, 0, None) == -2
     assert lib.spgt_batched_skinny_gemm(x.data_ptr(), x.data_ptr(), x.data_ptr(), 1.0, 8, 8, 16, 1, None, 0, None) == -4
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize('N,r', [(1, 1), (3, 17), (8, 211)])
+def test_relative_l2_metric_kernel(dev, N, r):
+    """spgt_relative_l2_fwd against the reference's formula (engine/metric.py:47-67, alpha = 0) in fp64."""
+    from spgt_b200 import ops
+    from spgt_b200.engine.metric import relative_l2_metric, relative_l2_sums
+    g = torch.Generator().manual_seed(N * 100 + r)
+    t = torch.randn(N, r, r, 1, generator=g)
+    p = t + 0.1 * torch.randn(N, r, r, 1, generator=g)
+    td, pd = t.double().squeeze(-1), p.double().squeeze(-1)
+    ref = ((pd - td).pow(2).mean(dim=[1, 2]) / (td.pow(2).mean(dim=[1, 2]) + 1e-10)).sqrt()
+    got = ops.relative_l2(p.to(dev), t.to(dev))
+    assert got.shape == (N,)
+    assert rel_l2(got, ref) < PER_LAYER_TOL
+    assert torch.equal(got, ops.relative_l2(p.to(dev), t.to(dev)))
+    assert abs(float(relative_l2_metric(p.to(dev), t.to(dev))) - float(ref.mean())) < 1e-5 * float(ref.mean())
+    s, c = relative_l2_sums(p.to(dev), t.to(dev))
+    assert float(c) == N and abs(float(s) - float(ref.sum())) < 1e-5 * float(ref.sum())
+    assert abs(float(relative_l2_metric(p, t)) - float(ref.mean())) < 1e-5 * float(ref.mean())      # host tensors: torch formula
