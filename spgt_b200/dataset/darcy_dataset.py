@@ -77,3 +77,76 @@ def synthetic_darcy_batch(indices, fine_resolution: int, sub_node: int, sub_attn
         node=torch.from_numpy(node.astype(np.float32)), coeff=torch.from_numpy(a),
         position=torch.from_numpy(np.broadcast_to(pos, (n, *pos.shape)).copy()),
         grid=torch.from_numpy(np.broadcast_to(grid, (n, *grid.shape)).copy()))
+
+
+def central_diff(X: np.ndarray, S: int):
+    """Central differences of [N, S, S] fields with zero padding, scaled by S (dataset/darcy_dataset.py:146-154)."""
+    X = np.pad(X, pad_width=[(0, 0), (1, 1), (1, 1)], mode='constant', constant_values=0)
+    grad_x = (X[:, 2:, 1:-1] - X[:, :-2, 1:-1]) / 2
+    grad_y = (X[:, 1:-1, 2:] - X[:, 1:-1, :-2]) / 2
+    return grad_x * S, grad_y * S
+
+
+class DarcyDataset(torch.utils.data.Dataset):
+    """The reference's Darcy dataset (dataset/darcy_dataset.py:48-175) for the inference path: coefficient `a` and
+    solution `u` of shape [N, R, R] from a .mat file, every sub-th node kept, the coefficient normalised per node.
+
+    Items are dicts of float32 tensors: grid [r,r,2], position [r_attn,r_attn,2], coeff [r,r,1] (raw coefficient),
+    node [r,r,1] (normalised), target [r,r,1], target_grad [r,r,2].  Training sets take the first num_data samples
+    and fit the normalisers; validation sets take the last num_data samples and need the training node_normalizer."""
+
+    def __init__(self, datapath, subsample_node, subsample_attn=None, num_data=None, fine_resolution=None,
+                 is_training=True, is_return_boundary=True, is_normalization=True, node_normalizer: GaussNormalizer = None,
+                 noise=0.0, random_seed=1127802, keys=('a', 'u')) -> None:
+        super().__init__()
+        from .data_accessor import read_matfile
+        self.datapath, self.is_training = datapath, is_training
+        self.subsample_node = subsample_node
+        self.subsample_attn = subsample_attn if subsample_attn is not None else 2 * subsample_node
+        self.is_return_boundary, self.is_normalization = is_return_boundary, is_normalization
+        self.node_normalizer, self.target_normalizer = node_normalizer, None
+        a, u = read_matfile(datapath, list(keys), [np.float32, np.float32])
+        N, R, _ = a.shape
+        self.num_data = num_data if num_data is not None else N
+        self.fine_resolution = fine_resolution if fine_resolution is not None else R
+        if is_training:
+            a, u = a[:self.num_data], u[:self.num_data]
+        else:
+            a, u = a[-self.num_data:], u[-self.num_data:]
+        sub = self.subsample_node
+        r = int((R - 1) / sub + 1)
+        n = a.shape[0]
+        self.grid = meshgrid(R, sub, is_return_boundary)
+        self.position = meshgrid(R, self.subsample_attn, True)
+        nodes = a[:, ::sub, ::sub].reshape(n, r, r, 1)
+        self.targets = u[:, ::sub, ::sub].reshape(n, r, r, 1)
+        gx, gy = central_diff(u, R)
+        self.targets_grad = np.stack([gx[:, ::sub, ::sub], gy[:, ::sub, ::sub]], axis=-1).reshape(n, r, r, 2)
+        self.coeffs = np.copy(nodes)
+        if is_normalization:
+            if is_training:
+                self.node_normalizer = GaussNormalizer(nodes)
+                self.target_normalizer = GaussNormalizer(self.targets if is_return_boundary else self.targets[:, 1:-1, 1:-1, :])
+            elif self.node_normalizer is None:
+                raise ValueError('a validation set needs the node_normalizer fitted on the training set')
+            nodes = self.node_normalizer.transform(nodes)
+        if noise > 0.0:
+            nodes = nodes + noise * np.random.default_rng(random_seed).standard_normal(nodes.shape)
+        self.nodes = nodes
+
+    def __len__(self):
+        return self.num_data
+
+    def __getitem__(self, index) -> dict:
+        return dict(
+            grid=torch.from_numpy(self.grid).float(), position=torch.from_numpy(self.position).float(),
+            coeff=torch.from_numpy(self.coeffs[index]).float(), node=torch.from_numpy(np.asarray(self.nodes[index])).float(),
+            target=torch.from_numpy(self.targets[index]).float(), target_grad=torch.from_numpy(self.targets_grad[index]).float())
+
+    def batches(self, batch_size: int, pin_memory: bool = False):
+        """Consecutive batches in the layout HostInference takes (grid and position repeated per sample)."""
+        for s in range(0, len(self), batch_size):
+            idx = range(s, min(s + batch_size, len(self)))
+            items = [self[i] for i in idx]
+            batch = {k: torch.stack([it[k] for it in items]) for k in items[0]}
+            yield {k: (v.pin_memory() if pin_memory else v) for k, v in batch.items()}

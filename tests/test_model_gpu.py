@@ -166,3 +166,38 @@ def test_host_inference_with_and_without_graphs_agree():
     for a, b in zip(eager, graphed):
         assert torch.equal(a, b)
     assert torch.equal(eager[3], direct)
+
+
+def test_real_data_inference_driver(tmp_path):
+    """run/darcy_inference.py on a small generated .mat file with a saved checkpoint: metric vs the CPU oracle."""
+    import numpy as np
+    from scipy.io import savemat
+    from spgt_b200.config.config_accessor import get_darcy_config
+    from spgt_b200.dataset.darcy_dataset import DarcyDataset
+    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+    from spgt_b200.run.darcy_inference import darcy_inference
+    R, n = 85, 7
+    rng = np.random.default_rng(8)
+    a = np.where(rng.standard_normal((n, R, R)) >= 0, 12.0, 3.0)
+    u = rng.standard_normal((n, R, R)) * 0.01
+    path = str(tmp_path / 'darcy_small.mat')
+    savemat(path, {'a': a, 'u': u})
+    cfg = get_darcy_config(3, 6, num_frequence_mode=4, clamp_attn=False, fine_resolution=R, batch_size=1, num_data=5)
+    torch.manual_seed(3)
+    ckpt = {'Module': Sp_GalerkinTransformer2D(dict(cfg, target_normalizer=None)).state_dict()}
+    torch.save(ckpt, str(tmp_path / 'm.pt'))
+    ckpt = torch.load(str(tmp_path / 'm.pt'), map_location='cpu')
+    metric = darcy_inference(cfg, ckpt, path, path, use_graphs=True)
+    # oracle: same normalisers, same batches of 2, mean over batches of the per-batch mean relative L2
+    train = DarcyDataset(path, 3, is_training=True)
+    valid = DarcyDataset(path, 3, 6, 5, R, is_training=False, node_normalizer=train.node_normalizer)
+    ocfg = O.default_config(R, 3, 6, 4)
+    ocfg['target_std'] = torch.from_numpy(np.asarray(train.target_normalizer.std)).float()
+    ocfg['target_mean'] = torch.from_numpy(np.asarray(train.target_normalizer.mean)).float()
+    total, nb = 0.0, 0
+    for b in valid.batches(2):
+        pred = O.model_forward(b['node'], b['position'], b['grid'], ckpt['Module'], ocfg)
+        total += float(O.relative_l2_metric(pred, b['target']))
+        nb += 1
+    assert nb == 3
+    assert abs(metric - total / nb) < 1e-4 * (total / nb)
