@@ -44,17 +44,7 @@ def import_reference(ref_path: str):
     return ref_layer, ref_model, get_resolution_size, GaussNormalizer, DarcyDataset
 
 
-def gt_to_spgt_state(sd: dict) -> dict:
-    """GT state_dict -> SpGT conventions: Q/K/V weights transposed, fourier weights [m,m,in,out,2]."""
-    out = {}
-    for k, v in sd.items():
-        v = v.detach().clone()
-        if k.split('.')[-1] in ('weight_Q', 'weight_K', 'weight_V'):
-            v = v.t().contiguous()
-        if 'fourier_weight' in k:
-            v = v.permute(2, 3, 0, 1, 4).contiguous()
-        out[k] = v
-    return out
+from spgt_b200.common.checkpoint import gt_to_spgt_state  # noqa: E402  (GT -> SpGT parameter layouts)
 
 
 def ref_config(oracle_cfg: dict, normalizer) -> dict:

@@ -90,3 +90,26 @@ def test_synthetic_fields_are_index_deterministic():
     assert a['position'].shape == (2, 15, 15, 2) and a['grid'].shape == (2, 29, 29, 2)
     n = GaussNormalizer()
     assert float(n.inverse_transform(torch.tensor(2.0))) == 2.0 * (1.0 + 1e-5)
+
+
+def test_checkpoint_conversion_roundtrip_and_shapes():
+    """GT <-> SpGT state dicts: Q/K/V transposed, Fourier weights permuted, everything else untouched; a round trip is exact."""
+    import torch
+    from spgt_b200.common.checkpoint import gt_to_spgt_state, spgt_to_gt_state
+    from spgt_b200.config.config_accessor import get_darcy_config
+    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+    torch.manual_seed(0)
+    sp = Sp_GalerkinTransformer2D(get_darcy_config(3, 10, num_frequence_mode=12)).state_dict()
+    gt = spgt_to_gt_state(sp)
+    assert gt.keys() == sp.keys()
+    back = gt_to_spgt_state(gt)
+    for k in sp:
+        assert torch.equal(back[k], sp[k]), k
+        last = k.split('.')[-1]
+        if last in ('weight_Q', 'weight_K', 'weight_V'):
+            assert torch.equal(gt[k], sp[k].t())
+        elif 'fourier_weight' in k:
+            assert gt[k].shape == (32, 32, 12, 12, 2) and sp[k].shape == (12, 12, 32, 32, 2)
+            assert torch.equal(gt[k][3, 5, 7, 2], sp[k][7, 2, 3, 5])
+        else:
+            assert torch.equal(gt[k], sp[k])
