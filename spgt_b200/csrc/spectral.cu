@@ -18,20 +18,22 @@ namespace spgt {
 constexpr int SP_C = 32;         // channel width handled by the tensor-core kernels
 constexpr int SP_WARPS = 4;
 constexpr int SP_YB = 32;        // y rows per staged chunk
-constexpr int SP_F1P = 40;       // pitch of F1T rows (j), == 8 (mod 32)
+// pitch of the F1T rows (j): the smallest value >= JP that is 8 or 24 (mod 32), so B-fragment loads are conflict-free
+__host__ __device__ constexpr int sp_f1p(int jp) { return jp <= 8 ? 8 : (jp <= 24 ? 24 : 40); }
 constexpr int SP_XP1 = 40;       // S1: X chunk pitch (A operand read M-contiguous), == 8 (mod 32)
 constexpr int SP_XP3 = 36;       // S3: X chunk pitch (A operand read K-contiguous), == 4 (mod 32)
 constexpr int SP_PP = 40;        // S3: P row-block pitch and Wr pitch (B operands), == 8 (mod 32)
 
 struct SpecTables {              // offsets in floats into the table buffer
-    int r, m, J, JP, RY, F3P;
+    int r, m, J, JP, RY, F3P, F1P;
     int f1t, f3, gr, gi, total;
 };
 __host__ __device__ inline SpecTables spec_tables(int r, int m) {
     SpecTables t;
     t.r = r; t.m = m; t.J = 2 * m; t.JP = (2 * m + 7) / 8 * 8; t.RY = (r + SP_YB - 1) / SP_YB * SP_YB; t.F3P = t.JP + 4;
+    t.F1P = sp_f1p(t.JP);
     t.f1t = 0;
-    t.f3 = t.f1t + t.RY * SP_F1P;
+    t.f3 = t.f1t + t.RY * t.F1P;
     t.gr = t.f3 + t.RY * t.F3P;
     t.gi = t.gr + t.J * r;
     t.total = (t.gi + t.J * r + 3) / 4 * 4;
@@ -46,7 +48,7 @@ __global__ void spectral_tables_kernel(float* tab, int r, int m) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         float v = 0.0f;
         if (i < T.f3) {                                        // F1T[y][j]
-            const int y = i / SP_F1P, j = i % SP_F1P;
+            const int y = i / T.F1P, j = i % T.F1P;
             if (y < r && j < T.J) {
                 const int ky = j < m ? j : j - m;
                 double s, c;
@@ -80,14 +82,15 @@ __global__ void spectral_tables_kernel(float* tab, int r, int m) {
 // One warp per row at a time; y is streamed in chunks of 32 rows through a private double buffer.
 // ------------------------------------------------------------------------------------------------------------
 template <int NT>
-__global__ void __launch_bounds__(SP_WARPS * 32, 2)
+__global__ void __launch_bounds__(SP_WARPS * 32, 3)
 spectral_fwd_y_kernel(const float* __restrict__ X, const float* __restrict__ tab, float* __restrict__ Y1, int r, int m,
                       int64_t nrows) {
     extern __shared__ __align__(16) float smem[];
     const SpecTables T = spec_tables(r, m);
     float* f1 = smem;                                           // [RY][40]
-    float* wbuf = smem + T.RY * SP_F1P + (threadIdx.x >> 5) * (2 * SP_YB * SP_XP1);
-    for (int i = threadIdx.x; i < T.RY * SP_F1P; i += blockDim.x) f1[i] = __ldg(tab + T.f1t + i);
+    constexpr int F1P = sp_f1p(8 * NT);
+    float* wbuf = smem + T.RY * F1P + (threadIdx.x >> 5) * (2 * SP_YB * SP_XP1);
+    for (int i = threadIdx.x; i < T.RY * F1P; i += blockDim.x) f1[i] = __ldg(tab + T.f1t + i);
     __syncthreads();
 
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -126,7 +129,7 @@ spectral_fwd_y_kernel(const float* __restrict__ X, const float* __restrict__ tab
                     for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.0f;
         }
         const float* xs = wbuf + (it & 1) * SP_YB * SP_XP1;
-        const float* fs = f1 + chunk * SP_YB * SP_F1P;
+        const float* fs = f1 + chunk * SP_YB * F1P;
 #pragma unroll
         for (int k8 = 0; k8 < SP_YB / 8; ++k8) {
             const int kk = k8 * 8 + t;
@@ -142,9 +145,9 @@ spectral_fwd_y_kernel(const float* __restrict__ X, const float* __restrict__ tab
             uint32_t bhi[NT][2], blo[NT][2];
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const float* p = fs + kk * SP_F1P + 8 * j + g;         // B[k=y][n=j]
+                const float* p = fs + kk * F1P + 8 * j + g;             // B[k=y][n=j]
                 split_tf32(p[0], bhi[j][0], blo[j][0]);
-                split_tf32(p[4 * SP_F1P], bhi[j][1], blo[j][1]);
+                split_tf32(p[4 * F1P], bhi[j][1], blo[j][1]);
             }
 #pragma unroll
             for (int i = 0; i < 2; ++i)
@@ -618,11 +621,11 @@ template <int NT>
 static int launch_fwd_y(const float* x, const float* tab, float* y1, int r, int m, int64_t nrows, cudaStream_t st) {
     static size_t configured = 0;
     const SpecTables T = spec_tables(r, m);
-    const size_t smem = ((size_t)T.RY * SP_F1P + (size_t)SP_WARPS * 2 * SP_YB * SP_XP1) * sizeof(float);
+    const size_t smem = ((size_t)T.RY * T.F1P + (size_t)SP_WARPS * 2 * SP_YB * SP_XP1) * sizeof(float);
     if (smem > 200 * 1024) return SPGT_ERR_SHAPE;
     if (int e = set_smem_once(spectral_fwd_y_kernel<NT>, smem, configured)) return e;
     const int64_t want = ceil_div(nrows, (int64_t)SP_WARPS);
-    const int64_t cap = (int64_t)num_sms() * 2;
+    const int64_t cap = (int64_t)num_sms() * (smem <= 74 * 1024 ? 3 : 2);
     spectral_fwd_y_kernel<NT><<<(unsigned)(want < cap ? want : cap), SP_WARPS * 32, smem, st>>>(x, tab, y1, r, m, nrows);
     return launch_status();
 }
