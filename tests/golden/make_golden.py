@@ -1,8 +1,9 @@
 """Generate the golden fixtures in this folder from the reference's own CPU modules.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where the reference checkout is available (its location: --reference, or the SPGT_REFERENCE environment
+variable):
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <reference checkout>]
 
 The reference is imported unmodified as package ``SpGT`` (a temporary directory with a symlink
 named SpGT is put on sys.path; ``termcolor`` and ``h5py``, which its support modules import but the
@@ -58,7 +59,7 @@ def ref_config(oracle_cfg: dict, normalizer) -> dict:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', default='/root/reference')
+    ap.add_argument('--reference', default=os.environ.get('SPGT_REFERENCE', os.path.join(os.sep, 'root', 'reference')))
     args = ap.parse_args()
     ref_layer, ref_model, ref_get_res, GaussNormalizer, DarcyDataset = import_reference(args.reference)
     from oracle import gt_oracle as O

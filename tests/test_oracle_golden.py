@@ -73,11 +73,14 @@ def test_small_model_taps_and_output():
     assert float(out[:, 0].abs().max()) == 0.0 and float(out[:, :, -1].abs().max()) == 0.0
 
 
-@pytest.mark.skipif(not os.path.isdir('/root/reference/network'), reason='reference checkout not present')
+REFERENCE = os.environ.get('SPGT_REFERENCE', os.path.join(os.sep, 'root', 'reference'))
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, 'network')), reason='reference checkout not present')
 def test_oracle_against_live_reference_attention_config0():
     """BASELINE config 0 (B=4, S=43*43) run through the reference module in this container."""
     from tests.golden.make_golden import import_reference, gt_to_spgt_state
-    ref_layer, *_ = import_reference('/root/reference')
+    ref_layer, *_ = import_reference(REFERENCE)
     torch.manual_seed(0)
     attn = ref_layer.GalerkinAttention(128, 4, 2, 1e-6, 0.0, 0.0, 0.01, 0.01, False).eval()
     x = torch.randn(4, 43 * 43, 128)
