@@ -33,15 +33,25 @@ constexpr int TC_SLOT_BYTES = 144;            // per-epilogue-thread staging row
 __device__ int g_tc_status = 0;          // 0 = ok; otherwise the code of the first wait that gave up
 
 #ifdef SPGT_TC_TRACE                      // developer build only: per-unit timestamps of CTA 0 (see spgt_tc_trace_read)
-__device__ long long g_tc_trace[64 * 32];
+__device__ long long g_tc_trace[64 * 32 + 32 * 8];   // per-unit time stamps of CTA 0, then 8 cycle counters per warp
 #define TC_TRACE(unit_i, slot) do { if (blockIdx.x == 0 && (unit_i) < 64) g_tc_trace[(unit_i) * 32 + (slot)] = clock64(); } while (0)
-#define TC_TADD(unit_i, slot, ...) do { const long long t_ = clock64(); __VA_ARGS__; if (blockIdx.x == 0 && (unit_i) < 64 && (threadIdx.x & 31) == 0) g_tc_trace[(unit_i) * 32 + (slot)] += clock64() - t_; } while (0)
+#define TC_TADD(unit_i, slot, ...) do { const long long t_ = clock64(); __VA_ARGS__; tc_acc[(slot) & 7] += clock64() - t_; } while (0)
+#define TC_ACC_DECL long long tc_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long tc_t0 = clock64();
+#define TC_ACC_FLUSH do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { for (int k_ = 0; k_ < 7; ++k_) g_tc_trace[64 * 32 + (threadIdx.x >> 5) * 8 + k_] = tc_acc[k_]; g_tc_trace[64 * 32 + (threadIdx.x >> 5) * 8 + 7] = clock64() - tc_t0; } } while (0)
 #else
 #define TC_TADD(unit_i, slot, ...) do { __VA_ARGS__; } while (0)
+#define TC_ACC_DECL
+#define TC_ACC_FLUSH do { } while (0)
 #define TC_TRACE(unit_i, slot) do { } while (0)
 #endif
 
 __host__ __device__ constexpr int tc_cols_per_thread(int bn, int mt) { return mt == 1 ? bn / 2 : bn; }
+
+// Position in a ring of N stages: stage index and the parity of the pass, advanced without division.
+struct TcRing {
+    uint32_t s = 0, ph = 0;
+    template <int N> __device__ __forceinline__ void next() { if (++s == (uint32_t)N) { s = 0; ph ^= 1u; } }
+};
 
 // ---- A-operand loaders.  A loader thread copies 16-byte chunk (t & 7) of rows (t >> 3) + 16 i of every tile:
 // per-row state is computed once per work unit, per-k-block state once per k-block.
@@ -149,6 +159,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 296);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    TC_ACC_DECL
     const int KB = kpad / TC_BK;
     const bool resident = KB <= SB;          // the whole column tile of W stays in shared memory
 
@@ -202,7 +213,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
 #pragma unroll
         for (int i = 0; i < 8; ++i) aoff[i] = tc_swz((t >> 3) + 16 * i, t & 7);
         const uint32_t raw_s = smem_u32(raw);
-        int64_t slot = 0;
+        TcRing rr;
         bool alive = true;
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const int row0 = (u0 + ui * ctas_per_nt) * MT * TC_BM + (t >> 3);
@@ -211,8 +222,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) rs[m][i] = ld.row_state(row0 + m * TC_BM + 16 * i);
-            for (int kb = 0; kb < KB; ++kb, ++slot) {
-                const uint32_t sr = (uint32_t)(slot % SR), ph = (uint32_t)((slot / SR) & 1);
+            for (int kb = 0; kb < KB; ++kb, rr.template next<SR>()) {
+                const uint32_t sr = rr.s, ph = rr.ph;
                 bool okw; TC_TADD(ui, 28, okw = mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1, &g_tc_status));
                 if (!okw) { alive = false; break; }
                 const typename Loader::Kst ks = ld.k_state(kb, t & 7);
@@ -240,10 +251,11 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
 #pragma unroll
         for (int c = 0; c < 8; ++c) roff[c] = tc_swz(r, c);
         const int64_t total = (int64_t)n_my_units * KB;
-        for (int64_t slot = 0; slot < total; ++slot) {
-            const uint32_t sr = (uint32_t)(slot % SR), pr = (uint32_t)((slot / SR) & 1);
-            const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
-            bool ok1, ok2; const int ui_t = (int)(slot / KB);
+        TcRing rr, ra;
+        for (int64_t slot = 0; slot < total; ++slot, rr.template next<SR>(), ra.template next<SA>()) {
+            const uint32_t sr = rr.s, pr = rr.ph;
+            const uint32_t sa = ra.s, pa = ra.ph;
+            bool ok1, ok2; const int ui_t = 0;
             TC_TADD(ui_t, 26, ok1 = mbar_wait(raw_full(sr), pr, abort_flag, 5, &g_tc_status));
             if (!ok1) break;
             TC_TADD(ui_t, 27, ok2 = mbar_wait(a_empty(sa), pa ^ 1, abort_flag, 8, &g_tc_status));
@@ -279,10 +291,13 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         if (lane == 0 && n_my_units > 0) {
             const uint32_t bytes = C::B_BYTES;
             const int64_t total = resident ? KB : (int64_t)n_my_units * KB;
-            for (int64_t slot = 0; slot < total; ++slot) {
-                const uint32_t sb = (uint32_t)(slot % SB), ph = (uint32_t)((slot / SB) & 1);
+            TcRing rb;
+            int kbw = 0;
+            for (int64_t slot = 0; slot < total; ++slot, rb.template next<SB>()) {
+                const uint32_t sb = rb.s, ph = rb.ph;
                 if (!mbar_wait(b_empty(sb), ph ^ 1, abort_flag, 6, &g_tc_status)) break;
-                const int kb = (int)(slot % KB);
+                const int kb = kbw;
+                if (++kbw == KB) kbw = 0;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(sb)), "r"(bytes) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                              ::"r"(smem_base + sb * C::B_BYTES), "l"(wtile + (int64_t)kb * (C::B_BYTES / 4)), "r"(bytes), "r"(b_full(sb)) : "memory");
@@ -301,7 +316,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         const uint32_t d_off = (MT == 2) ? (uint32_t)(iw * BN) : (uint32_t)(iw * NI);
         const uint32_t a_off = (MT == 2) ? (uint32_t)(iw * 64) : 0u;
         const uint32_t b_off = (MT == 2) ? 0u : (uint32_t)(iw * NI * 128);   // NI rows of 128 bytes
-        int64_t slot = 0;
+        TcRing ra, rb;
         bool alive = true;
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
@@ -310,10 +325,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             if (lane == 0 && iw == 0) TC_TRACE(ui, 5);
             tc_fence_after();
             const uint32_t d = tmem_base + buf * MT * BN + d_off;
-            for (int kb = 0; kb < KB; ++kb, ++slot) {
-                const uint32_t sa = (uint32_t)(slot % SA), pa = (uint32_t)((slot / SA) & 1);
-                const uint32_t sb = resident ? (uint32_t)kb : (uint32_t)(slot % SB);
-                const uint32_t pb = resident ? 0u : (uint32_t)((slot / SB) & 1);
+            for (int kb = 0; kb < KB; ++kb, ra.template next<SA>(), rb.template next<SB>()) {
+                const uint32_t sa = ra.s, pa = ra.ph;
+                const uint32_t sb = resident ? (uint32_t)kb : rb.s;
+                const uint32_t pb = resident ? 0u : rb.ph;
                 bool oka, okb = true;
                 TC_TADD(ui, 24 + 5 * iw, oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status));
                 if (!oka) { alive = false; break; }
@@ -499,6 +514,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             if (epi_idx == 0) TC_TRACE(ui, 10);
         }
     }
+    TC_ACC_FLUSH;
     // teardown: everyone meets, then the allocating warp frees the tensor memory
     tc_fence_before();
     __syncthreads();
@@ -592,9 +608,9 @@ extern "C" int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, 
 }
 
 #ifdef SPGT_TC_TRACE
-extern "C" int spgt_tc_trace_reset(void) { static long long z[64 * 32] = {}; return cudaMemcpyToSymbol(g_tc_trace, z, sizeof(z)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH; }
+extern "C" int spgt_tc_trace_reset(void) { static long long z[64 * 32 + 32 * 8] = {}; return cudaMemcpyToSymbol(g_tc_trace, z, sizeof(z)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH; }
 extern "C" int spgt_tc_trace_read(long long* host_out) {   // 64 units x 16 slots of clock64() values of CTA 0
-    return cudaMemcpyFromSymbol(host_out, g_tc_trace, sizeof(long long) * 64 * 32) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
+    return cudaMemcpyFromSymbol(host_out, g_tc_trace, sizeof(long long) * (64 * 32 + 32 * 8)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
 }
 #endif
 
