@@ -218,6 +218,11 @@ def micro_cases(device):
         return fn, B * S * (128 + 256 + 256 + 128 + 128) * 4, 2 * 2 * B * S * 128 * 256
     cases['ffn_tc'] = ffn_tc
 
+    def ffn_fused(B=64, S=2809):
+        x, w1, b1, w2, b2 = rnd(B * S, 128), ops.TcWeight(rnd(128, 256) / 11), rnd(256), ops.TcWeight(rnd(256, 128) / 16), rnd(128)
+        return (lambda: ops.ffn_tc(x, w1, b1, w2, b2, 'relu', x)), B * S * (128 + 128 + 128) * 4, 2 * 2 * B * S * 128 * 256
+    cases['ffn_fused'] = ffn_fused
+
     def lin_tc(B=64, S=2809, K=128, N=128):
         x, w, b_ = rnd(B * S, K), ops.TcWeight(rnd(K, N) / 11), rnd(N)
         return (lambda: ops.linear_tc(x, w, b_, None)), B * S * (K + N) * 4, 2 * B * S * K * N

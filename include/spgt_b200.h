@@ -206,6 +206,12 @@ int spgt_tc_status(void);
 /* As spgt_linear_fwd with wprep = spgt_tc_weight_prepare(w, ...). */
 int spgt_linear_tc_fwd(const float* x, int lda, const void* wprep, const float* bias, const float* residual, int ldr,
                        float* y, int ldc, int rows, int K, int N, int act, spgt_stream_t stream);
+/* y = act(x W1 + b1) W2 + b2 (+ residual) with x [rows, D = 128], W1 [128, 256], W2 [256, 128] prepared by
+ * spgt_tc_weight_prepare: both GEMMs of FeedForward.forward (network/layer.py:155-174) in one kernel, the hidden
+ * activations stay in tensor memory.  Only D = 128, Hd = 256 is supported (SPGT_ERR_SHAPE otherwise). */
+int spgt_ffn_tc_fwd(const float* x, int lda, const void* w1prep, const float* b1, const void* w2prep, const float* b2,
+                    const float* residual, int ldr, float* y, int ldc, int rows, int D, int Hd, int act, spgt_stream_t stream);
+
 /* As spgt_conv3x3_fwd with a prepared [9*Cin, Cout] weight; Cin, cin_off, cin_pitch must be multiples of 4. */
 int spgt_conv3x3_tc_fwd(const float* x, int cin_pitch, int cin_off, int Cin, const void* wprep, const float* bias,
                         float* y, int cout_pitch, int cout_off, int Cout, int B, int Hh, int Ww, int act,

@@ -36,6 +36,7 @@ SIGNATURES = {
     'spgt_batched_skinny_gemm': (_i, [_f, _f, _f, _fl, _i, _i, _i, _i, _f, _sz, _st]),
     'spgt_skinny_gemm_noalloc_max_bytes': (_sz, []),
     'spgt_batched_skinny_gemm_noalloc': (_i, [_f, _f, _f, _fl, _i, _i, _i, _i, _st]),
+    'spgt_ffn_tc_fwd': (_i, [_f, _i, _f, _f, _f, _f, _f, _i, _f, _i, _i, _i, _i, _i, _st]),
     'spgt_relative_l2_fwd': (_i, [_f, _f, _f, _i, C.c_int64, _fl, _st]),
     'spgt_batched_transpose': (_i, [_f, _f, _i, _i, _i, _st]),
     'spgt_transpose_gather_dual': (_i, [_f, _f, _f] + [_i] * 9 + [_st]),

@@ -614,14 +614,15 @@ extern "C" int spgt_tc_trace_read(long long* host_out) {   // 64 units x 16 slot
 }
 #endif
 
-namespace spgt { int attn_tc_status(); }      // attention_tc.cu
+namespace spgt { int attn_tc_status(); int ffn_tc_status(); }      // attention_tc.cu, tc_ffn.cu
 
 extern "C" int spgt_tc_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return SPGT_ERR_LAUNCH;
     if (v != 0) return v;
     const int a = spgt::attn_tc_status();
-    return a > 0 ? 100 + a : a;                 // 101..108: a wait of the attention kernel gave up
+    if (a != 0) return a > 0 ? 100 + a : a;     // 101..109: a wait of the attention kernel gave up
+    return spgt::ffn_tc_status();               // 21..33: a wait of the fused feed-forward kernel gave up
 }
 
 extern "C" int spgt_linear_tc_fwd(const float* x, int lda, const void* wprep, const float* bias, const float* residual,

@@ -93,10 +93,13 @@ class FeedForward(_KernelWeights):
         self.activation = activation
         self.layer1 = torch.nn.Linear(in_dim, dim_hidden)
         self.layer2 = torch.nn.Linear(dim_hidden, out_dim)
+        self.fused = True        # one kernel for both GEMMs when the shape is 128 -> 256 -> 128
 
     def forward(self, X: Tensor, residual: Tensor = None) -> Tensor:
         """X [..., in_dim] -> [..., out_dim] (+ residual when given, fused into the second GEMM)."""
         w1 = self._cached('w1', lambda: _linear_tc(self.layer1.weight))
         w2 = self._cached('w2', lambda: _linear_tc(self.layer2.weight))
+        if self.fused and w1.K == 128 and w1.N == 256 and w2.N == 128:
+            return ops.ffn_tc(X, w1, self.layer1.bias.detach(), w2, self.layer2.bias.detach(), self.activation, residual)
         h = ops.linear_tc(X, w1, self.layer1.bias.detach(), self.activation)
         return ops.linear_tc(h, w2, self.layer2.bias.detach(), None, residual)

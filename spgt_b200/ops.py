@@ -353,6 +353,22 @@ def linear_tc(x: Tensor, w: TcWeight, bias: Optional[Tensor], act=None, residual
     return out
 
 
+def ffn_tc(x: Tensor, w1: TcWeight, b1: Tensor, w2: TcWeight, b2: Optional[Tensor], act, residual: Optional[Tensor] = None) -> Tensor:
+    """act(x W1 + b1) W2 + b2 (+ residual) in one kernel; x [..., 128], W1 [128, 256], W2 [256, 128]."""
+    _chk(x, 'x'); _chk(b1, 'b1')
+    D = x.shape[-1]
+    if D != w1.K or w1.N != w2.K or w2.N != D:
+        raise ValueError('prepared weights do not chain: need W1 [D, H] and W2 [H, D]')
+    rows = x.numel() // D
+    out = torch.empty_like(x)
+    if residual is not None:
+        _chk(residual, 'residual')
+    with torch.cuda.device(x.device):
+        _call('spgt_ffn_tc_fwd', x.data_ptr(), D, w1.data_ptr(), b1.data_ptr(), w2.data_ptr(), _p(b2), _p(residual), D,
+              out.data_ptr(), D, rows, D, w1.N, act_code(act), _stream())
+    return out
+
+
 def conv3x3_tc(x: Tensor, cin_off: int, Cin: int, w: TcWeight, bias: Tensor, y: Tensor, cout_off: int, Cout: int, act) -> Tensor:
     _chk(x, 'x'); _chk(y, 'y'); _chk(bias, 'bias')
     B, Hh, Ww, cp = x.shape

@@ -86,3 +86,25 @@ def test_decoder_head_tc(dev):
     ref = (torch.nn.functional.linear(h, w2.double()) + b2) * 1.00001 + 0.5
     ref = torch.nn.functional.pad(ref[:, 1:-1, 1:-1], (0, 0, 1, 1, 1, 1))
     assert rel_l2(out, ref) < TOL
+
+
+@pytest.mark.parametrize('rows,act,res', [(1, 'relu', False), (128, 'relu', True), (129, 'silu', True), (1000, 'relu', True),
+                                          (64 * 2809, 'relu', True)])
+def test_ffn_tc_fused(dev, rows, act, res):
+    """The fused 128 -> 256 -> 128 feed-forward kernel against fp64, and bit-identical from run to run."""
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, 128, generator=g)
+    w1, b1 = torch.randn(256, 128, generator=g) / 128 ** 0.5, torch.randn(256, generator=g)
+    w2, b2 = torch.randn(128, 256, generator=g) / 256 ** 0.5, torch.randn(128, generator=g)
+    t1, t2 = ops.TcWeight(w1.t().contiguous().to(dev)), ops.TcWeight(w2.t().contiguous().to(dev))
+    xd = x.to(dev)
+    y = ops.ffn_tc(xd, t1, b1.to(dev), t2, b2.to(dev), act, xd if res else None)
+    assert ops.tc_status() == 0
+    h = torch.nn.functional.linear(x.double(), w1.double(), b1.double())
+    h = torch.relu(h) if act == 'relu' else torch.nn.functional.silu(h)
+    ref = torch.nn.functional.linear(h, w2.double(), b2.double()) + (x.double() if res else 0.0)
+    assert rel_l2(y, ref) < TOL
+    assert torch.equal(y, ops.ffn_tc(xd, t1, b1.to(dev), t2, b2.to(dev), act, xd if res else None))
+    two = ops.linear_tc(ops.linear_tc(xd, t1, b1.to(dev), act), t2, b2.to(dev), None, xd if res else None)
+    assert rel_l2(y, two) < TOL
