@@ -30,7 +30,7 @@ METRIC = 'darcy_gt_inference_samples_per_s_211'
 FINE, SUB_NODE, SUB_ATTN, MODES, SEED = 421, 2, 8, 12, 4
 # DRAM bytes (read + write) of one galerkin_attn_tc_kernel launch at B=64, H=4, S=2809 from the ncu capture
 # summarised in profiles/ (None until a capture of the current kernel exists).
-ATTN_TRAFFIC_BYTES = 346_700_000   # dram read + write per launch from the ncu capture under profiles/ (345.7 - 347.8 MB)
+ATTN_TRAFFIC_BYTES = 342_400_000   # dram read + write per launch from the ncu capture under profiles/ (342.1 - 342.6 MB)
 
 
 def measured_peak():
