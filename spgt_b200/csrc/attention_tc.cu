@@ -30,6 +30,8 @@ namespace spgt {
 __device__ int g_attn_status = 0;
 
 #ifdef SPGT_TC_TRACE
+__device__ int g_attn_dbg = 0;     // experiment mask of the trace build: skip parts of the work (wrong results) to find the bottleneck
+#define AT_DBG(bit) (dbg & (bit))
 __device__ long long g_attn_trace[16 + 10 * 2048];
 __device__ __forceinline__ long long at_gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 __device__ __forceinline__ int at_smid() { int t; asm volatile("mov.u32 %0, %%smid;" : "=r"(t)); return t; }
@@ -37,6 +39,7 @@ __device__ __forceinline__ int at_smid() { int t; asm volatile("mov.u32 %0, %%sm
     if (blockIdx.x < 2048) { g_attn_trace[16 + 10 * blockIdx.x + ((slot) & 7)] = at_gtime(); if ((slot) == 0) g_attn_trace[16 + 10 * blockIdx.x + 8] = at_smid(); } } while (0)
 #else
 #define AT_TRACE(slot) do { } while (0)
+#define AT_DBG(bit) false
 #endif
 
 constexpr int AT_THREADS = 320;                 // warps 0-3 loaders, 4-7 converters, 8-9 MMA issuers
@@ -131,6 +134,9 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     const uint32_t tmem_base = *tmem_slot;
     constexpr uint32_t idesc = tc_idesc(AT_NP);
 
+#ifdef SPGT_TC_TRACE
+    const int dbg = g_attn_dbg;
+#endif
     if (tid == 0) AT_TRACE(0);
     // ============================== phase A: partial T over my columns ==============================
     if (warp < 4) {
@@ -160,7 +166,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             const uint32_t dst0 = smem_base + st * AT_RAW_STAGE;
 #pragma unroll
             for (int n = 0; n < NPT; ++n) {
-                if (tid + 128 * n < NCH) {
+                if (tid + 128 * n < NCH && !AT_DBG(1)) {
                     int valid = crem[n] - s0;
                     valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
                     at_cp16(dst0 + cdst[n], valid > 0 ? cbase[n] + s0 : Kb, valid * 4);
@@ -191,7 +197,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             // V: raw rows -> hi / lo B operands (row = j, 32 k-values = grid nodes, 128B swizzle)
 #pragma unroll
             for (int n = 0; n < 3; ++n) {
-                if (vrow[n] < D) {
+                if (vrow[n] < D && !AT_DBG(2)) {
                     const float* p = vraw + vrow[n] * AT_RP + vsh[n] + 4 * (t & 7);
                     uint32_t h[4], l[4];
                     split_tf32_rn(p[0], h[0], l[0]); split_tf32_rn(p[1], h[1], l[1]); split_tf32_rn(p[2], h[2], l[2]); split_tf32_rn(p[3], h[3], l[3]);
@@ -201,7 +207,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 }
             }
             // K: one row per thread into tensor memory (stage `so`, freed together with the V operands)
-            if (k_warp) {
+            if (k_warp && !AT_DBG(4)) {
                 tc_fence_after();
                 const uint32_t a_hi = tmem_base + lane_addr + AT_A1_COL + so * 64;
                 const float* p = kraw + krow_rd * AT_RP + ksh;
@@ -233,7 +239,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 const uint32_t vhi = smem_base + AT_OP_OFF + so * (2 * AT_TILE);
                 const uint64_t dbh = tc_smem_desc(vhi), dbl = tc_smem_desc(vhi + AT_TILE);
 #pragma unroll
-                for (int kk = 0; kk < 2; ++kk) {
+                for (int kk = 0; kk < (AT_DBG(8) ? 0 : 2); ++kk) {
                     const int k8 = 2 * iw + kk;
                     const uint32_t ah = tmem_base + AT_A1_COL + so * 64 + k8 * 8, al = ah + 32;
                     const uint64_t adv = (uint64_t)(k8 * 2);
@@ -501,6 +507,7 @@ int launch_attn_tc(const float* Q, const float* K, const float* V, float* out, f
 }
 
 #ifdef SPGT_TC_TRACE
+extern "C" int spgt_attn_debug(int mask) { return cudaMemcpyToSymbol(g_attn_dbg, &mask, sizeof(int)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH; }
 extern "C" int spgt_attn_trace_read(long long* host_out) {
     return cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(long long) * (16 + 10 * 2048)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
 }
