@@ -83,6 +83,15 @@ int spgt_projpos_qkv_fwd(const float* x, const float* wq, const float* bq, const
 int spgt_galerkin_attn_fwd(const float* Q, const float* K, const float* V, float* out, float* t_out,
                            int B, int H, int dpk, int S, int merged_heads, spgt_stream_t stream);
 
+/* Backward of spgt_galerkin_attn_fwd (not-merged output layout): gradients dQ, dK, dV [B,H,dpk,S] from d_out
+ * [B,H,S,dpk].  Replaces multihead_galerkin_attention_cccr_backward (extension/bind/galerkin_attention.cu:126-173:
+ * three split-K + three small-K SGEMMs) with one streaming reduction and one apply kernel in exact fp32 FMA
+ * arithmetic; chunk partials are summed in chunk order (deterministic).  dpk <= 35. */
+size_t spgt_galerkin_attn_bwd_workspace_bytes(int B, int H, int dpk, int S);
+int spgt_galerkin_attn_bwd(const float* Q, const float* K, const float* V, const float* d_out, float* dQ, float* dK,
+                           float* dV, int B, int H, int dpk, int S, void* workspace, size_t workspace_bytes,
+                           spgt_stream_t stream);
+
 /* C[b] = alpha * A[b] * B[b] with A [batch,M,K], B [batch,K,N], C [batch,M,N], all row-major; K is the long
  * dimension.  Split-K with per-split partial tiles in `workspace`, summed in split order (deterministic).
  * Replaces batched_skinny_gemm (extension/bind/galerkin_attention.cu:175-198, GEMM_Order::RRR). */

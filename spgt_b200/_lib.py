@@ -32,6 +32,8 @@ SIGNATURES = {
     'spgt_projpos_lnorm_fwd': (_i, [_f, _f, _f, _f, _f, _fl, _f, _f, _f, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_projpos_qkv_fwd': (_i, [_f] * 11 + [_fl] + [_f] * 4 + [_i] * 6 + [_st]),
     'spgt_galerkin_attn_fwd': (_i, [_f, _f, _f, _f, _f, _i, _i, _i, _i, _i, _st]),
+    'spgt_galerkin_attn_bwd_workspace_bytes': (_sz, [_i, _i, _i, _i]),
+    'spgt_galerkin_attn_bwd': (_i, [_f, _f, _f, _f, _f, _f, _f, _i, _i, _i, _i, _f, _sz, _st]),
     'spgt_skinny_gemm_workspace_bytes': (_sz, [_i, _i, _i, _i]),
     'spgt_batched_skinny_gemm': (_i, [_f, _f, _f, _fl, _i, _i, _i, _i, _f, _sz, _st]),
     'spgt_skinny_gemm_noalloc_max_bytes': (_sz, []),

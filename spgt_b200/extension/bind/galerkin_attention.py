@@ -1,10 +1,11 @@
-"""Drop-in for the reference's extension/bind/galerkin_attention.py (forward / inference only).
+"""Drop-in for the reference's extension/bind/galerkin_attention.py (forward of every op; backward of the attention op).
 
 Same function names, argument order and tensor layouts as the reference's public functions
 (extension/bind/galerkin_attention.py:87-107); the work is done by the sm_100a kernels of libspgt_b200.so
 instead of a JIT-built pybind module.  Inputs must be contiguous fp32 CUDA tensors: the reference reads raw
 data pointers without checking, here a wrong device, dtype or layout raises.
 """
+import torch
 from torch import Tensor
 
 from ... import ops
@@ -25,8 +26,25 @@ def multihead_projection_layernorm_with_position_rrc_cuda(
     return ops.projpos_lnorm(input, weight, bias, ln_weight, ln_bias, position, norm_eps, num_head, dim_head, dim_position)
 
 
+class Multihead_Galerkin_Attention_cccr_Function(torch.autograd.Function):
+    """Autograd wrapper with the reference's class name (extension/bind/galerkin_attention.py:68-84)."""
+
+    @staticmethod
+    def forward(ctx, Q: Tensor, K: Tensor, V: Tensor) -> Tensor:
+        Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
+        ctx.save_for_backward(Q, K, V)
+        return ops.galerkin_attention(Q, K, V)
+
+    @staticmethod
+    def backward(ctx, grad_attn: Tensor):
+        Q, K, V = ctx.saved_tensors
+        return ops.galerkin_attention_backward(Q, K, V, grad_attn.contiguous())
+
+
 def multihead_galerkin_attention_cccr_cuda(Q: Tensor, K: Tensor, V: Tensor) -> Tensor:
-    """Q,K,V [B,H,d_posk,S] -> [B,H,S,d_posk] = Q^T (K V^T / S)."""
+    """Q,K,V [B,H,d_posk,S] -> [B,H,S,d_posk] = Q^T (K V^T / S); differentiable in Q, K and V."""
+    if torch.is_grad_enabled() and (Q.requires_grad or K.requires_grad or V.requires_grad):
+        return Multihead_Galerkin_Attention_cccr_Function.apply(Q, K, V)
     return ops.galerkin_attention(Q, K, V)
 
 

@@ -28,7 +28,7 @@ def _stream() -> int:
 
 
 # kernels launched by one call of each entry point (everything else launches one)
-_KERNELS_PER_CALL = {'spgt_batched_skinny_gemm': 2, 'spgt_spectral_conv2d_fwd': 5}
+_KERNELS_PER_CALL = {'spgt_batched_skinny_gemm': 2, 'spgt_spectral_conv2d_fwd': 5, 'spgt_galerkin_attn_bwd': 2}
 LAUNCHES = 0          # running count of kernels launched through this module
 _PROFILE = None       # None, or a dict name -> list of (start_event, end_event) filled while profiling
 
@@ -144,6 +144,22 @@ def galerkin_attention(Q: Tensor, K: Tensor, V: Tensor, merged_heads: bool = Fal
         _call('spgt_galerkin_attn_fwd', Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), _p(T),
                                          B, H, dpk, S, int(merged_heads), _stream())
     return (out, T) if return_kv else out
+
+
+def galerkin_attention_backward(Q: Tensor, K: Tensor, V: Tensor, grad_out: Tensor):
+    """Gradients (dQ, dK, dV), each [B,H,dpk,S], of galerkin_attention(Q, K, V) -> [B,H,S,dpk] for grad_out [B,H,S,dpk]."""
+    for t, n in ((Q, 'Q'), (K, 'K'), (V, 'V'), (grad_out, 'grad_out')):
+        _chk(t, n)
+    B, H, dpk, S = Q.shape
+    if K.shape != Q.shape or V.shape != Q.shape or grad_out.shape != (B, H, S, dpk):
+        raise ValueError('shape mismatch')
+    need = int(lib.spgt_galerkin_attn_bwd_workspace_bytes(B, H, dpk, S))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=Q.device)
+    dQ, dK, dV = torch.empty_like(Q), torch.empty_like(Q), torch.empty_like(Q)
+    with torch.cuda.device(Q.device):
+        _call('spgt_galerkin_attn_bwd', Q.data_ptr(), K.data_ptr(), V.data_ptr(), grad_out.data_ptr(), dQ.data_ptr(), dK.data_ptr(),
+              dV.data_ptr(), B, H, dpk, S, ws.data_ptr(), need, _stream())
+    return dQ, dK, dV
 
 
 def relative_l2(pred: Tensor, target: Tensor, eps: float = 1.0e-10) -> Tensor:

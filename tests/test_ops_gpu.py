@@ -297,3 +297,22 @@ def test_relative_l2_metric_kernel(dev, N, r):
     s, c = relative_l2_sums(p.to(dev), t.to(dev))
     assert float(c) == N and abs(float(s) - float(ref.sum())) < 1e-5 * float(ref.sum())
     assert abs(float(relative_l2_metric(p, t)) - float(ref.mean())) < 1e-5 * float(ref.mean())      # host tensors: torch formula
+
+
+@pytest.mark.parametrize('B,H,dpk,S', [(1, 1, 34, 1), (2, 2, 34, 129), (1, 4, 34, 1849), (2, 1, 32, 300), (1, 1, 35, 77)])
+def test_attention_backward_against_autograd(dev, B, H, dpk, S):
+    """Gradients of the attention op (through the reference-named autograd function) vs torch autograd on the fp64 oracle."""
+    from spgt_b200.extension.bind.galerkin_attention import multihead_galerkin_attention_cccr_cuda
+    g = torch.Generator().manual_seed(S + dpk)
+    Q, K, V = (torch.randn(B, H, dpk, S, generator=g) for _ in range(3))
+    G = torch.randn(B, H, S, dpk, generator=g)
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (Q, K, V))
+    O.galerkin_attention(qd, kd, vd).backward(G.double())
+    qg, kg, vg = (t.to(dev).requires_grad_(True) for t in (Q, K, V))
+    out = multihead_galerkin_attention_cccr_cuda(qg, kg, vg)
+    out.backward(G.to(dev))
+    for got, ref, name in ((qg.grad, qd.grad, 'dQ'), (kg.grad, kd.grad, 'dK'), (vg.grad, vd.grad, 'dV')):
+        assert got.shape == ref.shape
+        assert rel_l2(got, ref) < 5e-5, (name, rel_l2(got, ref))    # sums of S cancelling random terms, as for K^T V above
+    out2 = multihead_galerkin_attention_cccr_cuda(qg.detach().requires_grad_(True), kg.detach(), vg.detach())
+    assert torch.equal(out2, out)
