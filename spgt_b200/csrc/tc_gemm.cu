@@ -316,50 +316,51 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         const uint32_t d_off = (MT == 2) ? (uint32_t)(iw * BN) : (uint32_t)(iw * NI);
         const uint32_t a_off = (MT == 2) ? (uint32_t)(iw * 64) : 0u;
         const uint32_t b_off = (MT == 2) ? 0u : (uint32_t)(iw * NI * 128);   // NI rows of 128 bytes
-        TcRing ra, rb;
-        bool alive = true;
-        for (int ui = 0; ui < n_my_units && alive; ++ui) {
-            const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
-            if (lane == 0 && iw == 0) TC_TRACE(ui, 4);
-            if (!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2, &g_tc_status)) { alive = false; break; }
-            if (lane == 0 && iw == 0) TC_TRACE(ui, 5);
-            tc_fence_after();
-            const uint32_t d = tmem_base + buf * MT * BN + d_off;
-            for (int kb = 0; kb < KB; ++kb, ra.template next<SA>(), rb.template next<SB>()) {
-                const uint32_t sa = ra.s, pa = ra.ph;
-                const uint32_t sb = resident ? (uint32_t)kb : rb.s;
-                const uint32_t pb = resident ? 0u : rb.ph;
-                bool oka, okb = true;
-                TC_TADD(ui, 24 + 5 * iw, oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status));
-                if (!oka) { alive = false; break; }
-                if (!resident || ui == 0) {
-                    TC_TADD(ui, 25 + 5 * iw, okb = mbar_wait(b_full(sb), pb, abort_flag, 7, &g_tc_status));
-                    if (!okb) { alive = false; break; }
-                }
-                if (lane == 0 && kb == 0 && iw == 0) TC_TRACE(ui, 6);
+        // Only lane 0 runs the loop (waits included): no divergence and reconvergence per k-block.  The B descriptors
+        // differ between stages only in the address field of their low word, so they are advanced with 32-bit adds.
+        if (lane == 0) {
+            const uint64_t desc0 = tc_smem_desc(smem_base + b_off);
+            const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
+            TcRing ra, rb;
+            bool alive = true;
+            for (int ui = 0; ui < n_my_units && alive; ++ui) {
+                const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
+                if (iw == 0) TC_TRACE(ui, 4);
+                if (!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2, &g_tc_status)) break;
+                if (iw == 0) TC_TRACE(ui, 5);
                 tc_fence_after();
-                TC_TADD(ui, 31 - iw, if (lane == 0) {
-                    const uint32_t b_hi = smem_base + sb * C::B_BYTES + b_off;
-                    const uint64_t dbh = tc_smem_desc(b_hi), dbl = tc_smem_desc(b_hi + C::B_BYTES / 2);
-                    const uint32_t ah0 = tmem_a + sa * MT * 64 + a_off;
+                const uint32_t d = tmem_base + buf * MT * BN + d_off;
+                for (int kb = 0; kb < KB; ++kb, ra.template next<SA>(), rb.template next<SB>()) {
+                    const uint32_t sa = ra.s, pa = ra.ph;
+                    const uint32_t sb = resident ? (uint32_t)kb : rb.s;
+                    bool oka, okb = true;
+                    TC_TADD(ui, 24 + 5 * iw, oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status));
+                    if (!oka) { alive = false; break; }
+                    if (!resident || ui == 0) {
+                        TC_TADD(ui, 25 + 5 * iw, okb = mbar_wait(b_full(sb), resident ? 0u : rb.ph, abort_flag, 7, &g_tc_status));
+                        if (!okb) { alive = false; break; }
+                    }
+                    if (kb == 0 && iw == 0) TC_TRACE(ui, 6);
+                    tc_fence_after();
+                    const uint32_t bh = desc_lo0 + sb * (uint32_t)(C::B_BYTES >> 4), bl = bh + (uint32_t)(C::B_BYTES >> 5);
+                    const uint32_t ah = tmem_a + sa * MT * 64 + a_off, al = ah + 32;
+                    tc_mma_tf32_ts_p(d, al, bh, desc_hi, idesc, kb > 0 ? 1u : 0u);
+                    tc_mma_tf32_ts_acc(d, ah, bl, desc_hi, idesc);
+                    tc_mma_tf32_ts_acc(d, ah, bh, desc_hi, idesc);
 #pragma unroll
-                    for (int k8 = 0; k8 < TC_BK / 8; ++k8) {
-                        const uint64_t adv = (uint64_t)(k8 * 2);          // 32 bytes per k-step, in 16-byte units
-                        const uint32_t ah = ah0 + k8 * 8, al = ah + 32;
-                        const uint32_t accum = (kb > 0 || k8 > 0) ? 1u : 0u;
-                        tc_mma_tf32_ts(d, al, dbh + adv, idesc, accum);
-                        tc_mma_tf32_ts(d, ah, dbl + adv, idesc, 1u);
-                        tc_mma_tf32_ts(d, ah, dbh + adv, idesc, 1u);
+                    for (int k8 = 1; k8 < TC_BK / 8; ++k8) {          // 32 bytes (2 descriptor units) and 8 TMEM columns per k-step
+                        tc_mma_tf32_ts_acc(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc);
+                        tc_mma_tf32_ts_acc(d, ah + k8 * 8, bl + k8 * 2, desc_hi, idesc);
+                        tc_mma_tf32_ts_acc(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc);
                     }
                     tc_commit(a_empty(sa));            // A stage reusable once both issuers' MMAs have read it
                     if (!resident) tc_commit(b_empty(sb));
-                });
-                __syncwarp();
+                }
+                if (alive) tc_commit(acc_full(buf));
+                if (iw == 0) TC_TRACE(ui, 7);
             }
-            if (alive && lane == 0) tc_commit(acc_full(buf));
-            if (lane == 0 && iw == 0) TC_TRACE(ui, 7);
-            __syncwarp();
         }
+        __syncwarp();
         }
     } else {
         // ------------------------------------------ epilogue ------------------------------------------
