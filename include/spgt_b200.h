@@ -92,6 +92,18 @@ int spgt_galerkin_attn_bwd(const float* Q, const float* K, const float* V, const
                            float* dV, int B, int H, int dpk, int S, void* workspace, size_t workspace_bytes,
                            spgt_stream_t stream);
 
+/* Element-wise part of the backward of the projection (+ LayerNorm) + position op: from grad_out [B,H,d_pos+32,S] and the
+ * pre-LayerNorm projection h = x W + b [B*S, H*32] it writes dh [B*S, H*32] (gradient with respect to h) and the parameter
+ * gradients db, dlnw, dlnb [H*32] (dlnw, dlnb only with ln_weight != NULL; without LayerNorm dh is the gathered gradient
+ * and h may be NULL).  The caller finishes with two GEMMs, dX = dh W^T and dW = x^T dh (spgt_linear_tc_fwd and
+ * spgt_batched_transpose + spgt_batched_skinny_gemm).  Replaces the element-wise stages of
+ * multihead_projection[_layernorm]_with_position_rrc_backward (extension/bind/galerkin_attention.cu:26-48, 70-102).
+ * Partial sums are added in block order (deterministic).  d_head must be 32, H <= 8. */
+size_t spgt_projpos_bwd_workspace_bytes(int B, int S, int H);
+int spgt_projpos_bwd_elementwise(const float* grad_out, const float* h, const float* ln_weight, float eps, float* dh, float* db,
+                                 float* dlnw, float* dlnb, int B, int S, int H, int d_head, int d_pos, void* workspace,
+                                 size_t workspace_bytes, spgt_stream_t stream);
+
 /* C[b] = alpha * A[b] * B[b] with A [batch,M,K], B [batch,K,N], C [batch,M,N], all row-major; K is the long
  * dimension.  Split-K with per-split partial tiles in `workspace`, summed in split order (deterministic).
  * Replaces batched_skinny_gemm (extension/bind/galerkin_attention.cu:175-198, GEMM_Order::RRR). */

@@ -34,6 +34,8 @@ SIGNATURES = {
     'spgt_galerkin_attn_fwd': (_i, [_f, _f, _f, _f, _f, _i, _i, _i, _i, _i, _st]),
     'spgt_galerkin_attn_bwd_workspace_bytes': (_sz, [_i, _i, _i, _i]),
     'spgt_galerkin_attn_bwd': (_i, [_f, _f, _f, _f, _f, _f, _f, _i, _i, _i, _i, _f, _sz, _st]),
+    'spgt_projpos_bwd_workspace_bytes': (_sz, [_i, _i, _i]),
+    'spgt_projpos_bwd_elementwise': (_i, [_f, _f, _f, _fl, _f, _f, _f, _f, _i, _i, _i, _i, _i, _f, _sz, _st]),
     'spgt_skinny_gemm_workspace_bytes': (_sz, [_i, _i, _i, _i]),
     'spgt_batched_skinny_gemm': (_i, [_f, _f, _f, _fl, _i, _i, _i, _i, _f, _sz, _st]),
     'spgt_skinny_gemm_noalloc_max_bytes': (_sz, []),

@@ -28,7 +28,7 @@ def _stream() -> int:
 
 
 # kernels launched by one call of each entry point (everything else launches one)
-_KERNELS_PER_CALL = {'spgt_batched_skinny_gemm': 2, 'spgt_spectral_conv2d_fwd': 5, 'spgt_galerkin_attn_bwd': 2}
+_KERNELS_PER_CALL = {'spgt_batched_skinny_gemm': 2, 'spgt_spectral_conv2d_fwd': 5, 'spgt_galerkin_attn_bwd': 2, 'spgt_projpos_bwd_elementwise': 2}
 LAUNCHES = 0          # running count of kernels launched through this module
 _PROFILE = None       # None, or a dict name -> list of (start_event, end_event) filled while profiling
 
@@ -144,6 +144,33 @@ def galerkin_attention(Q: Tensor, K: Tensor, V: Tensor, merged_heads: bool = Fal
         _call('spgt_galerkin_attn_fwd', Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), _p(T),
                                          B, H, dpk, S, int(merged_heads), _stream())
     return (out, T) if return_kv else out
+
+
+def projpos_backward(x: Tensor, weight: Tensor, bias: Optional[Tensor], ln_weight: Optional[Tensor], grad_out: Tensor,
+                     norm_eps: float, num_head: int, dim_head: int, dim_position: int):
+    """Gradients of projpos (ln_weight None) or projpos_lnorm with respect to (x, weight, bias, ln_weight, ln_bias) for
+    grad_out [B, H, dim_position + dim_head, S].  The element-wise stage (gather, LayerNorm backward, parameter sums) is
+    one kernel; dX = dh W^T and dW = x^T dh reuse the tcgen05 linear and the transpose + split-K skinny GEMM."""
+    _chk(x, 'input'); _chk(weight, 'weight'); _chk(grad_out, 'grad_out')
+    B, S, D = x.shape
+    if grad_out.shape != (B, num_head, dim_position + dim_head, S) or D != num_head * dim_head:
+        raise ValueError('shape mismatch')
+    x2 = x.reshape(B * S, D)
+    h = linear_tc(x2, TcWeight(weight), bias) if ln_weight is not None else None
+    dh = torch.empty(B * S, D, device=x.device, dtype=x.dtype)
+    db = torch.empty(D, device=x.device, dtype=x.dtype)
+    dlnw = torch.empty(D, device=x.device, dtype=x.dtype) if ln_weight is not None else None
+    dlnb = torch.empty(D, device=x.device, dtype=x.dtype) if ln_weight is not None else None
+    need = int(lib.spgt_projpos_bwd_workspace_bytes(B, S, num_head))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _call('spgt_projpos_bwd_elementwise', grad_out.data_ptr(), _p(h), _p(ln_weight), float(norm_eps), dh.data_ptr(), db.data_ptr(),
+              _p(dlnw), _p(dlnb), B, S, num_head, dim_head, dim_position, ws.data_ptr(), need, _stream())
+    dx = linear_tc(dh, TcWeight(weight.t().contiguous()), None).view(B, S, D)
+    xT = batched_transpose(x2, [1], [B * S], [D])                       # [1, D, rows]
+    dW = batched_skinny_gemm(xT, dh.view(1, B * S, D), 1.0).view(D, D)
+    shape = ln_weight.shape if ln_weight is not None else None
+    return dx, dW, db, (dlnw.view(shape) if dlnw is not None else None), (dlnb.view(shape) if dlnb is not None else None)
 
 
 def galerkin_attention_backward(Q: Tensor, K: Tensor, V: Tensor, grad_out: Tensor):

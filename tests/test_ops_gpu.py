@@ -316,3 +316,59 @@ def test_attention_backward_against_autograd(dev, B, H, dpk, S):
         assert rel_l2(got, ref) < 5e-5, (name, rel_l2(got, ref))    # sums of S cancelling random terms, as for K^T V above
     out2 = multihead_galerkin_attention_cccr_cuda(qg.detach().requires_grad_(True), kg.detach(), vg.detach())
     assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize('B,S,ln', [(1, 1, True), (2, 77, True), (2, 77, False), (3, 1849, True), (1, 300, False)])
+def test_projection_backward_against_autograd(dev, B, S, ln):
+    """Gradients of the projection (+ LayerNorm) + position op through the reference-named autograd functions vs torch
+    autograd on the fp64 oracle."""
+    from spgt_b200.extension.bind.galerkin_attention import (multihead_projection_layernorm_with_position_rrc_cuda,
+                                                             multihead_projection_with_position_rrc_cuda)
+    H, d, dp, D = 4, 32, 2, 128
+    g = torch.Generator().manual_seed(S * 3 + B + ln)
+    x, w, b = torch.randn(B, S, D, generator=g), torch.randn(D, D, generator=g) / D ** 0.5, torch.randn(D, generator=g)
+    lnw, lnb = 1.0 + 0.3 * torch.randn(H, d, generator=g), 0.1 * torch.randn(H, d, generator=g)
+    pos, G = torch.rand(B, S, dp, generator=g), torch.randn(B, H, dp + d, S, generator=g)
+    leaves64 = [t.double().requires_grad_(True) for t in ((x, w, b, lnw, lnb) if ln else (x, w, b))]
+    if ln:
+        ref = O.projpos_lnorm(leaves64[0], leaves64[1], leaves64[2], leaves64[3], leaves64[4], pos.double(), 1e-5, H, d)
+    else:
+        ref = O.projpos(leaves64[0], leaves64[1], leaves64[2], pos.double(), H, d)
+    ref.backward(G.double())
+    leaves = [t.to(dev).requires_grad_(True) for t in ((x, w, b, lnw, lnb) if ln else (x, w, b))]
+    if ln:
+        out = multihead_projection_layernorm_with_position_rrc_cuda(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], pos.to(dev), 1e-5, H, d, dp)
+    else:
+        out = multihead_projection_with_position_rrc_cuda(leaves[0], leaves[1], leaves[2], pos.to(dev), H, d, dp)
+    assert rel_l2(out, ref) < PER_LAYER_TOL
+    out.backward(G.to(dev))
+    for got, want, name in zip(leaves, leaves64, ('dx', 'dW', 'db', 'dlnw', 'dlnb')):
+        assert got.grad is not None and got.grad.shape == want.grad.shape, name
+        assert rel_l2(got.grad, want.grad) < 5e-5, (name, rel_l2(got.grad, want.grad))
+
+
+def test_datamove_ops_are_differentiable(dev):
+    """The data-movement ops back-propagate through their inverse ops, as the reference's autograd functions do."""
+    from spgt_b200.extension.bind.datamove import batched_transpose, transpose_gather_dual, transpose_scatter_dual
+    g = torch.Generator().manual_seed(9)
+    X = torch.randn(2, 3, 5, 7, generator=g).to(dev).requires_grad_(True)
+    Y = batched_transpose(X, [2], [3, 5], [7])
+    G = torch.randn(Y.shape, generator=g).to(dev)
+    Y.backward(G)
+    assert torch.equal(X.grad, G.permute(0, 2, 3, 1))
+    dims, Ha, Wa, Hl, Wl = [2, 3], 9, 5, 3, 3
+    src = torch.view_as_complex(torch.randn(2, 3, Ha, Wa, 2, generator=g)).to(dev).requires_grad_(True)
+    o1, o2 = transpose_gather_dual(src, dims, Ha, Wa, Hl, Wl, 0, 0, Ha - Hl, 0)
+    g1 = torch.view_as_complex(torch.randn(*o1.shape, 2, generator=g)).to(dev)
+    g2 = torch.view_as_complex(torch.randn(*o2.shape, 2, generator=g)).to(dev)
+    torch.autograd.backward([o1, o2], [g1, g2])
+    want = torch.zeros_like(src)
+    want[:, :, :Hl, :Wl] = g1.permute(2, 3, 0, 1)
+    want[:, :, Ha - Hl:, :Wl] = g2.permute(2, 3, 0, 1)
+    assert torch.equal(torch.view_as_real(src.grad), torch.view_as_real(want))
+    s1, s2 = (g1.clone().requires_grad_(True), g2.clone().requires_grad_(True))
+    full = transpose_scatter_dual(s1, s2, dims, Ha, Wa, Hl, Wl, 0, 0, Ha - Hl, 0)
+    gf = torch.view_as_complex(torch.randn(*full.shape, 2, generator=g)).to(dev)
+    full.backward(gf)
+    assert torch.equal(torch.view_as_real(s1.grad), torch.view_as_real(gf[:, :, :Hl, :Wl].permute(2, 3, 0, 1).contiguous()))
+    assert torch.equal(torch.view_as_real(s2.grad), torch.view_as_real(gf[:, :, Ha - Hl:, :Wl].permute(2, 3, 0, 1).contiguous()))
