@@ -26,14 +26,18 @@ __global__ void __launch_bounds__(256)
 bilinear_kernel(const float4* __restrict__ x, float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int C4, int act,
                 int rows) {
     const int per_row = Wo * C4;
+    const bool fixed_c = (blockDim.x % C4) == 0;          // a thread keeps its channel quad: no division per element
+    const int c_fix = threadIdx.x % C4, x_step = blockDim.x / C4;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const int b = row / Ho, yo = row - b * Ho;
         const Tap ty = make_tap(yo, Hi, Ho);
         const float4* r0 = x + ((int64_t)b * Hi + ty.i0) * Wi * C4;
         const float4* r1 = x + ((int64_t)b * Hi + ty.i1) * Wi * C4;
         float4* yr = y + (int64_t)row * per_row;
-        for (int e = threadIdx.x; e < per_row; e += blockDim.x) {
-            const int xo = e / C4, c = e - xo * C4;
+        int xo = threadIdx.x / C4;
+        for (int e = threadIdx.x; e < per_row; e += blockDim.x, xo += x_step) {
+            int c = c_fix;
+            if (!fixed_c) { xo = e / C4; c = e - xo * C4; }
             const Tap tx = make_tap(xo, Wi, Wo);
             const float4 v00 = __ldg(r0 + tx.i0 * C4 + c);
             const float4 v01 = __ldg(r0 + tx.i1 * C4 + c);
@@ -140,6 +144,12 @@ upsample_grid_kernel(const float4* __restrict__ uw, const float2* __restrict__ g
                      const float4* __restrict__ bias, float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int C4,
                      int rows) {
     const int per_row = Wo * C4;
+    // When the block size is a multiple of C4 a thread keeps its channel quad for every element: the three parameter
+    // vectors stay in registers and the pixel index advances by a constant, without a division.
+    const bool fixed_c = (blockDim.x % C4) == 0;
+    const int c_fix = threadIdx.x % C4, x_fix = threadIdx.x / C4, x_step = blockDim.x / C4;
+    float4 g0f, g1f, bbf;
+    if (fixed_c) { g0f = __ldg(wg + c_fix); g1f = __ldg(wg + C4 + c_fix); bbf = __ldg(bias + c_fix); }
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const int b = row / Ho, yo = row - b * Ho;
         const Tap ty = make_tap(yo, Hi, Ho);
@@ -147,8 +157,14 @@ upsample_grid_kernel(const float4* __restrict__ uw, const float2* __restrict__ g
         const float4* r1 = uw + ((int64_t)b * Hi + ty.i1) * Wi * C4;
         const float2* gr = grid + (int64_t)row * Wo;
         float4* yr = y + (int64_t)row * per_row;
-        for (int e = threadIdx.x; e < per_row; e += blockDim.x) {
-            const int xo = e / C4, c = e - xo * C4;
+        int xo = x_fix;
+        for (int e = threadIdx.x; e < per_row; e += blockDim.x, xo += x_step) {
+            int c = c_fix;
+            float4 g0 = g0f, g1 = g1f, bb = bbf;
+            if (!fixed_c) {
+                xo = e / C4; c = e - xo * C4;
+                g0 = __ldg(wg + c); g1 = __ldg(wg + C4 + c); bb = __ldg(bias + c);
+            }
             const Tap tx = make_tap(xo, Wi, Wo);
             const float4 v00 = __ldg(r0 + tx.i0 * C4 + c);
             const float4 v01 = __ldg(r0 + tx.i1 * C4 + c);
@@ -156,7 +172,6 @@ upsample_grid_kernel(const float4* __restrict__ uw, const float2* __restrict__ g
             const float4 v11 = __ldg(r1 + tx.i1 * C4 + c);
             const float w00 = ty.w0 * tx.w0, w01 = ty.w0 * tx.w1, w10 = ty.w1 * tx.w0, w11 = ty.w1 * tx.w1;
             const float2 gxy = __ldg(gr + xo);
-            const float4 g0 = __ldg(wg + c), g1 = __ldg(wg + C4 + c), bb = __ldg(bias + c);
             float4 o;
             o.x = v00.x * w00 + v01.x * w01 + v10.x * w10 + v11.x * w11 + gxy.x * g0.x + gxy.y * g1.x + bb.x;
             o.y = v00.y * w00 + v01.y * w01 + v10.y * w10 + v11.y * w11 + gxy.x * g0.y + gxy.y * g1.y + bb.y;
