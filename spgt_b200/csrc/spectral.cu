@@ -24,9 +24,17 @@ constexpr int SP_XP1 = 40;       // S1: X chunk pitch (A operand read M-contiguo
 constexpr int SP_XP3 = 36;       // S3: X chunk pitch (A operand read K-contiguous), == 4 (mod 32)
 constexpr int SP_PP = 40;        // S3: P row-block pitch and Wr pitch (B operands), == 8 (mod 32)
 
+constexpr int SP_XMAX = 256;      // largest r the staged S2a / S2c kernels accept (shared-memory budget)
+__host__ __device__ inline int sp_round_pitch(int n, int rem) {   // smallest p >= n with p % 32 == rem
+    int p = (n + 31) / 32 * 32 + rem;
+    if (p - 32 >= n) p -= 32;
+    return p;
+}
+
 struct SpecTables {              // offsets in floats into the table buffer
     int r, m, J, JP, RY, F3P, F1P;
     int f1t, f3, gr, gi, total;
+    int GA_ROWS, GA_P, ga, GC_ROWS, GC_P, gc;    // zero-padded copies of G in the shared-memory layouts of S2a / S2c (r <= SP_XMAX)
 };
 __host__ __device__ inline SpecTables spec_tables(int r, int m) {
     SpecTables t;
@@ -37,6 +45,13 @@ __host__ __device__ inline SpecTables spec_tables(int r, int m) {
     t.gr = t.f3 + t.RY * t.F3P;
     t.gi = t.gr + t.J * r;
     t.total = (t.gi + t.J * r + 3) / 4 * 4;
+    t.GA_ROWS = (2 * t.J + 15) / 16 * 16; t.GA_P = sp_round_pitch((r + 7) / 8 * 8, 4);
+    t.GC_ROWS = (2 * t.J + 7) / 8 * 8;    t.GC_P = sp_round_pitch((r + 15) / 16 * 16, 8);
+    t.ga = t.total; t.gc = t.ga;
+    if (r <= SP_XMAX) {
+        t.gc = t.ga + t.GA_ROWS * t.GA_P;
+        t.total = t.gc + t.GC_ROWS * t.GC_P;
+    }
     return t;
 }
 
@@ -72,6 +87,16 @@ __global__ void spectral_tables_kernel(float* tab, int r, int m) {
             double s, c;
             sincospi(2.0 * (double)(((int64_t)kept_kx(q, r, m) * x) % r) / (double)r, &s, &c);
             v = (float)(im ? -s : c);
+        } else if (i >= T.ga && r <= SP_XMAX) {                 // padded copies [rows][pitch]: row q' < 2J = (Re | Im) of G
+            const bool c_copy = i >= T.gc;
+            const int k = i - (c_copy ? T.gc : T.ga), P = c_copy ? T.GC_P : T.GA_P;
+            const int q2 = k / P, x = k % P;
+            if (q2 < 2 * T.J && x < r) {
+                const int q = q2 < T.J ? q2 : q2 - T.J;
+                double s, c;
+                sincospi(2.0 * (double)(((int64_t)kept_kx(q, r, m) * x) % r) / (double)r, &s, &c);
+                v = (float)(q2 < T.J ? c : -s);
+            }
         }
         tab[i] = v;
     }
@@ -289,14 +314,8 @@ spectral_inv_x_kernel(const float* __restrict__ Or, const float* __restrict__ Oi
 // Both stage the whole G table ([2J][r], zero padded) and their Y1 / O block in shared memory, then every warp
 // owns a slice of the output (S2a: 16 columns, S2c: every fourth 16-row tile).
 // ------------------------------------------------------------------------------------------------------------
-constexpr int SP_XMAX = 256;      // largest r the staged kernels accept (shared-memory budget)
 constexpr int SP_YP = 72;         // pitch of the [x][64] / [k][64] B operands, == 8 (mod 32)
 
-__host__ __device__ inline int sp_round_pitch(int n, int rem) {   // smallest p >= n with p % 32 == rem
-    int p = (n + 31) / 32 * 32 + rem;
-    if (p - 32 >= n) p -= 32;
-    return p;
-}
 
 __global__ void __launch_bounds__(128)
 spectral_fwd_x_mma_kernel(const float* __restrict__ Y1, const float* __restrict__ tab, float* __restrict__ Zr,
@@ -320,10 +339,8 @@ spectral_fwd_x_mma_kernel(const float* __restrict__ Y1, const float* __restrict_
         cp_async_zfill<16>(ys + x * SP_YP + c4 * 4, src, ok);
     }
     cp_async_commit();
-    for (int i = tid; i < 16 * MT * GP; i += 128) {
-        const int q = i / GP, x = i % GP;
-        gs[i] = (q < M2 && x < r) ? __ldg(tab + T.gr + q * r + x) : 0.0f;
-    }
+    for (int i = tid; i < 16 * MT * GP / 4; i += 128) cp_async_zfill<16>(gs + 4 * i, tab + T.ga + 4 * i, true);   // padded G, as stored
+    cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
 
@@ -395,10 +412,8 @@ spectral_inv_x_mma_kernel(const float* __restrict__ Or, const float* __restrict_
     const int ky = blockIdx.x; const int64_t b = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    for (int i = tid; i < K8 * GP; i += 128) {
-        const int q = i / GP, x = i % GP;
-        gs[i] = (q < M2 && x < r) ? __ldg(tab + T.gr + q * r + x) : 0.0f;
-    }
+    for (int i = tid; i < K8 * GP / 4; i += 128) cp_async_zfill<16>(gs + 4 * i, tab + T.gc + 4 * i, true);     // padded G, as stored
+    cp_async_commit();
     for (int i = tid; i < K8 * 64; i += 128) {
         const int k = i >> 6, n = i & 63;
         float v = 0.0f;
@@ -410,6 +425,7 @@ spectral_inv_x_mma_kernel(const float* __restrict__ Or, const float* __restrict_
         }
         bs[k * SP_YP + n] = v;
     }
+    cp_async_wait<0>();
     __syncthreads();
     float* pb = P + (b * r) * (int64_t)J * SP_C;
     for (int mt = warp; mt < r16 / 16; mt += 4) {
