@@ -1,7 +1,7 @@
 // Dense contractions on the 5th-generation tensor cores (tcgen05) with 3xTF32:
 //   C[rows, N] = A[rows, K] * W[K, N],   A*W ~= A_lo*W_hi + A_hi*W_lo + A_hi*W_hi   (fp32-level accuracy).
 //
-// Persistent, warp-specialised kernel, one CTA (576 threads) per SM.  A 128 x 128 x 8 tf32 MMA with both operands
+// Persistent, warp-specialised kernel, one CTA (576 or 608 threads) per SM.  A 128 x 128 x 8 tf32 MMA with both operands
 // in shared memory already consumes the whole shared-memory bandwidth of an SM, and 3xTF32 reads every operand
 // twice, so the operands are kept off that path:
 //   * A (activations) is an MMA operand in TENSOR MEMORY: loader warps cp.async the raw fp32 tile (dense rows, or
@@ -14,10 +14,12 @@
 //   * Accumulators live in TMEM.  MT = 1: one 128-row tile with double-buffered accumulators (the epilogue of a
 //     tile overlaps the MMAs of the next).  MT = 2: two 128-row tiles share every W stage (halves the L2 traffic of
 //     W for long-K problems such as the 3x3 convolutions).
-//   * Row-major epilogues stage each thread's row in padded shared memory and leave through cp.async.bulk stores
-//     (full 128-byte lines); the projection epilogue (LayerNorm + head-major transposed store) and the decoder
-//     head (row dot product) store directly, one row per thread.
-//   warps 0-3 A loaders, 4-7 A splitters, 8 W loader, 9-10 MMA issuers (one elected lane each), 11-18 epilogue.
+//   * Row-major epilogues stage each thread's row in padded shared memory and leave as warp-cooperative coalesced
+//     float4 stores (full 128-byte lines, residual added on the way); the projection epilogue does the per-head
+//     LayerNorm thread-locally and stores head-major through the same staging; the decoder head keeps its
+//     constants in shared memory and reduces its row dot product across the two column halves.
+//   warps 0-3 A loaders, 4-7 A splitters, 8 W loader, 9 (MT = 2: 9-10) MMA issuers (lane 0 runs the whole issue loop),
+//   then 8 epilogue warps.
 // All waits are bounded mbarrier polls: on expiry the kernel records an error code, stops waiting and returns.
 #include "tc_common.cuh"
 
