@@ -328,7 +328,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             for (int ui = 0; ui < n_my_units && alive; ++ui) {
                 const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
                 if (iw == 0) TC_TRACE(ui, 4);
-                if (!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2, &g_tc_status)) break;
+                bool okc; TC_TADD(ui, 26, okc = mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2, &g_tc_status));
+                if (!okc) break;
                 if (iw == 0) TC_TRACE(ui, 5);
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * MT * BN + d_off;
@@ -378,7 +379,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
             if (epi_idx == 0) TC_TRACE(ui, 8);
-            if (!mbar_wait(acc_full(buf), aph, abort_flag, 4, &g_tc_status)) { alive = false; break; }
+            bool okf; TC_TADD(ui, 24, okf = mbar_wait(acc_full(buf), aph, abort_flag, 4, &g_tc_status));
+            if (!okf) { alive = false; break; }
             if (epi_idx == 0) TC_TRACE(ui, 9);
             tc_fence_after();
             const int unit = u0 + ui * ctas_per_nt;
@@ -449,8 +451,12 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 for (int hd = half; hd < 4; hd += 2) {           // one head = 32 columns = one TMEM load
                     float v[32];
                     tc_ld32(taddr + hd * 32, v);
+                    const float4* c4 = reinterpret_cast<const float4*>(consts) + hd * 8;    // bias | LN weight (+32) | LN bias (+64)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] += consts[hd * 32 + j];
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 bb = c4[j4];
+                        v[4 * j4] += bb.x; v[4 * j4 + 1] += bb.y; v[4 * j4 + 2] += bb.z; v[4 * j4 + 3] += bb.w;
+                    }
                     if (lnw != nullptr) {
                         float s = 0.0f;
 #pragma unroll
@@ -461,8 +467,13 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                         for (int j = 0; j < 32; ++j) { const float d = v[j] - mu; qq += d * d; }
                         const float inv = 1.0f / sqrtf(qq * (1.0f / 32.0f) + e.eps);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            v[j] = (v[j] - mu) * inv * consts[128 + hd * 32 + j] + consts[256 + hd * 32 + j];
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 w = c4[32 + j4], lb = c4[64 + j4];
+                            v[4 * j4] = (v[4 * j4] - mu) * inv * w.x + lb.x;
+                            v[4 * j4 + 1] = (v[4 * j4 + 1] - mu) * inv * w.y + lb.y;
+                            v[4 * j4 + 2] = (v[4 * j4 + 2] - mu) * inv * w.z + lb.z;
+                            v[4 * j4 + 3] = (v[4 * j4 + 3] - mu) * inv * w.w + lb.w;
+                        }
                     }
                     if (rok) {
                         float* o = out + (((int64_t)b * e.H + hd) * dpk + e.d_pos) * e.S + s_;
