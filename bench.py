@@ -223,10 +223,15 @@ def micro_cases(device):
         return (lambda: ops.ffn_tc(x, w1, b1, w2, b2, 'relu', x)), B * S * (128 + 128 + 128) * 4, 2 * 2 * B * S * 128 * 256
     cases['ffn_fused'] = ffn_fused
 
-    def lin_tc(B=64, S=2809, K=128, N=128):
+    def lin_tc(B=64, S=2809, K=128, N=128, res=False):
         x, w, b_ = rnd(B * S, K), ops.TcWeight(rnd(K, N) / 11), rnd(N)
-        return (lambda: ops.linear_tc(x, w, b_, None)), B * S * (K + N) * 4, 2 * B * S * K * N
+        r = rnd(B * S, N) if res else None
+        return (lambda: ops.linear_tc(x, w, b_, None, r)), B * S * (K + N + (N if res else 0)) * 4, 2 * B * S * K * N
     cases['lin_tc'] = lin_tc
+    cases['lin_tc_k136'] = lambda: lin_tc(K=136, res=True)      # attention output projection + residual
+    cases['lin_tc_res'] = lambda: lin_tc(res=True)
+    cases['lin_tc_k136_nores'] = lambda: lin_tc(K=136)
+    cases['lin_tc_k160'] = lambda: lin_tc(K=160)
     cases['lin_tc_k256'] = lambda: lin_tc(K=256)
     cases['lin_tc_n32'] = lambda: lin_tc(N=32)
 

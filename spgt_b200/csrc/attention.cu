@@ -463,6 +463,8 @@ static int g_attn_impl = 0;               // 0 = tcgen05 kernel (attention_tc.cu
 int launch_attn_tc(const float* Q, const float* K, const float* V, float* out, float* t_out, int64_t BH, int H, int dpk,
                    int S, int merged, int cluster, cudaStream_t stream);
 
+void tc_set_pair_mode(int on);            // tc_gemm.cu
+
 }  // namespace spgt
 
 using namespace spgt;
@@ -647,6 +649,11 @@ extern "C" int spgt_set_tuning(const char* key, int value) {
     if (eq("attn_cluster")) {
         if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return SPGT_ERR_SHAPE;
         g_attn_cluster_override = value;
+        return SPGT_OK;
+    }
+    if (eq("tc_pair")) {
+        if (value < 0 || value > 2) return SPGT_ERR_SHAPE;
+        tc_set_pair_mode(value);
         return SPGT_OK;
     }
     if (eq("attn_impl")) {

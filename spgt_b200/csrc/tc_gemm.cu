@@ -128,21 +128,28 @@ template <int BN, int MT> struct TcCfg {
     static constexpr int SR = (MT == 1) ? 3 : 2;                    // raw A stages in shared memory
     static constexpr int STAGING_BYTES = 32 * TC_EPI_WARPS * TC_SLOT_BYTES;
     static constexpr int CONST_BYTES = 2048;                        // per-CTA epilogue constants (bias, LayerNorm affine, head vectors)
-    static constexpr int BAR_BYTES = 320;
+    static constexpr int BAR_BYTES = 384;
     static constexpr size_t BYTES = 1024 + (size_t)SB * B_BYTES + SR * RAW_BYTES + STAGING_BYTES + CONST_BYTES + BAR_BYTES;
 };
 
-template <int BN, int MT, class Loader, int EPI, class EpiParams>
+// PAIR = 1: the kernel runs as 2-CTA clusters.  Each CTA still loads, splits and finishes its own MT row tiles, but an
+// MMA (cta_group::2) covers 256 rows, tile m of both CTAs, and takes half of the W rows from each CTA's shared memory:
+// a CTA holds half of W, so a column tile of twice the K stays resident, and W is read from shared memory half as often
+// per row.  CTA m of the pair issues the MMAs of tile m (with one tile per CTA only CTA 0 issues).
+template <int BN, int MT, class Loader, int EPI, class EpiParams, int PAIR = 0>
 __global__ void __launch_bounds__(tc_threads(MT), 1)
 tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_units, EpiParams ep) {
     using C = TcCfg<BN, MT>;
-    constexpr int SA = C::SA, SB = C::SB, NBUF = C::NBUF, SR = C::SR;
+    constexpr int SA = C::SA, NBUF = C::NBUF, SR = C::SR;
+    // W stages: a CTA of a pair holds only half of the W rows of a k-block, so the same memory gives twice the stages
+    constexpr int SB = PAIR ? (2 * C::SB > 8 ? 8 : 2 * C::SB) : C::SB;
+    constexpr uint32_t B_STAGE = PAIR ? C::B_BYTES / 2 : C::B_BYTES;
     constexpr int NIWARPS = tc_mma_warps(MT);                       // MMA-issuing warps
     constexpr int TC_THREADS = tc_threads(MT), TC_EPI_WARP0 = tc_epi_warp0(MT);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // 1024-aligned for the 128B swizzle
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint8_t* raw = smem + SB * C::B_BYTES;                                      // raw A ring (1024-aligned stages)
+    uint8_t* raw = smem + C::SB * C::B_BYTES;                                      // raw A ring (1024-aligned stages)
     uint8_t* staging = raw + SR * C::RAW_BYTES;
     float* consts = reinterpret_cast<float*>(staging + C::STAGING_BYTES);
     uint8_t* bar_mem = staging + C::STAGING_BYTES + C::CONST_BYTES;
@@ -156,6 +163,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     auto acc_empty = [&](int b) { return bars + 8u * (26 + b); };       // [2]
     auto raw_full = [&](int s) { return bars + 8u * (28 + s); };        // [3]
     auto raw_empty = [&](int s) { return bars + 8u * (31 + s); };       // [3]
+    auto b_half = [&](int s) { return bars + 8u * (38 + s); };          // [8] pair mode: this CTA's half of a W stage has landed
     static_assert(SA <= 4 && SB <= 8 && SR <= 3 && NBUF <= 2, "barrier slots");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 288);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 296);
@@ -165,30 +173,36 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     const int KB = kpad / TC_BK;
     const bool resident = KB <= SB;          // the whole column tile of W stays in shared memory
 
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;            // CTA m of a pair issues the MMAs of row tile m
     if (tid == 0) {
-        for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), NIWARPS); }
+        for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), PAIR ? 8 : 128); mbar_init(a_empty(s), NIWARPS); }
         for (int s = 0; s < SR; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
-        for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), NIWARPS); }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), NIWARPS); mbar_init(acc_empty(b), 32 * TC_EPI_WARPS); }
+        for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), PAIR ? 2 : 1); mbar_init(b_half(s), 1); mbar_init(b_empty(s), NIWARPS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), NIWARPS); mbar_init(acc_empty(b), PAIR ? 2 * TC_EPI_WARPS / MT : 32 * TC_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TC_MMA_WARP) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     // Epilogue constants of this CTA's column tile go to shared memory once: a global load issued from the epilogue
     // queues behind the producers' traffic and costs microseconds of latency per use.
     if constexpr (EPI == EPI_HEAD) {
         for (int i = tid; i < 256; i += TC_THREADS) consts[i] = i < 128 ? __ldg(ep.b1 + i) : __ldg(ep.w2 + i - 128);
     } else if constexpr (EPI == EPI_LINEAR) {
-        const int ntc = blockIdx.x % n_tiles;
+        const int ntc = (PAIR ? blockIdx.x / 2 : blockIdx.x) % n_tiles;
         for (int i = tid; i < BN; i += TC_THREADS) {
             const int col = ntc * BN + i;
             consts[i] = (ep.bias != nullptr && col < ep.N) ? __ldg(ep.bias + col) : 0.0f;
         }
     } else {
-        const int p = blockIdx.x % n_tiles;
+        const int p = (PAIR ? blockIdx.x / 2 : blockIdx.x) % n_tiles;
         for (int i = tid; i < 128; i += TC_THREADS) {
             consts[i] = ep.bias[p] ? __ldg(ep.bias[p] + i) : 0.0f;
             consts[128 + i] = ep.lnw[p] ? __ldg(ep.lnw[p] + i) : 1.0f;
@@ -196,17 +210,21 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         }
     }
     tc_fence_before();
-    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();     // the partner's barriers are initialised too
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + C::ACC_COLS;
 
-    // Work distribution: this CTA keeps one column tile (so a resident W is loaded once) and strides over row units.
-    const int ctas_per_nt = gridDim.x / n_tiles;
-    const int nt = blockIdx.x % n_tiles;
-    const int u0 = blockIdx.x / n_tiles;
+    // Work distribution: this CTA (pair) keeps one column tile (so a resident W is loaded once) and strides over row
+    // units; in pair mode a unit is 512 rows, two tiles for each CTA of the pair.
+    const int sched_id = PAIR ? blockIdx.x / 2 : blockIdx.x, sched_n = PAIR ? gridDim.x / 2 : gridDim.x;
+    const int ctas_per_nt = sched_n / n_tiles;
+    const int nt = sched_id % n_tiles;
+    const int u0 = sched_id / n_tiles;
     const int n_my_units = (u0 < m_units) ? (m_units - u0 + ctas_per_nt - 1) / ctas_per_nt : 0;
     const float* wtile = wimg + (int64_t)nt * KB * (C::B_BYTES / 4);
+    // first row tile of unit ui (MT tiles follow each other; in pair mode the two CTAs take one tile each)
+    auto unit_tile0 = [&](int ui) { return (PAIR ? (u0 + ui * ctas_per_nt) * 2 + (int)crank : u0 + ui * ctas_per_nt) * MT; };
 
     if (warp < 4) {
         // ------------------------------------------ A loaders ------------------------------------------
@@ -218,7 +236,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         TcRing rr;
         bool alive = true;
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
-            const int row0 = (u0 + ui * ctas_per_nt) * MT * TC_BM + (t >> 3);
+            const int row0 = unit_tile0(ui) * TC_BM + (t >> 3);
             typename Loader::Row rs[MT][8];
 #pragma unroll
             for (int m = 0; m < MT; ++m)
@@ -286,7 +304,17 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             mbar_arrive(raw_empty(sr));                         // the raw stage has been read
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(a_full(sa));
+            if constexpr (PAIR) {                 // every issuing CTA (CTA m issues tile m) reads both CTAs' tiles;
+                __syncwarp();                     // one arrival per warp: arrivals that cross to the other SM are slow
+                if (lane == 0) {
+#pragma unroll
+                    for (uint32_t c = 0; c < (uint32_t)MT; ++c) {
+                        if (c == crank) mbar_arrive(a_full(sa)); else mbar_arrive_cluster(cluster_map(a_full(sa), c));
+                    }
+                }
+            } else {
+                mbar_arrive(a_full(sa));
+            }
         }
     } else if (warp == TC_BLOAD_WARP) {
         // ------------------------------------------ W loader ------------------------------------------
@@ -300,11 +328,34 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 if (!mbar_wait(b_empty(sb), ph ^ 1, abort_flag, 6, &g_tc_status)) break;
                 const int kb = kbw;
                 if (++kbw == KB) kbw = 0;
+                if constexpr (PAIR) {
+                    // this CTA's half of the W rows: hi rows at the start of the stage, lo rows a quarter stage later
+                    constexpr uint32_t QB = C::B_BYTES / 4;
+                    const float* src = wtile + (int64_t)kb * (C::B_BYTES / 4) + crank * (QB / 4);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_half(sb)), "r"(2 * QB) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(smem_base + sb * B_STAGE), "l"(src), "r"(QB), "r"(b_half(sb)) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(smem_base + sb * B_STAGE + QB), "l"(src + C::B_BYTES / 8), "r"(QB), "r"(b_half(sb)) : "memory");
+                } else {
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(sb)), "r"(bytes) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(smem_base + sb * C::B_BYTES), "l"(wtile + (int64_t)kb * (C::B_BYTES / 4)), "r"(bytes), "r"(b_full(sb)) : "memory");
+                             ::"r"(smem_base + sb * B_STAGE), "l"(wtile + (int64_t)kb * (C::B_BYTES / 4)), "r"(bytes), "r"(b_full(sb)) : "memory");
+                }
+            }
+        } else if (PAIR && lane == 1 && n_my_units > 0) {
+            // tell the issuing CTAs of the pair when this CTA's half of a W stage has landed
+            const int64_t total = resident ? KB : (int64_t)n_my_units * KB;
+            TcRing rb;
+            for (int64_t slot = 0; slot < total; ++slot, rb.template next<SB>()) {
+                if (!mbar_wait(b_half(rb.s), rb.ph, abort_flag, 9, &g_tc_status)) break;
+#pragma unroll
+                for (uint32_t c = 0; c < (uint32_t)MT; ++c) {
+                    if (c == crank) mbar_arrive(b_full(rb.s)); else mbar_arrive_cluster(cluster_map(b_full(rb.s), c));
+                }
             }
         }
+        __syncwarp();
     } else if (warp < TC_MMA_WARP + NIWARPS) {
         // ------------------------------------------ MMA issuers ------------------------------------------
         // One thread issues a tcgen05.mma about every 54 cycles, while a 128 x 64 x 8 tf32 MMA occupies the tensor
@@ -314,13 +365,15 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         const int iw = warp - TC_MMA_WARP;
         constexpr int NI = BN;                                              // N of one instruction
         {
-        constexpr uint32_t idesc = tc_idesc(NI);
+        constexpr uint32_t idesc = PAIR ? tc2_idesc(NI) : tc_idesc(NI);
         const uint32_t d_off = (MT == 2) ? (uint32_t)(iw * BN) : (uint32_t)(iw * NI);
         const uint32_t a_off = (MT == 2) ? (uint32_t)(iw * 64) : 0u;
         const uint32_t b_off = (MT == 2) ? 0u : (uint32_t)(iw * NI * 128);   // NI rows of 128 bytes
         // Only lane 0 runs the loop (waits included): no divergence and reconvergence per k-block.  The B descriptors
         // differ between stages only in the address field of their low word, so they are advanced with 32-bit adds.
-        if (lane == 0) {
+        if (PAIR && iw != (int)crank) {
+            // CTA m of a pair issues tile m only
+        } else if (lane == 0) {
             const uint64_t desc0 = tc_smem_desc(smem_base + b_off);
             const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
             TcRing ra, rb;
@@ -345,8 +398,21 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     }
                     if (kb == 0 && iw == 0) TC_TRACE(ui, 6);
                     tc_fence_after();
-                    const uint32_t bh = desc_lo0 + sb * (uint32_t)(C::B_BYTES >> 4), bl = bh + (uint32_t)(C::B_BYTES >> 5);
+                    const uint32_t bh = desc_lo0 + sb * (B_STAGE >> 4), bl = bh + (B_STAGE >> 5);
                     const uint32_t ah = tmem_a + sa * MT * 64 + a_off, al = ah + 32;
+                    if constexpr (PAIR) {
+                        tc2_mma_tf32_ts(d, al, bh, desc_hi, idesc, kb > 0 ? 1u : 0u);
+                        tc2_mma_tf32_ts(d, ah, bl, desc_hi, idesc, 1u);
+                        tc2_mma_tf32_ts(d, ah, bh, desc_hi, idesc, 1u);
+#pragma unroll
+                        for (int k8 = 1; k8 < TC_BK / 8; ++k8) {
+                            tc2_mma_tf32_ts(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc, 1u);
+                            tc2_mma_tf32_ts(d, ah + k8 * 8, bl + k8 * 2, desc_hi, idesc, 1u);
+                            tc2_mma_tf32_ts(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc, 1u);
+                        }
+                        tc2_commit(a_empty(sa));           // arrives in both CTAs of the pair
+                        if (!resident) tc2_commit(b_empty(sb));
+                    } else {
                     tc_mma_tf32_ts_p(d, al, bh, desc_hi, idesc, kb > 0 ? 1u : 0u);
                     tc_mma_tf32_ts_acc(d, ah, bl, desc_hi, idesc);
                     tc_mma_tf32_ts_acc(d, ah, bh, desc_hi, idesc);
@@ -359,7 +425,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     tc_commit(a_empty(sa));            // A stage reusable once both issuers' MMAs have read it
                     if (!resident) tc_commit(b_empty(sb));
                 }
-                if (alive) tc_commit(acc_full(buf));
+                    }
+                if (alive) { if constexpr (PAIR) tc2_commit(acc_full(buf)); else tc_commit(acc_full(buf)); }
                 if (iw == 0) TC_TRACE(ui, 7);
             }
         }
@@ -376,6 +443,28 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         const int epi_idx = (warp - TC_EPI_WARP0) * 32 + lane;
         float* slot_ptr = reinterpret_cast<float*>(staging + epi_idx * TC_SLOT_BYTES);
         bool alive = true;
+        // LINEAR epilogue with a residual: the residual values of the elements this thread stores in the next store
+        // phase are fetched one phase ahead (the first ones while the accumulator is still being computed); a load
+        // issued where it is needed queues behind the producers' traffic and stalls the store phase for microseconds.
+        constexpr int EP_PASS = tc_cols_per_thread(BN, MT) > 32 ? 32 : tc_cols_per_thread(BN, MT);
+        constexpr int EP_LPR = EP_PASS / 4, EP_RPI = 32 / EP_LPR, EP_NIT = 32 / EP_RPI;
+        float4 rres[EP_NIT];
+        auto res_fetch = [&](int ui_, int c0_) {
+            if constexpr (EPI == EPI_LINEAR) {
+                const TcLinearEpi& e = ep;
+                const int row0_ = (unit_tile0(ui_) + mt_e) * TC_BM + q * 32 + lane / EP_LPR;
+                const int col_ = nt * BN + c0_ + (lane % EP_LPR) * 4;
+#pragma unroll
+                for (int i = 0; i < EP_NIT; ++i) {
+                    const int orow = row0_ + i * EP_RPI;
+                    rres[i] = (col_ < e.N && orow < rows) ? __ldg(reinterpret_cast<const float4*>(e.residual + (int64_t)orow * e.ldr + col_))
+                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+        };
+        if constexpr (EPI == EPI_LINEAR) {
+            if (ep.residual != nullptr && n_my_units > 0) res_fetch(0, (MT == 1) ? half * tc_cols_per_thread(BN, MT) : 0);
+        }
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
             if (epi_idx == 0) TC_TRACE(ui, 8);
@@ -383,8 +472,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             if (!okf) { alive = false; break; }
             if (epi_idx == 0) TC_TRACE(ui, 9);
             tc_fence_after();
-            const int unit = u0 + ui * ctas_per_nt;
-            const int row = (unit * MT + mt_e) * TC_BM + r_in_tile;
+            const int tile = unit_tile0(ui) + mt_e;
+            const int row = tile * TC_BM + r_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (buf * MT + mt_e) * BN;
 
             if constexpr (EPI == EPI_LINEAR) {
@@ -393,7 +482,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 constexpr int LPR = PASS / 4;                    // lanes per row in the store phase (float4 each)
                 constexpr int RPI = 32 / LPR;                    // rows per store instruction
                 const uint8_t* warp_stage = staging + (warp - TC_EPI_WARP0) * 32 * TC_SLOT_BYTES;
-                const int tile_row0 = (unit * MT + mt_e) * TC_BM + q * 32;
+                const int tile_row0 = tile * TC_BM + q * 32;
 #pragma unroll 1
                 for (int c0 = col_lo; c0 < col_lo + CPT; c0 += PASS) {
                     // phase 1: each thread finishes its own row (bias, activation) into its padded staging slot
@@ -421,20 +510,33 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 12);
                     // phase 2: the warp writes its 32 rows with full-line coalesced float4 stores (+ residual)
                     const int col = nt * BN + c0 + (lane % LPR) * 4;
+                    static_assert(PASS == EP_PASS && 32 / RPI == EP_NIT, "residual prefetch follows the store phase's mapping");
                     if (col < e.N) {
-#pragma unroll 4
-                        for (int i = 0; i < 32 / RPI; ++i) {
-                            const int rr = i * RPI + lane / LPR;
-                            const int orow = tile_row0 + rr;
-                            if (orow < rows) {
-                                float4 o = *reinterpret_cast<const float4*>(warp_stage + rr * TC_SLOT_BYTES + (lane % LPR) * 16);
-                                if (e.residual) {
-                                    const float4 r = __ldg(reinterpret_cast<const float4*>(e.residual + (int64_t)orow * e.ldr + col));
-                                    o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+                        if (e.residual) {
+#pragma unroll
+                            for (int i = 0; i < 32 / RPI; ++i) {
+                                const int rr = i * RPI + lane / LPR;
+                                const int orow = tile_row0 + rr;
+                                if (orow < rows) {
+                                    float4 o = *reinterpret_cast<const float4*>(warp_stage + rr * TC_SLOT_BYTES + (lane % LPR) * 16);
+                                    o.x += rres[i].x; o.y += rres[i].y; o.z += rres[i].z; o.w += rres[i].w;
+                                    *reinterpret_cast<float4*>(e.y + (int64_t)orow * e.ldc + col) = o;
                                 }
-                                *reinterpret_cast<float4*>(e.y + (int64_t)orow * e.ldc + col) = o;
+                            }
+                        } else {
+#pragma unroll 4
+                            for (int i = 0; i < 32 / RPI; ++i) {
+                                const int rr = i * RPI + lane / LPR;
+                                const int orow = tile_row0 + rr;
+                                if (orow < rows)
+                                    *reinterpret_cast<float4*>(e.y + (int64_t)orow * e.ldc + col) =
+                                        *reinterpret_cast<const float4*>(warp_stage + rr * TC_SLOT_BYTES + (lane % LPR) * 16);
                             }
                         }
+                    }
+                    if (e.residual) {                // the next store phase's residual values: next pass, else next unit
+                        if (c0 + PASS < col_lo + CPT) res_fetch(ui, c0 + PASS);
+                        else if (ui + 1 < n_my_units) res_fetch(ui + 1, col_lo);
                     }
                     __syncwarp();
                     if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 13);
@@ -524,17 +626,23 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 }
             }
             tc_fence_before();
-            mbar_arrive(acc_empty(buf));
+            if constexpr (PAIR) {                 // one arrival per warp, to the CTA that issues tile mt_e
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(cluster_map(acc_empty(buf), (uint32_t)mt_e));
+            } else {
+                mbar_arrive(acc_empty(buf));
+            }
             if (epi_idx == 0) TC_TRACE(ui, 10);
         }
     }
     TC_ACC_FLUSH;
     // teardown: everyone meets, then the allocating warp frees the tensor memory
     tc_fence_before();
-    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();     // the pair's MMAs read both CTAs' memories
     if (warp == TC_MMA_WARP) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
 }
 
@@ -563,9 +671,13 @@ __global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, i
 // 136-wide merged attention heads) two 64-wide column tiles with W resident beat one 128-wide tile that re-streams W
 // for every row tile, the second read of the rows coming from L2.  At K = 256 the doubled row traffic costs more
 // than the W stream (measured: 0.125 vs 0.094 ms for 180k rows).
+static int g_tc_pair = 0;                 // experiment switch: CTA-pair kernels (1: one row tile per CTA, 2: two)
+void tc_set_pair_mode(int on) { g_tc_pair = on; }
+
 static int tc_bn_for(int N, int K) {
     if (N <= 32) return 32;
     if (N <= 64) return 64;
+    if (g_tc_pair == 1) return 128;           // a pair keeps a 128-wide W resident up to K = 256
     return (K > 128 && K <= 192) ? 64 : 128;
 }
 
@@ -586,10 +698,39 @@ static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_til
     return launch_status();
 }
 
+// The same kernel as 2-CTA clusters: a unit is MT row tiles for each CTA of the pair.
+template <int BN, int MT, class Loader, int EPI, class EpiParams>
+static int tc_launch_pair(Loader ld, const float* wimg, int kpad, int rows, int n_tiles, const EpiParams& ep, cudaStream_t st) {
+    static bool done = false;
+    auto kern = tc_gemm_kernel<BN, MT, Loader, EPI, EpiParams, 1>;
+    if (!done) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcCfg<BN, MT>::BYTES) != cudaSuccess) return launch_status();
+        done = true;
+    }
+    const int m_units = ceil_div(rows, TC_BM * MT * 2);
+    int per_nt = (num_sms() / 2) / n_tiles;           // pairs per column tile
+    if (per_nt < 1) per_nt = 1;
+    if (per_nt > m_units) per_nt = m_units;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * per_nt * n_tiles);
+    cfg.blockDim = dim3(tc_threads(MT));
+    cfg.dynamicSmemBytes = TcCfg<BN, MT>::BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ld, wimg, kpad, rows, n_tiles, m_units, ep) != cudaSuccess) return launch_status();
+    return launch_status();
+}
+
 template <class Loader>
 static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int rows, const TcLinearEpi& ep, bool long_k, cudaStream_t st) {
     const int bn = tc_bn_for(N, K), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
     const int n_tiles = npad / bn;
+    if (g_tc_pair == 2 && bn == 128) return tc_launch_pair<128, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+    if (g_tc_pair == 1 && bn == 128 && !long_k) return tc_launch_pair<128, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     if (long_k && bn == 128) return tc_launch<128, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     if (long_k && bn == 64) return tc_launch<64, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     switch (bn) {
