@@ -271,13 +271,26 @@ tc_ffn_kernel(const float* __restrict__ x, int lda, const float* __restrict__ w1
                 mbar_arrive(a_full(sa));
             }
             if (!alive) break;
-            // epilogue of GEMM2: columns [half * 64, +64) of the 128 outputs, 32 at a time through the staging slots
-            if (!mbar_wait(d2_full, tph, abort_flag, 33, &g_ffn_status)) break;
-            tc_fence_after();
+            // epilogue of GEMM2: columns [half * 64, +64) of the 128 outputs, 32 at a time through the staging slots.
+            // The residual values of the elements this thread will store are fetched while GEMM2 is still running: a
+            // load issued in the store phase queues behind the producers' traffic and stalls it for microseconds.
             const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
             const int tile_row0 = tile * TC_BM + q * 32;
-#pragma unroll 1
-            for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+            float4 rres[8];
+            auto res_fetch = [&](int c0_) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int orow = tile_row0 + i * 4 + (lane >> 3);
+                    rres[i] = orow < rows ? __ldg(reinterpret_cast<const float4*>(residual + (int64_t)orow * ldr + c0_ + (lane & 7) * 4))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            };
+            if (residual != nullptr) res_fetch(half * 64);
+            if (!mbar_wait(d2_full, tph, abort_flag, 33, &g_ffn_status)) break;
+            tc_fence_after();
+#pragma unroll
+            for (int ps = 0; ps < 2; ++ps) {
+                const int c0 = half * 64 + ps * 32;
 #pragma unroll 1
                 for (int cc = 0; cc < 32; cc += 16) {
                     float v[16];
@@ -292,19 +305,20 @@ tc_ffn_kernel(const float* __restrict__ x, int lda, const float* __restrict__ w1
                 if (c0 + 32 >= half * 64 + 64) { tc_fence_before(); mbar_arrive(d2_empty); }   // D2 is in registers / staging
                 __syncwarp();
                 const int col = c0 + (lane & 7) * 4;
-#pragma unroll 4
+#pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int rr = i * 4 + (lane >> 3);
                     const int orow = tile_row0 + rr;
                     if (orow < rows) {
                         float4 o = *reinterpret_cast<const float4*>(warp_stage + rr * FF_SLOT_BYTES + (lane & 7) * 16);
                         if (residual != nullptr) {
-                            const float4 rv = __ldg(reinterpret_cast<const float4*>(residual + (int64_t)orow * ldr + col));
+                            const float4 rv = rres[i];
                             o.x += rv.x; o.y += rv.y; o.z += rv.z; o.w += rv.w;
                         }
                         *reinterpret_cast<float4*>(y + (int64_t)orow * ldc + col) = o;
                     }
                 }
+                if (ps == 0 && residual != nullptr) res_fetch(half * 64 + 32);
                 __syncwarp();
             }
         }

@@ -468,6 +468,25 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
             if (epi_idx == 0) TC_TRACE(ui, 8);
+            float posv[8];                     // PROJ: this row's position values, fetched while the accumulator is still being computed
+            if constexpr (EPI == EPI_PROJ) {
+                const int prow = (unit_tile0(ui) + mt_e) * TC_BM + r_in_tile;
+#pragma unroll
+                for (int pp = 0; pp < 8; ++pp)
+                    posv[pp] = (pp < ep.d_pos && prow < rows) ? __ldg(ep.pos + (int64_t)prow * ep.d_pos + pp) : 0.0f;
+            }
+            float head_sc = 0.0f, head_sh = 0.0f;   // HEAD: this row's de-normalisation and frame flag, prepared ahead in the same way
+            bool head_edge = false;
+            if constexpr (EPI == EPI_HEAD) {
+                const int prow = (unit_tile0(ui) + mt_e) * TC_BM + r_in_tile;
+                if (half == 0 && prow < rows) {
+                    const int prem = prow % (ep.Hh * ep.Ww);
+                    head_sc = ep.scale_map ? __ldg(ep.scale_map + prem) : ep.scale;
+                    head_sh = ep.shift_map ? __ldg(ep.shift_map + prem) : ep.shift;
+                    const int y = prem / ep.Ww, x = prem - y * ep.Ww;
+                    head_edge = ep.dirichlet && (y == 0 || x == 0 || y == ep.Hh - 1 || x == ep.Ww - 1);
+                }
+            }
             bool okf; TC_TADD(ui, 24, okf = mbar_wait(acc_full(buf), aph, abort_flag, 4, &g_tc_status));
             if (!okf) { alive = false; break; }
             if (epi_idx == 0) TC_TRACE(ui, 9);
@@ -581,8 +600,9 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                         float* o = out + (((int64_t)b * e.H + hd) * dpk + e.d_pos) * e.S + s_;
 #pragma unroll
                         for (int j = 0; j < 32; ++j) o[(int64_t)j * e.S] = v[j];     // lanes = consecutive s: coalesced
-                        for (int pp = 0; pp < e.d_pos; ++pp)
-                            out[(((int64_t)b * e.H + hd) * dpk + pp) * e.S + s_] = __ldg(e.pos + (int64_t)row * e.d_pos + pp);
+#pragma unroll
+                        for (int pp = 0; pp < 8; ++pp)
+                            if (pp < e.d_pos) out[(((int64_t)b * e.H + hd) * dpk + pp) * e.S + s_] = posv[pp];
                     }
                 }
             } else {
@@ -614,15 +634,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");   // epilogue warps only
                 if (half == 0 && row < rows) {
                     acc += part[(ui & 1) * 128 + r_in_tile];
-                    const int rem = row % (e.Hh * e.Ww);
-                    const float sc = e.scale_map ? __ldg(e.scale_map + rem) : e.scale;
-                    const float sh = e.shift_map ? __ldg(e.shift_map + rem) : e.shift;
-                    float o = (acc + e.b2) * sc + sh;
-                    if (e.dirichlet) {
-                        const int y = rem / e.Ww, x = rem - y * e.Ww;
-                        if (y == 0 || x == 0 || y == e.Hh - 1 || x == e.Ww - 1) o = 0.0f;
-                    }
-                    e.out[row] = o;
+                    e.out[row] = head_edge ? 0.0f : (acc + e.b2) * head_sc + head_sh;
                 }
             }
             tc_fence_before();
