@@ -5,7 +5,7 @@
 namespace spgt {
 
 constexpr int TC_BM = 128, TC_BK = 32;
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 19;   // about two seconds of polling before a wait gives up
 
 // ---- mbarrier / tcgen05 primitives -------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -128,6 +128,23 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
           "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
         : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Two 16-column loads (taddr and taddr + second_off) with one wait, summed: the two partial accumulators of a merged tile.
+__device__ __forceinline__ void tc_ld16_sum(uint32_t taddr, uint32_t second_off, float (&v)[16]) {
+    uint32_t a[16], b[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]),
+          "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15])
+        : "r"(taddr) : "memory");
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]),
+          "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15])
+        : "r"(taddr + second_off) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(a[j]) + __uint_as_float(b[j]);
 }
 // Store 16 consecutive 32-bit columns of this thread's TMEM lane.
 __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&u)[16]) {

@@ -118,8 +118,13 @@ struct TcHeadEpi {
 enum { EPI_LINEAR = 0, EPI_PROJ = 1, EPI_HEAD = 2 };
 
 template <int BN, int MT> struct TcCfg {
-    static constexpr int NBUF = (MT == 1 || BN <= 64) ? 2 : 1;      // accumulator buffers
-    static constexpr int ACC_COLS = NBUF * MT * BN;
+    // Column tiles of up to 64: W_hi and W_lo of a k-block lie one after the other in shared memory, so one MMA of
+    // twice the width computes A_hi W_hi and A_hi W_lo side by side (two partial accumulators, summed by the epilogue)
+    // and a k-step of 8 takes two MMA instructions instead of three; the issuing thread is what limits these tiles.
+    static constexpr bool MERGE = BN <= 64;
+    static constexpr int ACCW = MERGE ? 2 * BN : BN;                // accumulator columns of one row tile
+    static constexpr int NBUF = (MT == 1 || ACCW <= 64) ? 2 : 1;    // accumulator buffers
+    static constexpr int ACC_COLS = NBUF * MT * ACCW;
     static constexpr int SA = (MT == 1) ? 4 : 2;                    // A stages in TMEM, 64 columns (hi|lo) per tile
     static_assert(ACC_COLS + SA * MT * 64 <= 512, "tensor memory budget");
     static constexpr int B_BYTES = 2 * BN * TC_BK * 4;              // W_hi | W_lo image of one k-block
@@ -366,7 +371,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         constexpr int NI = BN;                                              // N of one instruction
         {
         constexpr uint32_t idesc = PAIR ? tc2_idesc(NI) : tc_idesc(NI);
-        const uint32_t d_off = (MT == 2) ? (uint32_t)(iw * BN) : (uint32_t)(iw * NI);
+        const uint32_t d_off = (MT == 2) ? (uint32_t)(iw * C::ACCW) : (uint32_t)(iw * NI);
         const uint32_t a_off = (MT == 2) ? (uint32_t)(iw * 64) : 0u;
         const uint32_t b_off = (MT == 2) ? 0u : (uint32_t)(iw * NI * 128);   // NI rows of 128 bytes
         // Only lane 0 runs the loop (waits included): no divergence and reconvergence per k-block.  The B descriptors
@@ -385,7 +390,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 if (!okc) break;
                 if (iw == 0) TC_TRACE(ui, 5);
                 tc_fence_after();
-                const uint32_t d = tmem_base + buf * MT * BN + d_off;
+                const uint32_t d = tmem_base + buf * MT * C::ACCW + d_off;
                 for (int kb = 0; kb < KB; ++kb, ra.template next<SA>(), rb.template next<SB>()) {
                     const uint32_t sa = ra.s, pa = ra.ph;
                     const uint32_t sb = resident ? (uint32_t)kb : rb.s;
@@ -410,8 +415,15 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                             tc2_mma_tf32_ts(d, ah + k8 * 8, bl + k8 * 2, desc_hi, idesc, 1u);
                             tc2_mma_tf32_ts(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc, 1u);
                         }
-                        tc2_commit(a_empty(sa));           // arrives in both CTAs of the pair
-                        if (!resident) tc2_commit(b_empty(sb));
+                    } else if constexpr (C::MERGE) {
+                        constexpr uint32_t idesc2 = tc_idesc(2 * NI);           // [W_hi | W_lo] as one operand of twice the rows
+                        tc_mma_tf32_ts_p(d, ah, bh, desc_hi, idesc2, kb > 0 ? 1u : 0u);
+                        tc_mma_tf32_ts_acc(d, al, bh, desc_hi, idesc);
+#pragma unroll
+                        for (int k8 = 1; k8 < TC_BK / 8; ++k8) {
+                            tc_mma_tf32_ts_acc(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc2);
+                            tc_mma_tf32_ts_acc(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc);
+                        }
                     } else {
                     tc_mma_tf32_ts_p(d, al, bh, desc_hi, idesc, kb > 0 ? 1u : 0u);
                     tc_mma_tf32_ts_acc(d, ah, bl, desc_hi, idesc);
@@ -422,10 +434,16 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                         tc_mma_tf32_ts_acc(d, ah + k8 * 8, bl + k8 * 2, desc_hi, idesc);
                         tc_mma_tf32_ts_acc(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc);
                     }
-                    tc_commit(a_empty(sa));            // A stage reusable once both issuers' MMAs have read it
-                    if (!resident) tc_commit(b_empty(sb));
-                }
                     }
+                    // the A stage (and a streamed W stage) is reusable once every issuer's MMAs have read it
+                    if constexpr (PAIR) {
+                        tc2_commit(a_empty(sa));           // arrives in both CTAs of the pair
+                        if (!resident) tc2_commit(b_empty(sb));
+                    } else {
+                        tc_commit(a_empty(sa));
+                        if (!resident) tc_commit(b_empty(sb));
+                    }
+                }
                 if (alive) { if constexpr (PAIR) tc2_commit(acc_full(buf)); else tc_commit(acc_full(buf)); }
                 if (iw == 0) TC_TRACE(ui, 7);
             }
@@ -493,7 +511,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             tc_fence_after();
             const int tile = unit_tile0(ui) + mt_e;
             const int row = tile * TC_BM + r_in_tile;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (buf * MT + mt_e) * BN;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (buf * MT + mt_e) * C::ACCW;
 
             if constexpr (EPI == EPI_LINEAR) {
                 const TcLinearEpi& e = ep;
@@ -508,7 +526,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
 #pragma unroll 1
                     for (int cc = 0; cc < PASS; cc += 16) {
                         float v[16];
-                        tc_ld16(taddr + c0 + cc, v);
+                        if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + cc, BN, v); else tc_ld16(taddr + c0 + cc, v);
                         if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 16 + cc / 16);
                         const int colb = nt * BN + c0 + cc;
 #pragma unroll
