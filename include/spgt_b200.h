@@ -40,7 +40,10 @@ int spgt_last_cuda_error(void);
 /* Library ABI version (bumped when a signature changes). */
 int spgt_abi_version(void);
 /* Experiment knobs: "attn_cluster" = 0 (heuristic), 1, 2, 4 or 8 CTAs per (batch, head) in spgt_galerkin_attn_fwd;
- * "attn_impl" = 0 (tcgen05 kernel, default) or 1 (warp-MMA kernel). */
+ * "attn_impl" = 0 (tcgen05 kernel, default) or 1 (warp-MMA kernel);
+ * "tc_pair" = 0 (default), 1 or 2: run the 128-column tcgen05 GEMM tiles as 2-CTA clusters (cta_group::2 MMAs over 256
+ * rows, half of W in each CTA's shared memory) with one or two row tiles per CTA.  It also changes the column tile that
+ * spgt_tc_weight_prepare lays W out for, so set it before preparing the weights that are used with it. */
 int spgt_set_tuning(const char* key, int value);
 
 /* ---------------------------------------------------------------------------------------------
