@@ -17,7 +17,12 @@
 //   * Row-major epilogues stage each thread's row in padded shared memory and leave as warp-cooperative coalesced
 //     float4 stores (full 128-byte lines, residual added on the way); the projection epilogue does the per-head
 //     LayerNorm thread-locally and stores head-major through the same staging; the decoder head keeps its
-//     constants in shared memory and reduces its row dot product across the two column halves.
+//     constants in shared memory and reduces its row dot product across the two column halves.  Whatever an
+//     epilogue reads from global memory (residual, position values, de-normalisation maps) is fetched one phase
+//     ahead, while the accumulator is still being computed.
+//   * Column tiles of up to 64 use two MMAs per k-step instead of three: A_hi * [W_hi | W_lo] as one instruction of
+//     twice the width into two partial accumulators, A_lo * W_hi into the first.
+//   * PAIR = 1 (experiment, off by default): 2-CTA clusters and cta_group::2 MMAs over 256 rows.
 //   warps 0-3 A loaders, 4-7 A splitters, 8 W loader, 9 (MT = 2: 9-10) MMA issuers (lane 0 runs the whole issue loop),
 //   then 8 epilogue warps.
 // All waits are bounded mbarrier polls: on expiry the kernel records an error code, stops waiting and returns.
