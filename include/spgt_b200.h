@@ -25,6 +25,7 @@ extern "C" {
 #define SPGT_ERR_WORKSPACE (-4)   /* workspace missing or smaller than the *_workspace_bytes() answer */
 #define SPGT_ERR_LAUNCH (-5)      /* the CUDA runtime refused the launch; see spgt_last_cuda_error() */
 #define SPGT_ERR_TOO_LARGE (-6)   /* the problem exceeds the fixed scratch of a *_noalloc entry point */
+#define SPGT_ERR_NOT_CONVERGED (-7) /* an iterative solver stopped at its iteration limit; outputs hold the last iterate */
 
 #define SPGT_ACT_NONE 0
 #define SPGT_ACT_RELU 1
@@ -139,6 +140,23 @@ int spgt_batched_skinny_gemm_noalloc(const float* A, const float* B, float* C, f
  * One block per sample, fixed summation order. */
 int spgt_relative_l2_fwd(const float* pred, const float* target, float* per_sample, int N, int64_t n_per_sample,
                          float eps, spgt_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Data generation (reference: dataset/darcy_generate/Solve_GWF.m, MATLAB)
+ * ------------------------------------------------------------------------------------------- */
+
+/* Finite-volume Darcy solve of the reference's generator, for B coefficient fields at once, in float64:
+ *   sum over the 4 neighbours n of (a[n] + a[i,j]) / 2 * (p[i,j] - p[n]) * (K-1)^2 = f[i,j]  on the interior nodes of the
+ *   K x K node grid, p = 0 on the boundary                          (the matrix of Solve_GWF.m:16-35).
+ * coef_nodes, f_nodes, p_nodes [B, K, K] float64 on the device (border values of f are ignored, the border of p is set
+ * to 0).  The reference calls MATLAB's sparse direct solver (Solve_GWF.m:38); this is a Jacobi-preconditioned conjugate
+ * gradient iteration with deterministic reductions, stopped when every sample has |r| <= rel_tol * |f| (checked every
+ * check_every iterations, which synchronises the stream) or after max_iter iterations (SPGT_ERR_NOT_CONVERGED, the
+ * last iterate is kept).  iters_out (one int) and relres_out ([B]) are HOST pointers and may be NULL. */
+size_t spgt_darcy_fv_workspace_bytes(int B, int K);
+int spgt_darcy_fv_solve(const double* coef_nodes, const double* f_nodes, double* p_nodes, int B, int K, int max_iter,
+                        double rel_tol, int check_every, void* workspace, size_t workspace_bytes, int* iters_out,
+                        double* relres_out, spgt_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Data-movement ops (reference: extension/bind/datamove.{py,cu}, extension/native/datamove.cu)

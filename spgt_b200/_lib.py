@@ -42,6 +42,8 @@ SIGNATURES = {
     'spgt_batched_skinny_gemm_noalloc': (_i, [_f, _f, _f, _fl, _i, _i, _i, _i, _st]),
     'spgt_ffn_tc_fwd': (_i, [_f, _i, _f, _f, _f, _f, _f, _i, _f, _i, _i, _i, _i, _i, _st]),
     'spgt_relative_l2_fwd': (_i, [_f, _f, _f, _i, C.c_int64, _fl, _st]),
+    'spgt_darcy_fv_workspace_bytes': (C.c_size_t, [_i, _i]),
+    'spgt_darcy_fv_solve': (_i, [_f, _f, _f, _i, _i, _i, C.c_double, _i, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, _st]),
     'spgt_batched_transpose': (_i, [_f, _f, _i, _i, _i, _st]),
     'spgt_transpose_gather_dual': (_i, [_f, _f, _f] + [_i] * 9 + [_st]),
     'spgt_transpose_scatter_dual': (_i, [_f, _f, _f] + [_i] * 9 + [_st]),

@@ -18,7 +18,7 @@ CSRC = os.path.join(PKG, 'csrc')
 INCLUDE = os.path.join(os.path.dirname(PKG), 'include')
 LIB = os.path.join(PKG, 'libspgt_b200.so')
 OBJ = os.path.join(PKG, 'build')
-SOURCES = ['abi.cu', 'datamove.cu', 'attention.cu', 'attention_tc.cu', 'attention_bwd.cu', 'projection_bwd.cu', 'gemm.cu', 'tc_gemm.cu', 'tc_ffn.cu', 'scaler.cu', 'spectral.cu', 'metric.cu']
+SOURCES = ['abi.cu', 'datamove.cu', 'attention.cu', 'attention_tc.cu', 'attention_bwd.cu', 'projection_bwd.cu', 'gemm.cu', 'tc_gemm.cu', 'tc_ffn.cu', 'scaler.cu', 'spectral.cu', 'metric.cu', 'darcy_solve.cu']
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
               '-Xcompiler', '-fPIC', '-I', INCLUDE]
 

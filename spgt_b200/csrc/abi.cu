@@ -14,6 +14,7 @@ extern "C" const char* spgt_error_string(int code) {
         case SPGT_ERR_WORKSPACE: return "workspace missing or too small";
         case SPGT_ERR_LAUNCH: return "the CUDA runtime refused the launch";
         case SPGT_ERR_TOO_LARGE: return "the problem needs more scratch than the fixed array of the no-allocation entry point holds";
+        case SPGT_ERR_NOT_CONVERGED: return "the iterative solver reached its iteration limit before the requested tolerance";
         default: return "unknown spgt error code";
     }
 }

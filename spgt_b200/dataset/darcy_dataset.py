@@ -89,7 +89,7 @@ def central_diff(X: np.ndarray, S: int):
 
 class DarcyDataset(torch.utils.data.Dataset):
     """The reference's Darcy dataset (dataset/darcy_dataset.py:48-175) for the inference path: coefficient `a` and
-    solution `u` of shape [N, R, R] from a .mat file, every sub-th node kept, the coefficient normalised per node.
+    solution `u` of shape [N, R, R] from a .mat file (or a dict holding those arrays), every sub-th node kept, the coefficient normalised per node.
 
     Items are dicts of float32 tensors: grid [r,r,2], position [r_attn,r_attn,2], coeff [r,r,1] (raw coefficient),
     node [r,r,1] (normalised), target [r,r,1], target_grad [r,r,2].  Training sets take the first num_data samples
@@ -105,7 +105,10 @@ class DarcyDataset(torch.utils.data.Dataset):
         self.subsample_attn = subsample_attn if subsample_attn is not None else 2 * subsample_node
         self.is_return_boundary, self.is_normalization = is_return_boundary, is_normalization
         self.node_normalizer, self.target_normalizer = node_normalizer, None
-        a, u = read_matfile(datapath, list(keys), [np.float32, np.float32])
+        if isinstance(datapath, dict):            # in-memory samples, e.g. from dataset.darcy_generate.generate()
+            a, u = (np.asarray(datapath[k], dtype=np.float32) for k in keys)
+        else:
+            a, u = read_matfile(datapath, list(keys), [np.float32, np.float32])
         N, R, _ = a.shape
         self.num_data = num_data if num_data is not None else N
         self.fine_resolution = fine_resolution if fine_resolution is not None else R

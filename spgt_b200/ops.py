@@ -5,6 +5,7 @@ torch.empty on the input's device and launches on torch's current stream.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from typing import Optional, Sequence, Tuple
 
@@ -198,6 +199,27 @@ def relative_l2(pred: Tensor, target: Tensor, eps: float = 1.0e-10) -> Tensor:
     out = torch.empty(N, dtype=torch.float32, device=pred.device)
     _call('spgt_relative_l2_fwd', pred.data_ptr(), target.data_ptr(), out.data_ptr(), N, pred.numel() // N, float(eps), _stream())
     return out
+
+
+def darcy_fv_solve(coef_nodes: Tensor, f_nodes: Tensor, rel_tol: float = 1.0e-10, max_iter: int = 20000,
+                   check_every: int = 100):
+    """Solve the finite-volume Darcy system of the reference's generator (dataset/darcy_generate/Solve_GWF.m:16-38) for
+    a batch of node coefficient fields: float64 CUDA tensors [B, K, K] in, (p [B, K, K], iterations, relative residuals
+    [B]) out.  Raises if the conjugate-gradient iteration does not reach rel_tol within max_iter."""
+    for t, n in ((coef_nodes, 'coef_nodes'), (f_nodes, 'f_nodes')):
+        if not (t.is_cuda and t.dtype == torch.float64):
+            raise ValueError(f'{n} must be a float64 CUDA tensor')
+    coef_nodes, f_nodes = coef_nodes.contiguous(), f_nodes.contiguous()
+    if coef_nodes.dim() != 3 or coef_nodes.shape[1] != coef_nodes.shape[2] or coef_nodes.shape != f_nodes.shape:
+        raise ValueError('coef_nodes and f_nodes must both be [B, K, K]')
+    B, K = coef_nodes.shape[0], coef_nodes.shape[1]
+    p = torch.empty_like(coef_nodes)
+    ws = torch.empty(int(lib.spgt_darcy_fv_workspace_bytes(B, K)), dtype=torch.uint8, device=coef_nodes.device)
+    iters = ctypes.c_int(0)
+    rel = (ctypes.c_double * B)()
+    _call('spgt_darcy_fv_solve', coef_nodes.data_ptr(), f_nodes.data_ptr(), p.data_ptr(), B, K, int(max_iter), float(rel_tol),
+          int(check_every), ws.data_ptr(), ws.numel(), ctypes.addressof(iters), ctypes.addressof(rel), _stream())
+    return p, iters.value, list(rel)
 
 
 def skinny_gemm_workspace_bytes(M: int, N: int, K: int, batch: int) -> int:
