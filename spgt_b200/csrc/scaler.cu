@@ -7,7 +7,7 @@ namespace spgt {
 // Source coordinate exactly as ATen computes it in fp32: scale = (in-1)/(out-1), src = scale*dst,
 // i0 = min(int(src), in-1), lambda = clamp(src - i0, 0, 1), i1 = i0 + (i0 < in-1).
 struct Tap { int i0, i1; float w0, w1; };
-__device__ __forceinline__ Tap make_tap(int dst, int in_size, int out_size) {
+__host__ __device__ __forceinline__ Tap make_tap(int dst, int in_size, int out_size) {
     Tap tp;
     if (in_size == out_size) { tp.i0 = tp.i1 = dst; tp.w0 = 1.0f; tp.w1 = 0.0f; return tp; }
     const float scale = out_size > 1 ? (float)(in_size - 1) / (float)(out_size - 1) : 0.0f;
@@ -182,6 +182,104 @@ upsample_grid_kernel(const float4* __restrict__ uw, const float2* __restrict__ g
     }
 }
 
+// Up-sampling variant of the two kernels above (MODE 0: bilinear_kernel, MODE 1: upsample_grid_kernel, the same
+// arithmetic in the same order).  When the output has more rows than the input every source row is a tap of several
+// output rows and every source pixel of several output pixels; gathered straight from global memory most of those
+// reads miss L1 and the kernel runs at the L2 rate.  Here a block takes G consecutive output rows of one image,
+// copies the few source rows they need (contiguous in NHWC) into shared memory once with 16-byte cp.async, and lerps
+// from there: global reads are ns / G source rows per output row, all coalesced.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+lerp_staged_kernel(const float4* __restrict__ x, float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int C4, int act,
+                   const float2* __restrict__ grid, const float4* __restrict__ wg, const float4* __restrict__ bias, int G,
+                   int groups_per_img, int n_groups) {
+    extern __shared__ float4 srow[];                       // the source rows of the current group
+    const int row_f4 = Wi * C4, per_row = Wo * C4;
+    const int c = threadIdx.x % C4, x0 = threadIdx.x / C4, x_step = blockDim.x / C4;     // blockDim.x % C4 == 0 (host)
+    float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0, bb = g0;
+    if (MODE == 1) { g0 = __ldg(wg + c); g1 = __ldg(wg + C4 + c); bb = __ldg(bias + c); }
+    for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
+        const int b = grp / groups_per_img, y0 = (grp - b * groups_per_img) * G;
+        const int y1 = y0 + G < Ho ? y0 + G : Ho;
+        const int s_lo = make_tap(y0, Hi, Ho).i0, s_hi = make_tap(y1 - 1, Hi, Ho).i1;
+        const float4* src = x + ((int64_t)b * Hi + s_lo) * row_f4;
+        __syncthreads();                                   // the previous group has been read
+        for (int i = threadIdx.x; i < (s_hi - s_lo + 1) * row_f4; i += blockDim.x) cp_async_zfill<16>(srow + i, src + i, true);
+        cp_async_commit();
+        cp_async_wait_all();
+        __syncthreads();
+        for (int yo = y0; yo < y1; ++yo) {
+            const Tap ty = make_tap(yo, Hi, Ho);
+            const float4* r0 = srow + (ty.i0 - s_lo) * row_f4;
+            const float4* r1 = srow + (ty.i1 - s_lo) * row_f4;
+            const int64_t row = (int64_t)b * Ho + yo;
+            float4* yr = y + row * per_row;
+            const float2* gr = MODE == 1 ? grid + row * Wo : nullptr;
+            int xo = x0;
+            for (int e = threadIdx.x; e < per_row; e += blockDim.x, xo += x_step) {
+                const Tap tx = make_tap(xo, Wi, Wo);
+                const float4 v00 = r0[tx.i0 * C4 + c], v01 = r0[tx.i1 * C4 + c];
+                const float4 v10 = r1[tx.i0 * C4 + c], v11 = r1[tx.i1 * C4 + c];
+                const float w00 = ty.w0 * tx.w0, w01 = ty.w0 * tx.w1, w10 = ty.w1 * tx.w0, w11 = ty.w1 * tx.w1;
+                float4 o;
+                if (MODE == 1) {
+                    const float2 gxy = __ldg(gr + xo);
+                    o.x = v00.x * w00 + v01.x * w01 + v10.x * w10 + v11.x * w11 + gxy.x * g0.x + gxy.y * g1.x + bb.x;
+                    o.y = v00.y * w00 + v01.y * w01 + v10.y * w10 + v11.y * w11 + gxy.x * g0.y + gxy.y * g1.y + bb.y;
+                    o.z = v00.z * w00 + v01.z * w01 + v10.z * w10 + v11.z * w11 + gxy.x * g0.z + gxy.y * g1.z + bb.z;
+                    o.w = v00.w * w00 + v01.w * w01 + v10.w * w10 + v11.w * w11 + gxy.x * g0.w + gxy.y * g1.w + bb.w;
+                } else {
+                    o.x = apply_act(v00.x * w00 + v01.x * w01 + v10.x * w10 + v11.x * w11, act);
+                    o.y = apply_act(v00.y * w00 + v01.y * w01 + v10.y * w10 + v11.y * w11, act);
+                    o.z = apply_act(v00.z * w00 + v01.z * w01 + v10.z * w10 + v11.z * w11, act);
+                    o.w = apply_act(v00.w * w00 + v01.w * w01 + v10.w * w10 + v11.w * w11, act);
+                }
+                yr[e] = o;
+            }
+        }
+    }
+}
+
+static unsigned grid_for(int64_t items, int threads, int per_sm) {
+    const int64_t want = ceil_div(items, (int64_t)threads);
+    const int64_t cap = (int64_t)num_sms() * per_sm;
+    return (unsigned)(want < cap ? want : cap);
+}
+
+// Rows per group and shared-memory bytes of lerp_staged_kernel for an up-sampling shape, or G = 0 when the gather
+// kernels should be used (down-sampling, channel counts that do not divide the block, rows too long).
+struct StagedPlan { int G; size_t smem; };
+static StagedPlan staged_plan(int Hi, int Wi, int Ho, int C4) {
+    StagedPlan p{0, 0};
+    if (Ho <= Hi || 256 % C4 != 0) return p;
+    const size_t row_bytes = (size_t)Wi * C4 * sizeof(float4);
+    for (int G = 4; G >= 2; G -= 2) {
+        int ns = 0;
+        for (int y0 = 0; y0 < Ho; y0 += G) {
+            const int y1 = y0 + G < Ho ? y0 + G : Ho;
+            const int n = make_tap(y1 - 1, Hi, Ho).i1 - make_tap(y0, Hi, Ho).i0 + 1;
+            if (n > ns) ns = n;
+        }
+        if (ns * row_bytes <= (G == 4 ? 48u : 100u) * 1024u) { p.G = G; p.smem = ns * row_bytes; return p; }
+    }
+    return p;
+}
+template <int MODE>
+static int launch_staged(const StagedPlan& p, const float4* x, float4* y, int B, int Hi, int Wi, int Ho, int Wo, int C4, int act,
+                         const float2* grid, const float4* wg, const float4* bias, cudaStream_t st) {
+    static size_t configured = 0;
+    if (p.smem > configured) {
+        if (cudaFuncSetAttribute(lerp_staged_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess) return launch_status();
+        configured = p.smem;
+    }
+    const int gpi = ceil_div(Ho, p.G);
+    const int64_t n_groups = (int64_t)B * gpi;
+    const int per_sm = (int)(200 * 1024 / (p.smem + 1024));
+    lerp_staged_kernel<MODE><<<grid_for(n_groups, 1, per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm)), 256, p.smem, st>>>(
+        x, y, Hi, Wi, Ho, Wo, C4, act, grid, wg, bias, p.G, gpi, (int)n_groups);
+    return launch_status();
+}
+
 // y[b,yo,xo,:] = act(bilinear(concat(x1[..., :c1], x2[..., :c2], x3[..., :c3])))  -- the three sources keep their own
 // (padded) channel pitch, the output is dense.  One thread per (pixel, 4 output channels), scalar gathers.
 __global__ void __launch_bounds__(256)
@@ -217,12 +315,6 @@ bilinear_concat3_kernel(const float* __restrict__ x1, const float* __restrict__ 
     }
 }
 
-static unsigned grid_for(int64_t items, int threads, int per_sm) {
-    const int64_t want = ceil_div(items, (int64_t)threads);
-    const int64_t cap = (int64_t)num_sms() * per_sm;
-    return (unsigned)(want < cap ? want : cap);
-}
-
 }  // namespace spgt
 
 using namespace spgt;
@@ -234,6 +326,10 @@ extern "C" int spgt_bilinear_fwd(const float* x, float* y, int B, int Hi, int Wi
     if (!aligned16(x) || !aligned16(y)) return SPGT_ERR_ALIGN;
     const int64_t rows = (int64_t)B * Ho;
     if (rows > 0x7fffffffLL || (int64_t)Wo * (C / 4) > 0x7fffffffLL || (int64_t)Wi * (C / 4) > 0x7fffffffLL) return SPGT_ERR_SHAPE;
+    const StagedPlan plan = staged_plan(Hi, Wi, Ho, C / 4);
+    if (plan.G > 0)
+        return launch_staged<0>(plan, reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), B, Hi, Wi, Ho, Wo, C / 4, act,
+                                nullptr, nullptr, nullptr, (cudaStream_t)stream);
     bilinear_kernel<<<grid_for(rows, 1, 8), 256, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), Hi, Wi, Ho, Wo, C / 4, act, (int)rows);
     return launch_status();
@@ -274,6 +370,11 @@ extern "C" int spgt_upsample_grid_fwd(const float* uw, const float* grid, const 
     if (!aligned16(uw) || !aligned16(grid) || !aligned16(wg) || !aligned16(bias) || !aligned16(y)) return SPGT_ERR_ALIGN;
     const int64_t rows = (int64_t)B * Ho;
     if (rows > 0x7fffffffLL || (int64_t)Wo * (C / 4) > 0x7fffffffLL || (int64_t)Wi * (C / 4) > 0x7fffffffLL) return SPGT_ERR_SHAPE;
+    const StagedPlan plan = staged_plan(Hi, Wi, Ho, C / 4);
+    if (plan.G > 0)
+        return launch_staged<1>(plan, reinterpret_cast<const float4*>(uw), reinterpret_cast<float4*>(y), B, Hi, Wi, Ho, Wo, C / 4, 0,
+                                reinterpret_cast<const float2*>(grid), reinterpret_cast<const float4*>(wg),
+                                reinterpret_cast<const float4*>(bias), (cudaStream_t)stream);
     upsample_grid_kernel<<<grid_for(rows, 1, 8), 256, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const float4*>(uw), reinterpret_cast<const float2*>(grid), reinterpret_cast<const float4*>(wg),
         reinterpret_cast<const float4*>(bias), reinterpret_cast<float4*>(y), Hi, Wi, Ho, Wo, C / 4, (int)rows);
