@@ -188,8 +188,9 @@ upsample_grid_kernel(const float4* __restrict__ uw, const float2* __restrict__ g
 // reads miss L1 and the kernel runs at the L2 rate.  Here a block takes G consecutive output rows of one image,
 // copies the few source rows they need (contiguous in NHWC) into shared memory once with 16-byte cp.async, and lerps
 // from there: global reads are ns / G source rows per output row, all coalesced.
+constexpr int LS_THREADS = 512;
 template <int MODE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(LS_THREADS)
 lerp_staged_kernel(const float4* __restrict__ x, float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int C4, int act,
                    const float2* __restrict__ grid, const float4* __restrict__ wg, const float4* __restrict__ bias, int G,
                    int groups_per_img, int n_groups) {
@@ -251,7 +252,7 @@ static unsigned grid_for(int64_t items, int threads, int per_sm) {
 struct StagedPlan { int G; size_t smem; };
 static StagedPlan staged_plan(int Hi, int Wi, int Ho, int C4) {
     StagedPlan p{0, 0};
-    if (Ho <= Hi || 256 % C4 != 0) return p;
+    if (Ho <= Hi || (LS_THREADS / 2) % C4 != 0) return p;
     const size_t row_bytes = (size_t)Wi * C4 * sizeof(float4);
     for (int G = 4; G >= 2; G -= 2) {
         int ns = 0;
@@ -275,7 +276,9 @@ static int launch_staged(const StagedPlan& p, const float4* x, float4* y, int B,
     const int gpi = ceil_div(Ho, p.G);
     const int64_t n_groups = (int64_t)B * gpi;
     const int per_sm = (int)(200 * 1024 / (p.smem + 1024));
-    lerp_staged_kernel<MODE><<<grid_for(n_groups, 1, per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm)), 256, p.smem, st>>>(
+    // few resident blocks (long rows): larger blocks keep enough threads per SM (measured: 512 better above 48 KB, worse below)
+    const int threads = (p.smem > 48 * 1024 && LS_THREADS % (2 * C4) == 0) ? LS_THREADS : LS_THREADS / 2;
+    lerp_staged_kernel<MODE><<<grid_for(n_groups, 1, per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm)), threads, p.smem, st>>>(
         x, y, Hi, Wi, Ho, Wo, C4, act, grid, wg, bias, p.G, gpi, (int)n_groups);
     return launch_status();
 }
