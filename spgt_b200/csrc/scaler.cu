@@ -58,12 +58,18 @@ bilinear_kernel(const float4* __restrict__ x, float4* __restrict__ y, int Hi, in
 // A block handles C0_PIX consecutive output pixels: the 4x4 input patch around each pixel's taps (zero padded
 // outside the image) and the four lerp weights are staged once in shared memory, then thread c evaluates the
 // convolution of channel c at the taps whose weight is non-zero (for exact 2:1 down-scaling that is one tap).
+// The activation is a template parameter (the kernel is bound by its instruction count: a run-time switch per element
+// costs a fifth of it), and the per-pixel index arithmetic (two divisions, two taps) is done once per pixel, not once
+// per patch element.
 constexpr int C0_PIX = 32;
+template <int ACT>
 __global__ void __launch_bounds__(128)
 conv0_down_kernel(const float* __restrict__ node, const float4* __restrict__ w, const float4* __restrict__ bias,
-                  float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int CQ, int act, int npix) {
+                  float4* __restrict__ y, int Hi, int Wi, int Ho, int Wo, int CQ, int npix) {
+    constexpr int act = ACT;
     __shared__ __align__(16) float patch[C0_PIX][16];
     __shared__ __align__(16) float wt[C0_PIX][4];
+    __shared__ int pix_row0[C0_PIX], pix_y0[C0_PIX], pix_x0[C0_PIX];    // b * Hi, first tap row - 1, first tap column - 1
     const bool fixed_cq = (128 % CQ) == 0;            // every item of a thread has the same channel quad: keep its weights in registers
     float4 wk[9], bc;
     if (fixed_cq) {
@@ -74,22 +80,26 @@ conv0_down_kernel(const float* __restrict__ node, const float4* __restrict__ w, 
     }
     for (int p0 = blockIdx.x * C0_PIX; p0 < npix; p0 += gridDim.x * C0_PIX) {
         __syncthreads();                              // the previous group's patch has been consumed
-        for (int i = threadIdx.x; i < C0_PIX * 16; i += blockDim.x) {
-            const int pi = i >> 4, e = i & 15;
-            const int p = p0 + pi;
-            float v = 0.0f;
+        if (threadIdx.x < C0_PIX) {
+            const int pi = threadIdx.x, p = p0 + pi;
             if (p < npix) {
                 const int t2 = p / Wo, xo = p - t2 * Wo;
                 const int b = t2 / Ho, yo = t2 - b * Ho;
                 const Tap ty = make_tap(yo, Hi, Ho), tx = make_tap(xo, Wi, Wo);
-                const int yy = ty.i0 - 1 + (e >> 2), xx = tx.i0 - 1 + (e & 3);
-                if (yy >= 0 && yy < Hi && xx >= 0 && xx < Wi) v = __ldg(node + ((int64_t)b * Hi + yy) * Wi + xx);
-                if (e < 4) {
-                    // a clamped second tap (i1 == i0) reads the same pixel: fold its weight into the first tap
-                    const float wy0 = ty.i1 == ty.i0 ? ty.w0 + ty.w1 : ty.w0, wy1 = ty.i1 == ty.i0 ? 0.0f : ty.w1;
-                    const float wx0 = tx.i1 == tx.i0 ? tx.w0 + tx.w1 : tx.w0, wx1 = tx.i1 == tx.i0 ? 0.0f : tx.w1;
-                    wt[pi][e] = ((e >> 1) ? wy1 : wy0) * ((e & 1) ? wx1 : wx0);
-                }
+                pix_row0[pi] = b * Hi; pix_y0[pi] = ty.i0 - 1; pix_x0[pi] = tx.i0 - 1;
+                // a clamped second tap (i1 == i0) reads the same pixel: fold its weight into the first tap
+                const float wy0 = ty.i1 == ty.i0 ? ty.w0 + ty.w1 : ty.w0, wy1 = ty.i1 == ty.i0 ? 0.0f : ty.w1;
+                const float wx0 = tx.i1 == tx.i0 ? tx.w0 + tx.w1 : tx.w0, wx1 = tx.i1 == tx.i0 ? 0.0f : tx.w1;
+                *reinterpret_cast<float4*>(&wt[pi][0]) = make_float4(wy0 * wx0, wy0 * wx1, wy1 * wx0, wy1 * wx1);
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < C0_PIX * 16; i += blockDim.x) {
+            const int pi = i >> 4, e = i & 15;
+            float v = 0.0f;
+            if (p0 + pi < npix) {
+                const int yy = pix_y0[pi] + (e >> 2), xx = pix_x0[pi] + (e & 3);
+                if (yy >= 0 && yy < Hi && xx >= 0 && xx < Wi) v = __ldg(node + ((int64_t)pix_row0[pi] + yy) * Wi + xx);
             }
             patch[pi][e] = v;
         }
@@ -360,9 +370,17 @@ extern "C" int spgt_conv0_down_fwd(const float* node, const float* w, const floa
     const int64_t npix = (int64_t)B * Ho * Wo;
     if (npix > 0x7fffffffLL - 64 * 1024 * 1024) return SPGT_ERR_SHAPE;
     if (!aligned16(w) || !aligned16(bias) || !aligned16(y)) return SPGT_ERR_ALIGN;
-    conv0_down_kernel<<<grid_for(ceil_div(npix, (int64_t)C0_PIX), 1, 16), 128, 0, (cudaStream_t)stream>>>(
-        node, reinterpret_cast<const float4*>(w), reinterpret_cast<const float4*>(bias), reinterpret_cast<float4*>(y), Hi, Wi, Ho,
-        Wo, Cout / 4, act, (int)npix);
+    const unsigned grid = grid_for(ceil_div(npix, (int64_t)C0_PIX), 1, 16);
+    auto launch = [&](auto kern) {
+        kern<<<grid, 128, 0, (cudaStream_t)stream>>>(node, reinterpret_cast<const float4*>(w), reinterpret_cast<const float4*>(bias),
+                                                     reinterpret_cast<float4*>(y), Hi, Wi, Ho, Wo, Cout / 4, (int)npix);
+    };
+    switch (act) {
+        case SPGT_ACT_RELU: launch(conv0_down_kernel<SPGT_ACT_RELU>); break;
+        case SPGT_ACT_SILU: launch(conv0_down_kernel<SPGT_ACT_SILU>); break;
+        case SPGT_ACT_SILU2: launch(conv0_down_kernel<SPGT_ACT_SILU2>); break;
+        default: launch(conv0_down_kernel<SPGT_ACT_NONE>); break;
+    }
     return launch_status();
 }
 

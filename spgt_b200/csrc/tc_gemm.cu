@@ -533,19 +533,20 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                         float v[16];
                         if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + cc, BN, v); else tc_ld16(taddr + c0 + cc, v);
                         if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 16 + cc / 16);
-                        const int colb = nt * BN + c0 + cc;
+                        // one branch on the activation per 16 columns, not per element (padding columns beyond N carry a
+                        // zero bias and are never stored)
+                        auto finish = [&](auto actf) {
 #pragma unroll
-                        for (int j4 = 0; j4 < 4; ++j4) {
-                            const int col = colb + 4 * j4;
-                            float4 o = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
-                            if (col < e.N) {
+                            for (int j4 = 0; j4 < 4; ++j4) {
                                 const float4 b = *reinterpret_cast<const float4*>(consts + c0 + cc + 4 * j4);
-                                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
-                                o.x = apply_act(o.x, e.act); o.y = apply_act(o.y, e.act);
-                                o.z = apply_act(o.z, e.act); o.w = apply_act(o.w, e.act);
+                                *reinterpret_cast<float4*>(slot_ptr + cc + 4 * j4) =
+                                    make_float4(actf(v[4 * j4] + b.x), actf(v[4 * j4 + 1] + b.y), actf(v[4 * j4 + 2] + b.z), actf(v[4 * j4 + 3] + b.w));
                             }
-                            *reinterpret_cast<float4*>(slot_ptr + cc + 4 * j4) = o;
-                        }
+                        };
+                        if (e.act == SPGT_ACT_SILU2) finish([](float t) { return silu_f(silu_f(t)); });
+                        else if (e.act == SPGT_ACT_RELU) finish([](float t) { return fmaxf(t, 0.0f); });
+                        else if (e.act == SPGT_ACT_SILU) finish([](float t) { return silu_f(t); });
+                        else finish([](float t) { return t; });
                         if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 20 + cc / 16);
                     }
                     __syncwarp();
