@@ -209,6 +209,27 @@ def test_bilinear_matches_aten(dev, Hi, Ho):
     assert rel_l2(y, ref.permute(0, 2, 3, 1)) < 2e-6
 
 
+@pytest.mark.parametrize('Hi,Wi,Ho,Wo,C', [(7, 9, 29, 31, 8), (1, 1, 5, 5, 4), (2, 3, 7, 4, 12), (5, 300, 9, 301, 128), (53, 53, 106, 106, 128),
+                                           (13, 11, 14, 33, 32), (106, 106, 211, 211, 32)])
+def test_upsampling_staged_and_gather_paths_agree_with_aten(dev, Hi, Wi, Ho, Wo, C):
+    """Up-sampling shapes take the kernel that stages source rows in shared memory when the rows fit and the channel
+    count divides the block, the gather kernel otherwise; both must reproduce ATen's align_corners interpolation."""
+    from spgt_b200 import ops
+    g = torch.Generator().manual_seed(Hi * 31 + Wo)
+    x = torch.randn(2, Hi, Wi, C, generator=g)
+    y = ops.bilinear(x.to(dev), Ho, Wo, None)
+    # ATen's own fp32 source coordinates are part of the contract (a float64 interpolation differs by 1e-5 at long rows)
+    ref = torch.nn.functional.interpolate(x.permute(0, 3, 1, 2), size=(Ho, Wo), mode='bilinear', align_corners=True)
+    assert rel_l2(y, ref.permute(0, 2, 3, 1)) < 2e-6
+    assert torch.equal(y, ops.bilinear(x.to(dev), Ho, Wo, None))
+    if C == 32:
+        grid = torch.rand(2, Ho, Wo, 2, generator=g)
+        wg, bb = torch.randn(2, C, generator=g), torch.randn(C, generator=g)
+        out = ops.upsample_grid(x.to(dev), grid.to(dev), wg.to(dev), bb.to(dev), Ho, Wo)
+        ref2 = ref.permute(0, 2, 3, 1) + grid.double() @ wg.double() + bb.double()
+        assert rel_l2(out, ref2) < 2e-6
+
+
 def test_conv0_down_and_upsample_grid(dev):
     from spgt_b200 import ops
     g = torch.Generator().manual_seed(3)
