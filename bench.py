@@ -252,6 +252,21 @@ def micro_cases(device):
         x, w1, b1, w2 = rnd(B, r, r, 32), ops.TcWeight(rnd(32, 128) / 6), rnd(128), rnd(128)
         return (lambda: ops.decoder_head_tc(x, w1, b1, w2, 0.1, 1.0, 0.0, True, 'silu')), B * r * r * 33 * 4, 2 * B * r * r * 32 * 128
     cases['head_tc'] = head_tc
+
+    def darcy_cg(B=16, K=421, iters=200):
+        # `iters` conjugate-gradient iterations of the batched finite-volume Darcy solve (data generator), float64:
+        # per iteration and node 13 array accesses of 8 bytes (step A: z, p, a in, p, q out; step B: a, p, q, x, r in, x, r, z out)
+        a = torch.where(torch.randn(B, K, K, device=device) >= 0, 12.0, 3.0).double()
+        f = torch.ones(B, K, K, device=device, dtype=torch.float64)
+        p = torch.empty_like(a)
+        ws = torch.empty(int(ops.lib.spgt_darcy_fv_workspace_bytes(B, K)), dtype=torch.uint8, device=device)
+
+        def fn():
+            code = ops.lib.spgt_darcy_fv_solve(a.data_ptr(), f.data_ptr(), p.data_ptr(), B, K, iters, 1e-300, iters, ws.data_ptr(),
+                                               ws.numel(), None, None, torch.cuda.current_stream().cuda_stream)
+            assert code == -7, code                     # stops at the iteration limit by construction
+        return fn, 13 * 8 * B * K * K * iters, 20 * B * K * K * iters
+    cases['darcy_cg'] = darcy_cg
     return cases
 
 

@@ -18,6 +18,7 @@
 namespace spgt {
 
 constexpr int DS_THREADS = 256;
+constexpr int DS_NPT = 4;             // nodes per thread: amortises the per-block reduction of the previous step's partial sums
 
 struct DsDims { int K, n, nblk; int64_t grid; };     // n = K - 2 interior nodes per side, nblk blocks per sample
 
@@ -57,16 +58,19 @@ ds_init_kernel(const double* __restrict__ coef, const double* __restrict__ f, do
     __shared__ double red[9];
     const int b = blockIdx.y;
     const int64_t base = (int64_t)b * d.grid;
-    const int idx = blockIdx.x * DS_THREADS + threadIdx.x;
     double rz = 0.0, rr = 0.0;
-    if (idx < d.n * d.n) {
-        const int i = idx / d.n + 1, j = idx - (i - 1) * d.n + 1;
-        const int64_t o = base + (int64_t)i * d.K + j;
-        const double scale = (double)(d.K - 1) * (double)(d.K - 1);
-        const double c = coef[o];
-        const double rv = f[o], zv = rv / (ds_diag(coef + o, d.K, c) * scale);
-        x[o] = 0.0; r[o] = rv; z[o] = zv;
-        rz = rv * zv; rr = rv * rv;
+#pragma unroll
+    for (int k = 0; k < DS_NPT; ++k) {
+        const int idx = (blockIdx.x * DS_NPT + k) * DS_THREADS + threadIdx.x;
+        if (idx < d.n * d.n) {
+            const int i = idx / d.n + 1, j = idx - (i - 1) * d.n + 1;
+            const int64_t o = base + (int64_t)i * d.K + j;
+            const double scale = (double)(d.K - 1) * (double)(d.K - 1);
+            const double c = coef[o];
+            const double rv = f[o], zv = rv / (ds_diag(coef + o, d.K, c) * scale);
+            x[o] = 0.0; r[o] = rv; z[o] = zv;
+            rz += rv * zv; rr += rv * rv;
+        }
     }
     const double s1 = ds_block_sum(rz, red);
     const double s2 = ds_block_sum(rr, red);
@@ -84,24 +88,27 @@ ds_step_a_kernel(const double* __restrict__ coef, const double* __restrict__ z, 
     if (iter > 0) { const double prev = rz_hist[2 * b + ((iter - 1) & 1)]; beta = prev != 0.0 ? rz / prev : 0.0; }
     if (blockIdx.x == 0 && threadIdx.x == 0) rz_hist[2 * b + (iter & 1)] = rz;
     const int64_t base = (int64_t)b * d.grid;
-    const int idx = blockIdx.x * DS_THREADS + threadIdx.x;
     double pq = 0.0;
-    if (idx < d.n * d.n) {
-        const int i = idx / d.n + 1, j = idx - (i - 1) * d.n + 1;
-        const int64_t o = base + (int64_t)i * d.K + j;
-        const int K = d.K;
-        const double scale = (double)(K - 1) * (double)(K - 1);
-        // the new search direction at this node and at its four neighbours (border nodes: z = p = 0)
-        const double pc = z[o] + beta * p_old[o];
-        const double pn = z[o - K] + beta * p_old[o - K], ps = z[o + K] + beta * p_old[o + K];
-        const double pw = z[o - 1] + beta * p_old[o - 1], pe = z[o + 1] + beta * p_old[o + 1];
-        const double c = coef[o];
-        const double wn = (coef[o - K] + c) * 0.5, ws = (coef[o + K] + c) * 0.5;
-        const double ww = (coef[o - 1] + c) * 0.5, we = (coef[o + 1] + c) * 0.5;
-        const double qv = (wn * (pc - pn) + ws * (pc - ps) + ww * (pc - pw) + we * (pc - pe)) * scale;
-        p_new[o] = pc;
-        q[o] = qv;
-        pq = pc * qv;
+#pragma unroll
+    for (int k = 0; k < DS_NPT; ++k) {
+        const int idx = (blockIdx.x * DS_NPT + k) * DS_THREADS + threadIdx.x;
+        if (idx < d.n * d.n) {
+            const int i = idx / d.n + 1, j = idx - (i - 1) * d.n + 1;
+            const int64_t o = base + (int64_t)i * d.K + j;
+            const int K = d.K;
+            const double scale = (double)(K - 1) * (double)(K - 1);
+            // the new search direction at this node and at its four neighbours (border nodes: z = p = 0)
+            const double pc = z[o] + beta * p_old[o];
+            const double pn = z[o - K] + beta * p_old[o - K], ps = z[o + K] + beta * p_old[o + K];
+            const double pw = z[o - 1] + beta * p_old[o - 1], pe = z[o + 1] + beta * p_old[o + 1];
+            const double c = coef[o];
+            const double wn = (coef[o - K] + c) * 0.5, ws = (coef[o + K] + c) * 0.5;
+            const double ww = (coef[o - 1] + c) * 0.5, we = (coef[o + 1] + c) * 0.5;
+            const double qv = (wn * (pc - pn) + ws * (pc - ps) + ww * (pc - pw) + we * (pc - pe)) * scale;
+            p_new[o] = pc;
+            q[o] = qv;
+            pq += pc * qv;
+        }
     }
     const double s = ds_block_sum(pq, red);
     if (threadIdx.x == 0) part_pq[(int64_t)b * d.nblk + blockIdx.x] = s;
@@ -117,17 +124,20 @@ ds_step_b_kernel(const double* __restrict__ coef, const double* __restrict__ p, 
     const double pq = ds_sample_sum(part_pq + (int64_t)b * d.nblk, d.nblk, red);
     const double alpha = pq != 0.0 ? rz_hist[2 * b + (iter & 1)] / pq : 0.0;
     const int64_t base = (int64_t)b * d.grid;
-    const int idx = blockIdx.x * DS_THREADS + threadIdx.x;
     double rz = 0.0, rr = 0.0;
-    if (idx < d.n * d.n) {
-        const int i = idx / d.n + 1, j = idx - (i - 1) * d.n + 1;
-        const int64_t o = base + (int64_t)i * d.K + j;
-        const double scale = (double)(d.K - 1) * (double)(d.K - 1);
-        x[o] += alpha * p[o];
-        const double rv = r[o] - alpha * q[o];
-        const double zv = rv / (ds_diag(coef + o, d.K, coef[o]) * scale);
-        r[o] = rv; z[o] = zv;
-        rz = rv * zv; rr = rv * rv;
+#pragma unroll
+    for (int k = 0; k < DS_NPT; ++k) {
+        const int idx = (blockIdx.x * DS_NPT + k) * DS_THREADS + threadIdx.x;
+        if (idx < d.n * d.n) {
+            const int i = idx / d.n + 1, j = idx - (i - 1) * d.n + 1;
+            const int64_t o = base + (int64_t)i * d.K + j;
+            const double scale = (double)(d.K - 1) * (double)(d.K - 1);
+            x[o] += alpha * p[o];
+            const double rv = r[o] - alpha * q[o];
+            const double zv = rv / (ds_diag(coef + o, d.K, coef[o]) * scale);
+            r[o] = rv; z[o] = zv;
+            rz += rv * zv; rr += rv * rv;
+        }
     }
     const double s1 = ds_block_sum(rz, red);
     const double s2 = ds_block_sum(rr, red);
@@ -135,7 +145,7 @@ ds_step_b_kernel(const double* __restrict__ coef, const double* __restrict__ p, 
 }
 
 static DsDims ds_dims(int K) {
-    DsDims d; d.K = K; d.n = K - 2; d.nblk = ceil_div(d.n * d.n, DS_THREADS); d.grid = (int64_t)K * K; return d;
+    DsDims d; d.K = K; d.n = K - 2; d.nblk = ceil_div(d.n * d.n, DS_THREADS * DS_NPT); d.grid = (int64_t)K * K; return d;
 }
 static size_t ds_align(size_t v) { return (v + 255) / 256 * 256; }
 
