@@ -41,10 +41,7 @@ int spgt_last_cuda_error(void);
 /* Library ABI version (bumped when a signature changes). */
 int spgt_abi_version(void);
 /* Experiment knobs: "attn_cluster" = 0 (heuristic), 1, 2, 4 or 8 CTAs per (batch, head) in spgt_galerkin_attn_fwd;
- * "attn_impl" = 0 (tcgen05 kernel, default) or 1 (warp-MMA kernel);
- * "tc_pair" = 0 (default), 1 or 2: run the 128-column tcgen05 GEMM tiles as 2-CTA clusters (cta_group::2 MMAs over 256
- * rows, half of W in each CTA's shared memory) with one or two row tiles per CTA.  It also changes the column tile that
- * spgt_tc_weight_prepare lays W out for, so set it before preparing the weights that are used with it. */
+ * "attn_impl" = 0 (tcgen05 kernel, default) or 1 (warp-MMA kernel). */
 int spgt_set_tuning(const char* key, int value);
 
 /* ---------------------------------------------------------------------------------------------
@@ -241,9 +238,18 @@ int spgt_decoder_head_fwd(const float* x, const float* w1, const float* b1, cons
 /* Bytes of a prepared weight for a [K,N] matrix, and the preparation itself (w_kn row-major, pitch ldw). */
 size_t spgt_tc_weight_bytes(int K, int N);
 int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, void* out, size_t out_bytes, spgt_stream_t stream);
-/* 0 if no tensor-core kernel ever gave up on a bounded wait, else the code of the first one that did
- * (GEMM: 1..8; attention: 101..108).  Synchronises the device. */
+/* 0 if no tensor-core kernel gave up on a bounded wait since the last reset, else the code of the first one that did
+ * (GEMM: 1..9; fused feed-forward: 21..34; attention: 101..109; spectral layer: 201..219).  Every wait inside these
+ * kernels is bounded by two seconds of wall time; a kernel whose wait expires stops waiting, records the code and
+ * returns with an incomplete output, so a host loop should read this at its synchronisation points and discard the
+ * results when it is not 0.  Synchronises the device.  No counterpart in the reference (its kernels have no waits). */
 int spgt_tc_status(void);
+/* Clears the latched code (after the caller has dealt with it).  Synchronises the device. */
+int spgt_tc_status_reset(void);
+/* Self-test of the bounded wait: launches one warp that waits, for at most limit_us microseconds (1..100000), on a
+ * barrier nothing arrives at.  The wait gives up, latches `code` (> 0) as spgt_tc_status() reports it and the kernel
+ * returns; *returned_dev (device int) is set to 2 when the wait expired, 1 if it was satisfied.  Test infrastructure. */
+int spgt_tc_selftest_wait_expiry(int code, int limit_us, int* returned_dev, spgt_stream_t stream);
 
 /* As spgt_linear_fwd with wprep = spgt_tc_weight_prepare(w, ...). */
 int spgt_linear_tc_fwd(const float* x, int lda, const void* wprep, const float* bias, const float* residual, int ldr,

@@ -10,7 +10,7 @@ benchmark's CPU-baseline leg may import it.  The product package never does.
 
 Parity status: the reference ships no golden vectors or known-answer tests for
 this path, so the oracle is pinned against outputs of the reference's own CPU
-modules generated in the build container (tests/golden/make_golden.py writes
+modules, generated where a checkout of the reference is at hand (tests/golden/make_golden.py writes
 them to tests/golden/*.npz; tests/test_oracle_golden.py replays them).
 
 Conventions that differ between the reference's GT modules and its SpGT ops,

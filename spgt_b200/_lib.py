@@ -57,6 +57,8 @@ SIGNATURES = {
     'spgt_tc_weight_bytes': (_sz, [_i, _i]),
     'spgt_tc_weight_prepare': (_i, [_f, _i, _i, _i, _f, _sz, _st]),
     'spgt_tc_status': (_i, []),
+    'spgt_tc_status_reset': (_i, []),
+    'spgt_tc_selftest_wait_expiry': (_i, [_i, _i, _f, _st]),
     'spgt_linear_tc_fwd': (_i, [_f, _i, _f, _f, _f, _i, _f, _i, _i, _i, _i, _i, _st]),
     'spgt_conv3x3_tc_fwd': (_i, [_f, _i, _i, _i, _f, _f, _f, _i, _i, _i, _i, _i, _i, _i, _st]),
     'spgt_projpos_qkv_tc_fwd': (_i, [_f] * 9 + [_fl] + [_f] * 4 + [_i] * 6 + [_st]),

@@ -47,8 +47,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(src):
         obj = os.path.join(OBJ, src.replace('.cu', '.o'))
-        extra = os.environ.get('SPGT_NVCC_EXTRA', '').split()      # developer switches, e.g. -DSPGT_TC_TRACE
-        cmd = [nvcc, *NVCC_FLAGS, *extra, '-c', os.path.join(CSRC, src), '-o', obj]
+        cmd = [nvcc, *NVCC_FLAGS, '-c', os.path.join(CSRC, src), '-o', obj]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f'nvcc failed on {src}:\n{res.stdout}\n{res.stderr}')

@@ -456,14 +456,13 @@ skinny_reduce_kernel(const float* __restrict__ ws, float* __restrict__ C, float 
     }
 }
 
+static SmemOptIn g_skinny_smem;           // shared-memory opt-in of skinny_splitk_kernel, per device
 static int g_attn_cluster_override = 0;   // 0 = heuristic; set through spgt_set_tuning("attn_cluster", n)
 static int g_attn_impl = 0;               // 0 = tcgen05 kernel (attention_tc.cu, default), 1 = warp-MMA kernel of this file
 
 // defined in attention_tc.cu
 int launch_attn_tc(const float* Q, const float* K, const float* V, float* out, float* t_out, int64_t BH, int H, int dpk,
                    int S, int merged, int cluster, cudaStream_t stream);
-
-void tc_set_pair_mode(int on);            // tc_gemm.cu
 
 }  // namespace spgt
 
@@ -490,13 +489,9 @@ static int pick_cluster(int64_t BH, int S) {
 template <int D>
 static int launch_attn(const float* Q, const float* K, const float* V, float* out, float* t_out, int64_t BH, int H,
                        int S, int merged, cudaStream_t stream) {
-    static bool configured = false;
+    static SmemOptIn configured;
     auto kern = galerkin_attn_kernel<D>;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AttnSmem<D>::BYTES) != cudaSuccess)
-            return launch_status();
-        configured = true;
-    }
+    if (int e = smem_opt_in(kern, AttnSmem<D>::BYTES, configured)) return e;
     const int C = pick_cluster(BH, S);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(BH * C), 1, 1);
@@ -562,13 +557,8 @@ extern "C" int spgt_batched_skinny_gemm(const float* A, const float* B, float* C
     const int splits = skinny_splits(M, N, K, batch);
     const int64_t blocks = (int64_t)tiles * splits * batch;
     if (blocks > 0x7fffffffLL) return SPGT_ERR_SHAPE;
-    static bool configured = false;
     const size_t smem = (size_t)SK_WARPS * SK_WARP_FLOATS * sizeof(float);
-    if (!configured) {
-        if (cudaFuncSetAttribute(skinny_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return launch_status();
-        configured = true;
-    }
+    if (int e = smem_opt_in(skinny_splitk_kernel, smem, g_skinny_smem)) return e;
     cudaStream_t st = (cudaStream_t)stream;
     const int vecB = (N % 4 == 0) ? 1 : 0;
     skinny_splitk_kernel<<<(unsigned)blocks, SK_WARPS * 32, smem, st>>>(A, B, (float*)workspace, M, N, K, tiles_n, tiles,
@@ -649,11 +639,6 @@ extern "C" int spgt_set_tuning(const char* key, int value) {
     if (eq("attn_cluster")) {
         if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return SPGT_ERR_SHAPE;
         g_attn_cluster_override = value;
-        return SPGT_OK;
-    }
-    if (eq("tc_pair")) {
-        if (value < 0 || value > 2) return SPGT_ERR_SHAPE;
-        tc_set_pair_mode(value);
         return SPGT_OK;
     }
     if (eq("attn_impl")) {

@@ -29,18 +29,6 @@ namespace spgt {
 
 __device__ int g_attn_status = 0;
 
-#ifdef SPGT_TC_TRACE
-__device__ int g_attn_dbg = 0;     // experiment mask of the trace build: skip parts of the work (wrong results) to find the bottleneck
-#define AT_DBG(bit) (dbg & (bit))
-__device__ long long g_attn_trace[16 + 10 * 2048];
-__device__ __forceinline__ long long at_gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ int at_smid() { int t; asm volatile("mov.u32 %0, %%smid;" : "=r"(t)); return t; }
-#define AT_TRACE(slot) do { if (blockIdx.x == 0) g_attn_trace[slot] = clock64(); \
-    if (blockIdx.x < 2048) { g_attn_trace[16 + 10 * blockIdx.x + ((slot) & 7)] = at_gtime(); if ((slot) == 0) g_attn_trace[16 + 10 * blockIdx.x + 8] = at_smid(); } } while (0)
-#else
-#define AT_TRACE(slot) do { } while (0)
-#define AT_DBG(bit) false
-#endif
 
 constexpr int AT_THREADS = 320;                 // warps 0-3 loaders, 4-7 converters, 8-9 MMA issuers
 constexpr int AT_NP = 48;                       // N (and B-tile rows) padded to a multiple of 16
@@ -134,10 +122,6 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     const uint32_t tmem_base = *tmem_slot;
     constexpr uint32_t idesc = tc_idesc(AT_NP);
 
-#ifdef SPGT_TC_TRACE
-    const int dbg = g_attn_dbg;
-#endif
-    if (tid == 0) AT_TRACE(0);
     // ============================== phase A: partial T over my columns ==============================
     if (warp < 4) {
         // The chunks a thread copies are the same for every sub-tile: (matrix, row, chunk) of index tid + 128 n.
@@ -166,7 +150,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             const uint32_t dst0 = smem_base + st * AT_RAW_STAGE;
 #pragma unroll
             for (int n = 0; n < NPT; ++n) {
-                if (tid + 128 * n < NCH && !AT_DBG(1)) {
+                if (tid + 128 * n < NCH) {
                     int valid = crem[n] - s0;
                     valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
                     at_cp16(dst0 + cdst[n], valid > 0 ? cbase[n] + s0 : Kb, valid * 4);
@@ -197,7 +181,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             // V: raw rows -> hi / lo B operands (row = j, 32 k-values = grid nodes, 128B swizzle)
 #pragma unroll
             for (int n = 0; n < 3; ++n) {
-                if (vrow[n] < D && !AT_DBG(2)) {
+                if (vrow[n] < D) {
                     const float* p = vraw + vrow[n] * AT_RP + vsh[n] + 4 * (t & 7);
                     uint32_t h[4], l[4];
                     split_tf32_rn(p[0], h[0], l[0]); split_tf32_rn(p[1], h[1], l[1]); split_tf32_rn(p[2], h[2], l[2]); split_tf32_rn(p[3], h[3], l[3]);
@@ -207,7 +191,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 }
             }
             // K: one row per thread into tensor memory (stage `so`, freed together with the V operands)
-            if (k_warp && !AT_DBG(4)) {
+            if (k_warp) {
                 tc_fence_after();
                 const uint32_t a_hi = tmem_base + lane_addr + AT_A1_COL + so * 64;
                 const float* p = kraw + krow_rd * AT_RP + ksh;
@@ -239,7 +223,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 const uint32_t vhi = smem_base + AT_OP_OFF + so * (2 * AT_TILE);
                 const uint64_t dbh = tc_smem_desc(vhi), dbl = tc_smem_desc(vhi + AT_TILE);
 #pragma unroll
-                for (int kk = 0; kk < (AT_DBG(8) ? 0 : 2); ++kk) {
+                for (int kk = 0; kk < 2; ++kk) {
                     const int k8 = 2 * iw + kk;
                     const uint32_t ah = tmem_base + AT_A1_COL + so * 64 + k8 * 8, al = ah + 32;
                     const uint64_t adv = (uint64_t)(k8 * 2);
@@ -254,9 +238,6 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         }
     }
 
-    if (tid == 0) AT_TRACE(1);      // loaders done issuing
-    if (tid == 128) AT_TRACE(2);    // converters done
-    if (tid == 256) AT_TRACE(3);    // MMAs issued
     // ============================== reduce T over the cluster ==============================
     if (warp >= 4 && warp < 8) {
         const int q = warp & 3;
@@ -311,7 +292,6 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     fence_proxy_async();
     __syncthreads();
 
-    if (tid == 0) AT_TRACE(4);
     // ============================== phase B: out = Q^T T over my columns ==============================
     const int col_begin = sub_begin * AT_SUB;
     const int col_end = min(sub_end * AT_SUB, S);
@@ -459,9 +439,6 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             __syncwarp();
         }
     }
-    if (tid == 0) AT_TRACE(5);
-    if (tid == 128) AT_TRACE(6);
-    if (tid == 256) AT_TRACE(7);
     tc_fence_before();
     cluster_sync_all();        // keep Tc alive until every CTA of the cluster has read it; all tensor-memory work is done
     if (warp == 8) {
@@ -473,12 +450,9 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
 template <int D>
 static int launch_attn_tc_d(const float* Q, const float* K, const float* V, float* out, float* t_out, int64_t BH, int H,
                             int S, int merged, int cluster, cudaStream_t stream) {
-    static bool configured = false;
+    static SmemOptIn configured;
     auto kern = galerkin_attn_tc_kernel<D>;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess) return launch_status();
-        configured = true;
-    }
+    if (int e = smem_opt_in(kern, AT_SMEM_BYTES, configured)) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(BH * cluster), 1, 1);
     cfg.blockDim = dim3(AT_THREADS, 1, 1);
@@ -506,12 +480,11 @@ int launch_attn_tc(const float* Q, const float* K, const float* V, float* out, f
     }
 }
 
-#ifdef SPGT_TC_TRACE
-extern "C" int spgt_attn_debug(int mask) { return cudaMemcpyToSymbol(g_attn_dbg, &mask, sizeof(int)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH; }
-extern "C" int spgt_attn_trace_read(long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(long long) * (16 + 10 * 2048)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
+
+int attn_tc_status_reset() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int)) == cudaSuccess ? SPGT_OK : SPGT_ERR_LAUNCH;
 }
-#endif
 
 int attn_tc_status() {
     int v = 0;

@@ -16,14 +16,34 @@ inline int launch_status() {
     return SPGT_OK;
 }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// Kernel attributes and device properties are per device: every cache below is indexed by the current device, so
+// one process may drive several GPUs.
+constexpr int SPGT_MAX_DEVICES = 64;
+inline int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= SPGT_MAX_DEVICES) dev = 0;
+    return dev;
+}
 inline int num_sms() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    static int n[SPGT_MAX_DEVICES] = {};
+    const int dev = current_device();
+    if (n[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n[dev] = v;
     }
-    return n;
+    return n[dev];
+}
+// Opt-in to more than 48 KB of dynamic shared memory, once per (kernel, device); `state` is a static of the call site.
+struct SmemOptIn { size_t bytes[SPGT_MAX_DEVICES] = {}; };
+template <class K> inline int smem_opt_in(K kern, size_t bytes, SmemOptIn& state) {
+    const int dev = current_device();
+    if (bytes > state.bytes[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) { g_last_cuda_error = (int)e; (void)cudaGetLastError(); return SPGT_ERR_LAUNCH; }
+        state.bytes[dev] = bytes;
+    }
+    return SPGT_OK;
 }
 template <typename T> __host__ __device__ constexpr T ceil_div(T a, T b) { return (a + b - 1) / b; }
 

@@ -421,19 +421,11 @@ gemm_head_kernel(DenseLoader<4> ld, const float* __restrict__ W1, int K, int row
 // ------------------------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------------------------
-template <class Kern> static int set_smem(Kern k, size_t bytes, bool& done) {
-    if (!done) {
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) return launch_status();
-        done = true;
-    }
-    return SPGT_OK;
-}
-
 template <int WN, class Loader>
 static int launch_linear(Loader ld, const float* W, int ldw, int N, int K, int rows, const LinearEpi& ep, cudaStream_t st) {
-    static bool done = false;
+    static SmemOptIn done;
     auto kern = gemm_linear_kernel<WN, Loader>;
-    if (int e = set_smem(kern, GemmSmem<WN>::BYTES, done)) return e;
+    if (int e = smem_opt_in(kern, GemmSmem<WN>::BYTES, done)) return e;
     const int n_tiles = ceil_div(N, 16 * WN);
     const int64_t blocks = (int64_t)ceil_div(rows, G_BM) * n_tiles;
     if (blocks > 0x7fffffffLL) return SPGT_ERR_SHAPE;
@@ -495,8 +487,8 @@ static int proj_common(const float* x, int nproj, ProjEpi& ep, int B, int S, int
     const int64_t rows64 = (int64_t)B * S;
     if (rows64 > 0x7fffffffLL / 2) return SPGT_ERR_SHAPE;
     if (d_pos > 0 && !ep.pos) return SPGT_ERR_NULL;
-    static bool done = false;
-    if (int e = set_smem(gemm_proj_kernel, GemmSmem<8>::BYTES, done)) return e;
+    static SmemOptIn done;
+    if (int e = smem_opt_in(gemm_proj_kernel, GemmSmem<8>::BYTES, done)) return e;
     static_assert(GemmSmem<8>::BYTES >= (size_t)128 * (G_BM + 4) * sizeof(float), "staging tile must fit");
     DenseLoader<4> ld;
     ld.x = x; ld.lda = D; ld.rows = (int)rows64; ld.K = D;
@@ -552,8 +544,8 @@ extern "C" int spgt_decoder_head_fwd(const float* x, const float* w1, const floa
     const int64_t rows64 = (int64_t)B * Hh * Ww;
     if (rows64 > 0x7fffffffLL / 2) return SPGT_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(w1)) return SPGT_ERR_ALIGN;
-    static bool done = false;
-    if (int e = set_smem(gemm_head_kernel, GemmSmem<8>::BYTES, done)) return e;
+    static SmemOptIn done;
+    if (int e = smem_opt_in(gemm_head_kernel, GemmSmem<8>::BYTES, done)) return e;
     DenseLoader<4> ld;
     ld.x = x; ld.lda = K; ld.rows = (int)rows64; ld.K = K;
     HeadEpi ep{b1, w2, b2, scale, shift, scale_map, shift_map, dirichlet, Hh, Ww, act, out};

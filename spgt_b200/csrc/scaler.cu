@@ -278,11 +278,8 @@ static StagedPlan staged_plan(int Hi, int Wi, int Ho, int C4) {
 template <int MODE>
 static int launch_staged(const StagedPlan& p, const float4* x, float4* y, int B, int Hi, int Wi, int Ho, int Wo, int C4, int act,
                          const float2* grid, const float4* wg, const float4* bias, cudaStream_t st) {
-    static size_t configured = 0;
-    if (p.smem > configured) {
-        if (cudaFuncSetAttribute(lerp_staged_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess) return launch_status();
-        configured = p.smem;
-    }
+    static SmemOptIn configured;
+    if (int e = smem_opt_in(lerp_staged_kernel<MODE>, p.smem, configured)) return e;
     const int gpi = ceil_div(Ho, p.G);
     const int64_t n_groups = (int64_t)B * gpi;
     const int per_sm = (int)(200 * 1024 / (p.smem + 1024));

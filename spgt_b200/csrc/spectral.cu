@@ -625,21 +625,13 @@ spectral_inv_y_kernel(const float* __restrict__ X, const float* __restrict__ P, 
     }
 }
 
-template <class K> static int set_smem_once(K kern, size_t bytes, size_t& configured) {
-    if (bytes > configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) return launch_status();
-        configured = bytes;
-    }
-    return SPGT_OK;
-}
-
 template <int NT>
 static int launch_fwd_y(const float* x, const float* tab, float* y1, int r, int m, int64_t nrows, cudaStream_t st) {
-    static size_t configured = 0;
+    static SmemOptIn configured;
     const SpecTables T = spec_tables(r, m);
     const size_t smem = ((size_t)T.RY * T.F1P + (size_t)SP_WARPS * 2 * SP_YB * SP_XP1) * sizeof(float);
     if (smem > 200 * 1024) return SPGT_ERR_SHAPE;
-    if (int e = set_smem_once(spectral_fwd_y_kernel<NT>, smem, configured)) return e;
+    if (int e = smem_opt_in(spectral_fwd_y_kernel<NT>, smem, configured)) return e;
     const int64_t want = ceil_div(nrows, (int64_t)SP_WARPS);
     const int64_t cap = (int64_t)num_sms() * (smem <= 74 * 1024 ? 3 : 2);
     spectral_fwd_y_kernel<NT><<<(unsigned)(want < cap ? want : cap), SP_WARPS * 32, smem, st>>>(x, tab, y1, r, m, nrows);
@@ -649,12 +641,12 @@ static int launch_fwd_y(const float* x, const float* tab, float* y1, int r, int 
 template <int KJ>
 static int launch_inv_y(const float* x, const float* p, const float* wr, const float* br, const float* tab, float* out,
                         int r, int m, int act, int64_t nrows, cudaStream_t st) {
-    static size_t configured = 0;
+    static SmemOptIn configured;
     const SpecTables T = spec_tables(r, m);
     const size_t smem = ((size_t)T.RY * T.F3P + SP_C * SP_PP +
                          (size_t)SP_WARPS * (2 * SP_YB * SP_XP3 + 2 * 8 * KJ * SP_PP)) * sizeof(float);
     if (smem > 200 * 1024) return SPGT_ERR_SHAPE;
-    if (int e = set_smem_once(spectral_inv_y_kernel<KJ>, smem, configured)) return e;
+    if (int e = smem_opt_in(spectral_inv_y_kernel<KJ>, smem, configured)) return e;
     const int64_t want = ceil_div(nrows, (int64_t)SP_WARPS);
     const int64_t cap = (int64_t)num_sms() * 2;
     spectral_inv_y_kernel<KJ><<<(unsigned)(want < cap ? want : cap), SP_WARPS * 32, smem, st>>>(x, p, wr, br, tab, out, r,
@@ -719,15 +711,15 @@ extern "C" int spgt_spectral_conv2d_fwd(const float* x, const float* wr, const f
     if (e) return e;
     const size_t gsmem = (size_t)2 * J * r * sizeof(float);
     if (gsmem > 200 * 1024) return SPGT_ERR_SHAPE;
-    static size_t cfg_a = 0, cfg_c = 0, cfg_am = 0, cfg_cm = 0;
+    static SmemOptIn cfg_a, cfg_c, cfg_am, cfg_cm;
     const bool staged = r <= SP_XMAX;                       // tensor-core S2a / S2c with everything staged in shared memory
     if (staged) {
         const int MT = ceil_div(2 * (int)J, 16), r8 = ceil_div(r, 8) * 8;
         const size_t smem_a = ((size_t)16 * MT * sp_round_pitch(r8, 4) + (size_t)(r8 > 16 * MT ? r8 : 16 * MT) * SP_YP) * sizeof(float);
-        if ((e = set_smem_once(spectral_fwd_x_mma_kernel, smem_a, cfg_am))) return e;
+        if ((e = smem_opt_in(spectral_fwd_x_mma_kernel, smem_a, cfg_am))) return e;
         spectral_fwd_x_mma_kernel<<<dim3(m, B), 128, smem_a, st>>>(Y1, tab, Zr, Zi, r, m);
     } else {
-        if ((e = set_smem_once(spectral_fwd_x_kernel, gsmem, cfg_a))) return e;
+        if ((e = smem_opt_in(spectral_fwd_x_kernel, gsmem, cfg_a))) return e;
         spectral_fwd_x_kernel<<<dim3(m, B), 256, gsmem, st>>>(Y1, tab, Zr, Zi, r, m);
     }
     if ((e = launch_status())) return e;
@@ -736,10 +728,10 @@ extern "C" int spgt_spectral_conv2d_fwd(const float* x, const float* wr, const f
     if (staged) {
         const int K8 = ceil_div(2 * (int)J, 8) * 8, r16 = ceil_div(r, 16) * 16;
         const size_t smem_c = ((size_t)K8 * sp_round_pitch(r16, 8) + (size_t)K8 * SP_YP) * sizeof(float);
-        if ((e = set_smem_once(spectral_inv_x_mma_kernel, smem_c, cfg_cm))) return e;
+        if ((e = smem_opt_in(spectral_inv_x_mma_kernel, smem_c, cfg_cm))) return e;
         spectral_inv_x_mma_kernel<<<dim3(m, B), 128, smem_c, st>>>(Or, Oi, tab, P, r, m);
     } else {
-        if ((e = set_smem_once(spectral_inv_x_kernel, gsmem, cfg_c))) return e;
+        if ((e = smem_opt_in(spectral_inv_x_kernel, gsmem, cfg_c))) return e;
         spectral_inv_x_kernel<<<dim3(m, B), 256, gsmem, st>>>(Or, Oi, tab, P, r, m);
     }
     if ((e = launch_status())) return e;

@@ -5,7 +5,7 @@
 namespace spgt {
 
 constexpr int TC_BM = 128, TC_BK = 32;
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 19;   // about two seconds of polling before a wait gives up
+constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds of wall time
 
 // ---- mbarrier / tcgen05 primitives -------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -32,15 +32,25 @@ __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
-// Bounded wait.  Returns false (and latches *abort_flag) when the limit is reached or another thread gave up.
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false (and latches *abort_flag) when `limit_ns` of wall time have passed or another thread
+// of the CTA gave up; the first code that expires is also latched in *status (device global, read by the host).
 // The non-blocking test comes first: in steady state most waits find their phase already complete, and a successful
 // test_wait costs the waiting thread ~120 cycles against ~300 for a successful try_wait (measured on B200), which
-// matters for the single thread that issues the MMAs.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status = nullptr) {
+// matters for the single thread that issues the MMAs.  Each try_wait may sleep up to its 100 us hint, so the clock
+// is read after every unsuccessful one.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status = nullptr,
+                                          unsigned long long limit_ns = TC_WAIT_LIMIT_NS) {
     if (mbar_test_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > limit_ns) break;
     }
     *abort_flag = code;
     if (status != nullptr) atomicCAS(status, 0, code);
@@ -79,34 +89,6 @@ __device__ __forceinline__ void tc_mma_tf32_ts_p(uint32_t d_tmem, uint32_t a_tme
         "mov.b64 bd, {%2, %3};\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], bd, %4, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate) : "memory");
-}
-// ---- CTA pairs (cta_group::2): one MMA covers 256 rows, 128 in the tensor memory of each CTA of a 2-CTA cluster, and
-// reads half of the B rows from the shared memory of each CTA.  Issued by one thread of the cluster's rank-0 CTA.
-__device__ __forceinline__ void tc2_mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t b_desc_hi, uint32_t idesc,
-                                                uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "mov.b64 bd, {%2, %3};\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], [%1], bd, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// arrive on the barrier at the same shared-memory offset in both CTAs of the pair once the issued MMAs have completed
-__device__ __forceinline__ void tc2_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(bar), "h"((uint16_t)3) : "memory");
-}
-// address of this CTA's shared-memory location `local` as seen in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
-    return remote;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-__host__ __device__ constexpr uint32_t tc2_idesc(int bn) {      // M = 256
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t* u = reinterpret_cast<uint32_t*>(v);

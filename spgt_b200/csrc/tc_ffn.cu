@@ -331,6 +331,11 @@ tc_ffn_kernel(const float* __restrict__ x, int lda, const float* __restrict__ w1
     }
 }
 
+int ffn_tc_status_reset() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_ffn_status, &zero, sizeof(int)) == cudaSuccess ? SPGT_OK : SPGT_ERR_LAUNCH;
+}
+
 int ffn_tc_status() {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_ffn_status, sizeof(int)) != cudaSuccess) return SPGT_ERR_LAUNCH;
@@ -350,11 +355,8 @@ extern "C" int spgt_ffn_tc_fwd(const float* x, int lda, const void* w1prep, cons
     if (!aligned16(x) || !aligned16(w1prep) || !aligned16(w2prep) || !aligned16(y) || (residual && !aligned16(residual)) ||
         !aligned16(b1) || (b2 && !aligned16(b2)))
         return SPGT_ERR_ALIGN;
-    static bool done = false;
-    if (!done) {
-        if (cudaFuncSetAttribute(tc_ffn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FF_SMEM) != cudaSuccess) return launch_status();
-        done = true;
-    }
+    static SmemOptIn configured;
+    if (int e = smem_opt_in(tc_ffn_kernel, FF_SMEM, configured)) return e;
     const int n_tiles = ceil_div(rows, TC_BM);
     const int grid = n_tiles < num_sms() ? n_tiles : num_sms();
     tc_ffn_kernel<<<grid, FF_THREADS, FF_SMEM, (cudaStream_t)stream>>>(x, lda, (const float*)w1prep, b1, (const float*)w2prep, b2,

@@ -22,7 +22,6 @@
 //     ahead, while the accumulator is still being computed.
 //   * Column tiles of up to 64 use two MMAs per k-step instead of three: A_hi * [W_hi | W_lo] as one instruction of
 //     twice the width into two partial accumulators, A_lo * W_hi into the first.
-//   * PAIR = 1 (experiment, off by default): 2-CTA clusters and cta_group::2 MMAs over 256 rows.
 //   warps 0-3 A loaders, 4-7 A splitters, 8 W loader, 9 (MT = 2: 9-10) MMA issuers (lane 0 runs the whole issue loop),
 //   then 8 epilogue warps.
 // All waits are bounded mbarrier polls: on expiry the kernel records an error code, stops waiting and returns.
@@ -39,18 +38,6 @@ constexpr int TC_SLOT_BYTES = 144;            // per-epilogue-thread staging row
 
 __device__ int g_tc_status = 0;          // 0 = ok; otherwise the code of the first wait that gave up
 
-#ifdef SPGT_TC_TRACE                      // developer build only: per-unit timestamps of CTA 0 (see spgt_tc_trace_read)
-__device__ long long g_tc_trace[64 * 32 + 32 * 8];   // per-unit time stamps of CTA 0, then 8 cycle counters per warp
-#define TC_TRACE(unit_i, slot) do { if (blockIdx.x == 0 && (unit_i) < 64) g_tc_trace[(unit_i) * 32 + (slot)] = clock64(); } while (0)
-#define TC_TADD(unit_i, slot, ...) do { const long long t_ = clock64(); __VA_ARGS__; tc_acc[(slot) & 7] += clock64() - t_; } while (0)
-#define TC_ACC_DECL long long tc_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long tc_t0 = clock64();
-#define TC_ACC_FLUSH do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { for (int k_ = 0; k_ < 7; ++k_) g_tc_trace[64 * 32 + (threadIdx.x >> 5) * 8 + k_] = tc_acc[k_]; g_tc_trace[64 * 32 + (threadIdx.x >> 5) * 8 + 7] = clock64() - tc_t0; } } while (0)
-#else
-#define TC_TADD(unit_i, slot, ...) do { __VA_ARGS__; } while (0)
-#define TC_ACC_DECL
-#define TC_ACC_FLUSH do { } while (0)
-#define TC_TRACE(unit_i, slot) do { } while (0)
-#endif
 
 __host__ __device__ constexpr int tc_cols_per_thread(int bn, int mt) { return mt == 1 ? bn / 2 : bn; }
 
@@ -142,18 +129,13 @@ template <int BN, int MT> struct TcCfg {
     static constexpr size_t BYTES = 1024 + (size_t)SB * B_BYTES + SR * RAW_BYTES + STAGING_BYTES + CONST_BYTES + BAR_BYTES;
 };
 
-// PAIR = 1: the kernel runs as 2-CTA clusters.  Each CTA still loads, splits and finishes its own MT row tiles, but an
-// MMA (cta_group::2) covers 256 rows, tile m of both CTAs, and takes half of the W rows from each CTA's shared memory:
-// a CTA holds half of W, so a column tile of twice the K stays resident, and W is read from shared memory half as often
-// per row.  CTA m of the pair issues the MMAs of tile m (with one tile per CTA only CTA 0 issues).
-template <int BN, int MT, class Loader, int EPI, class EpiParams, int PAIR = 0>
+template <int BN, int MT, class Loader, int EPI, class EpiParams>
 __global__ void __launch_bounds__(tc_threads(MT), 1)
 tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_units, EpiParams ep) {
     using C = TcCfg<BN, MT>;
     constexpr int SA = C::SA, NBUF = C::NBUF, SR = C::SR;
-    // W stages: a CTA of a pair holds only half of the W rows of a k-block, so the same memory gives twice the stages
-    constexpr int SB = PAIR ? (2 * C::SB > 8 ? 8 : 2 * C::SB) : C::SB;
-    constexpr uint32_t B_STAGE = PAIR ? C::B_BYTES / 2 : C::B_BYTES;
+    constexpr int SB = C::SB;
+    constexpr uint32_t B_STAGE = C::B_BYTES;
     constexpr int NIWARPS = tc_mma_warps(MT);                       // MMA-issuing warps
     constexpr int TC_THREADS = tc_threads(MT), TC_EPI_WARP0 = tc_epi_warp0(MT);
     extern __shared__ uint8_t smem_raw[];
@@ -173,46 +155,38 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     auto acc_empty = [&](int b) { return bars + 8u * (26 + b); };       // [2]
     auto raw_full = [&](int s) { return bars + 8u * (28 + s); };        // [3]
     auto raw_empty = [&](int s) { return bars + 8u * (31 + s); };       // [3]
-    auto b_half = [&](int s) { return bars + 8u * (38 + s); };          // [8] pair mode: this CTA's half of a W stage has landed
     static_assert(SA <= 4 && SB <= 8 && SR <= 3 && NBUF <= 2, "barrier slots");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 288);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 296);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    TC_ACC_DECL
     const int KB = kpad / TC_BK;
     const bool resident = KB <= SB;          // the whole column tile of W stays in shared memory
 
-    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;            // CTA m of a pair issues the MMAs of row tile m
     if (tid == 0) {
-        for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), PAIR ? 8 : 128); mbar_init(a_empty(s), NIWARPS); }
+        for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), NIWARPS); }
         for (int s = 0; s < SR; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
-        for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), PAIR ? 2 : 1); mbar_init(b_half(s), 1); mbar_init(b_empty(s), NIWARPS); }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), NIWARPS); mbar_init(acc_empty(b), PAIR ? 2 * TC_EPI_WARPS / MT : 32 * TC_EPI_WARPS); }
+        for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), NIWARPS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), NIWARPS); mbar_init(acc_empty(b), 32 * TC_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TC_MMA_WARP) {
-        if constexpr (PAIR) {
-            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-        } else {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-        }
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // Epilogue constants of this CTA's column tile go to shared memory once: a global load issued from the epilogue
     // queues behind the producers' traffic and costs microseconds of latency per use.
     if constexpr (EPI == EPI_HEAD) {
         for (int i = tid; i < 256; i += TC_THREADS) consts[i] = i < 128 ? __ldg(ep.b1 + i) : __ldg(ep.w2 + i - 128);
     } else if constexpr (EPI == EPI_LINEAR) {
-        const int ntc = (PAIR ? blockIdx.x / 2 : blockIdx.x) % n_tiles;
+        const int ntc = blockIdx.x % n_tiles;
         for (int i = tid; i < BN; i += TC_THREADS) {
             const int col = ntc * BN + i;
             consts[i] = (ep.bias != nullptr && col < ep.N) ? __ldg(ep.bias + col) : 0.0f;
         }
     } else {
-        const int p = (PAIR ? blockIdx.x / 2 : blockIdx.x) % n_tiles;
+        const int p = blockIdx.x % n_tiles;
         for (int i = tid; i < 128; i += TC_THREADS) {
             consts[i] = ep.bias[p] ? __ldg(ep.bias[p] + i) : 0.0f;
             consts[128 + i] = ep.lnw[p] ? __ldg(ep.lnw[p] + i) : 1.0f;
@@ -220,21 +194,20 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         }
     }
     tc_fence_before();
-    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();     // the partner's barriers are initialised too
+    __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + C::ACC_COLS;
 
-    // Work distribution: this CTA (pair) keeps one column tile (so a resident W is loaded once) and strides over row
-    // units; in pair mode a unit is 512 rows, two tiles for each CTA of the pair.
-    const int sched_id = PAIR ? blockIdx.x / 2 : blockIdx.x, sched_n = PAIR ? gridDim.x / 2 : gridDim.x;
+    // Work distribution: this CTA keeps one column tile (so a resident W is loaded once) and strides over row units.
+    const int sched_id = blockIdx.x, sched_n = gridDim.x;
     const int ctas_per_nt = sched_n / n_tiles;
     const int nt = sched_id % n_tiles;
     const int u0 = sched_id / n_tiles;
     const int n_my_units = (u0 < m_units) ? (m_units - u0 + ctas_per_nt - 1) / ctas_per_nt : 0;
     const float* wtile = wimg + (int64_t)nt * KB * (C::B_BYTES / 4);
-    // first row tile of unit ui (MT tiles follow each other; in pair mode the two CTAs take one tile each)
-    auto unit_tile0 = [&](int ui) { return (PAIR ? (u0 + ui * ctas_per_nt) * 2 + (int)crank : u0 + ui * ctas_per_nt) * MT; };
+    // first row tile of unit ui (MT tiles follow each other)
+    auto unit_tile0 = [&](int ui) { return (u0 + ui * ctas_per_nt) * MT; };
 
     if (warp < 4) {
         // ------------------------------------------ A loaders ------------------------------------------
@@ -254,7 +227,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 for (int i = 0; i < 8; ++i) rs[m][i] = ld.row_state(row0 + m * TC_BM + 16 * i);
             for (int kb = 0; kb < KB; ++kb, rr.template next<SR>()) {
                 const uint32_t sr = rr.s, ph = rr.ph;
-                bool okw; TC_TADD(ui, 28, okw = mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1, &g_tc_status));
+                bool okw; okw = mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1, &g_tc_status);
                 if (!okw) { alive = false; break; }
                 const typename Loader::Kst ks = ld.k_state(kb, t & 7);
                 const uint32_t dst = raw_s + sr * C::RAW_BYTES;
@@ -285,10 +258,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int64_t slot = 0; slot < total; ++slot, rr.template next<SR>(), ra.template next<SA>()) {
             const uint32_t sr = rr.s, pr = rr.ph;
             const uint32_t sa = ra.s, pa = ra.ph;
-            bool ok1, ok2; const int ui_t = 0;
-            TC_TADD(ui_t, 26, ok1 = mbar_wait(raw_full(sr), pr, abort_flag, 5, &g_tc_status));
+            bool ok1, ok2;
+            ok1 = mbar_wait(raw_full(sr), pr, abort_flag, 5, &g_tc_status);
             if (!ok1) break;
-            TC_TADD(ui_t, 27, ok2 = mbar_wait(a_empty(sa), pa ^ 1, abort_flag, 8, &g_tc_status));
+            ok2 = mbar_wait(a_empty(sa), pa ^ 1, abort_flag, 8, &g_tc_status);
             if (!ok2) break;
             tc_fence_after();
 #pragma unroll
@@ -314,17 +287,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             mbar_arrive(raw_empty(sr));                         // the raw stage has been read
             tc_wait_st();
             tc_fence_before();
-            if constexpr (PAIR) {                 // every issuing CTA (CTA m issues tile m) reads both CTAs' tiles;
-                __syncwarp();                     // one arrival per warp: arrivals that cross to the other SM are slow
-                if (lane == 0) {
-#pragma unroll
-                    for (uint32_t c = 0; c < (uint32_t)MT; ++c) {
-                        if (c == crank) mbar_arrive(a_full(sa)); else mbar_arrive_cluster(cluster_map(a_full(sa), c));
-                    }
-                }
-            } else {
-                mbar_arrive(a_full(sa));
-            }
+            mbar_arrive(a_full(sa));
         }
     } else if (warp == TC_BLOAD_WARP) {
         // ------------------------------------------ W loader ------------------------------------------
@@ -338,31 +301,9 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 if (!mbar_wait(b_empty(sb), ph ^ 1, abort_flag, 6, &g_tc_status)) break;
                 const int kb = kbw;
                 if (++kbw == KB) kbw = 0;
-                if constexpr (PAIR) {
-                    // this CTA's half of the W rows: hi rows at the start of the stage, lo rows a quarter stage later
-                    constexpr uint32_t QB = C::B_BYTES / 4;
-                    const float* src = wtile + (int64_t)kb * (C::B_BYTES / 4) + crank * (QB / 4);
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_half(sb)), "r"(2 * QB) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(smem_base + sb * B_STAGE), "l"(src), "r"(QB), "r"(b_half(sb)) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(smem_base + sb * B_STAGE + QB), "l"(src + C::B_BYTES / 8), "r"(QB), "r"(b_half(sb)) : "memory");
-                } else {
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(sb)), "r"(bytes) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                              ::"r"(smem_base + sb * B_STAGE), "l"(wtile + (int64_t)kb * (C::B_BYTES / 4)), "r"(bytes), "r"(b_full(sb)) : "memory");
-                }
-            }
-        } else if (PAIR && lane == 1 && n_my_units > 0) {
-            // tell the issuing CTAs of the pair when this CTA's half of a W stage has landed
-            const int64_t total = resident ? KB : (int64_t)n_my_units * KB;
-            TcRing rb;
-            for (int64_t slot = 0; slot < total; ++slot, rb.template next<SB>()) {
-                if (!mbar_wait(b_half(rb.s), rb.ph, abort_flag, 9, &g_tc_status)) break;
-#pragma unroll
-                for (uint32_t c = 0; c < (uint32_t)MT; ++c) {
-                    if (c == crank) mbar_arrive(b_full(rb.s)); else mbar_arrive_cluster(cluster_map(b_full(rb.s), c));
-                }
             }
         }
         __syncwarp();
@@ -375,52 +316,37 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         const int iw = warp - TC_MMA_WARP;
         constexpr int NI = BN;                                              // N of one instruction
         {
-        constexpr uint32_t idesc = PAIR ? tc2_idesc(NI) : tc_idesc(NI);
+        constexpr uint32_t idesc = tc_idesc(NI);
         const uint32_t d_off = (MT == 2) ? (uint32_t)(iw * C::ACCW) : (uint32_t)(iw * NI);
         const uint32_t a_off = (MT == 2) ? (uint32_t)(iw * 64) : 0u;
         const uint32_t b_off = (MT == 2) ? 0u : (uint32_t)(iw * NI * 128);   // NI rows of 128 bytes
         // Only lane 0 runs the loop (waits included): no divergence and reconvergence per k-block.  The B descriptors
         // differ between stages only in the address field of their low word, so they are advanced with 32-bit adds.
-        if (PAIR && iw != (int)crank) {
-            // CTA m of a pair issues tile m only
-        } else if (lane == 0) {
+        if (lane == 0) {
             const uint64_t desc0 = tc_smem_desc(smem_base + b_off);
             const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
             TcRing ra, rb;
             bool alive = true;
             for (int ui = 0; ui < n_my_units && alive; ++ui) {
                 const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
-                if (iw == 0) TC_TRACE(ui, 4);
-                bool okc; TC_TADD(ui, 26, okc = mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2, &g_tc_status));
+                bool okc; okc = mbar_wait(acc_empty(buf), aph ^ 1, abort_flag, 2, &g_tc_status);
                 if (!okc) break;
-                if (iw == 0) TC_TRACE(ui, 5);
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * MT * C::ACCW + d_off;
                 for (int kb = 0; kb < KB; ++kb, ra.template next<SA>(), rb.template next<SB>()) {
                     const uint32_t sa = ra.s, pa = ra.ph;
                     const uint32_t sb = resident ? (uint32_t)kb : rb.s;
                     bool oka, okb = true;
-                    TC_TADD(ui, 24 + 5 * iw, oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status));
+                    oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status);
                     if (!oka) { alive = false; break; }
                     if (!resident || ui == 0) {
-                        TC_TADD(ui, 25 + 5 * iw, okb = mbar_wait(b_full(sb), resident ? 0u : rb.ph, abort_flag, 7, &g_tc_status));
+                        okb = mbar_wait(b_full(sb), resident ? 0u : rb.ph, abort_flag, 7, &g_tc_status);
                         if (!okb) { alive = false; break; }
                     }
-                    if (kb == 0 && iw == 0) TC_TRACE(ui, 6);
                     tc_fence_after();
                     const uint32_t bh = desc_lo0 + sb * (B_STAGE >> 4), bl = bh + (B_STAGE >> 5);
                     const uint32_t ah = tmem_a + sa * MT * 64 + a_off, al = ah + 32;
-                    if constexpr (PAIR) {
-                        tc2_mma_tf32_ts(d, al, bh, desc_hi, idesc, kb > 0 ? 1u : 0u);
-                        tc2_mma_tf32_ts(d, ah, bl, desc_hi, idesc, 1u);
-                        tc2_mma_tf32_ts(d, ah, bh, desc_hi, idesc, 1u);
-#pragma unroll
-                        for (int k8 = 1; k8 < TC_BK / 8; ++k8) {
-                            tc2_mma_tf32_ts(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc, 1u);
-                            tc2_mma_tf32_ts(d, ah + k8 * 8, bl + k8 * 2, desc_hi, idesc, 1u);
-                            tc2_mma_tf32_ts(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc, 1u);
-                        }
-                    } else if constexpr (C::MERGE) {
+                    if constexpr (C::MERGE) {
                         constexpr uint32_t idesc2 = tc_idesc(2 * NI);           // [W_hi | W_lo] as one operand of twice the rows
                         tc_mma_tf32_ts_p(d, ah, bh, desc_hi, idesc2, kb > 0 ? 1u : 0u);
                         tc_mma_tf32_ts_acc(d, al, bh, desc_hi, idesc);
@@ -441,16 +367,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     }
                     }
                     // the A stage (and a streamed W stage) is reusable once every issuer's MMAs have read it
-                    if constexpr (PAIR) {
-                        tc2_commit(a_empty(sa));           // arrives in both CTAs of the pair
-                        if (!resident) tc2_commit(b_empty(sb));
-                    } else {
-                        tc_commit(a_empty(sa));
-                        if (!resident) tc_commit(b_empty(sb));
-                    }
+                    tc_commit(a_empty(sa));
+                    if (!resident) tc_commit(b_empty(sb));
                 }
-                if (alive) { if constexpr (PAIR) tc2_commit(acc_full(buf)); else tc_commit(acc_full(buf)); }
-                if (iw == 0) TC_TRACE(ui, 7);
+                if (alive) tc_commit(acc_full(buf));
             }
         }
         __syncwarp();
@@ -490,7 +410,6 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         }
         for (int ui = 0; ui < n_my_units && alive; ++ui) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
-            if (epi_idx == 0) TC_TRACE(ui, 8);
             float posv[8];                     // PROJ: this row's position values, fetched while the accumulator is still being computed
             if constexpr (EPI == EPI_PROJ) {
                 const int prow = (unit_tile0(ui) + mt_e) * TC_BM + r_in_tile;
@@ -510,9 +429,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     head_edge = ep.dirichlet && (y == 0 || x == 0 || y == ep.Hh - 1 || x == ep.Ww - 1);
                 }
             }
-            bool okf; TC_TADD(ui, 24, okf = mbar_wait(acc_full(buf), aph, abort_flag, 4, &g_tc_status));
+            bool okf; okf = mbar_wait(acc_full(buf), aph, abort_flag, 4, &g_tc_status);
             if (!okf) { alive = false; break; }
-            if (epi_idx == 0) TC_TRACE(ui, 9);
             tc_fence_after();
             const int tile = unit_tile0(ui) + mt_e;
             const int row = tile * TC_BM + r_in_tile;
@@ -532,7 +450,6 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     for (int cc = 0; cc < PASS; cc += 16) {
                         float v[16];
                         if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + cc, BN, v); else tc_ld16(taddr + c0 + cc, v);
-                        if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 16 + cc / 16);
                         // one branch on the activation per 16 columns, not per element (padding columns beyond N carry a
                         // zero bias and are never stored)
                         auto finish = [&](auto actf) {
@@ -547,10 +464,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                         else if (e.act == SPGT_ACT_RELU) finish([](float t) { return fmaxf(t, 0.0f); });
                         else if (e.act == SPGT_ACT_SILU) finish([](float t) { return silu_f(t); });
                         else finish([](float t) { return t; });
-                        if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 20 + cc / 16);
                     }
                     __syncwarp();
-                    if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 12);
                     // phase 2: the warp writes its 32 rows with full-line coalesced float4 stores (+ residual)
                     const int col = nt * BN + c0 + (lane % LPR) * 4;
                     static_assert(PASS == EP_PASS && 32 / RPI == EP_NIT, "residual prefetch follows the store phase's mapping");
@@ -582,7 +497,6 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                         else if (ui + 1 < n_my_units) res_fetch(ui + 1, col_lo);
                     }
                     __syncwarp();
-                    if (epi_idx == 0 && c0 == col_lo) TC_TRACE(ui, 13);
                 }
             } else if constexpr (EPI == EPI_PROJ) {
                 const TcProjEpi& e = ep;
@@ -662,23 +576,15 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 }
             }
             tc_fence_before();
-            if constexpr (PAIR) {                 // one arrival per warp, to the CTA that issues tile mt_e
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(cluster_map(acc_empty(buf), (uint32_t)mt_e));
-            } else {
-                mbar_arrive(acc_empty(buf));
-            }
-            if (epi_idx == 0) TC_TRACE(ui, 10);
+            mbar_arrive(acc_empty(buf));
         }
     }
-    TC_ACC_FLUSH;
     // teardown: everyone meets, then the allocating warp frees the tensor memory
     tc_fence_before();
-    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();     // the pair's MMAs read both CTAs' memories
+    __syncthreads();
     if (warp == TC_MMA_WARP) {
         tc_fence_after();
-        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
-        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
 }
 
@@ -707,24 +613,18 @@ __global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, i
 // 136-wide merged attention heads) two 64-wide column tiles with W resident beat one 128-wide tile that re-streams W
 // for every row tile, the second read of the rows coming from L2.  At K = 256 the doubled row traffic costs more
 // than the W stream (measured: 0.125 vs 0.094 ms for 180k rows).
-static int g_tc_pair = 0;                 // experiment switch: CTA-pair kernels (1: one row tile per CTA, 2: two)
-void tc_set_pair_mode(int on) { g_tc_pair = on; }
 
 static int tc_bn_for(int N, int K) {
     if (N <= 32) return 32;
     if (N <= 64) return 64;
-    if (g_tc_pair == 1) return 128;           // a pair keeps a 128-wide W resident up to K = 256
     return (K > 128 && K <= 192) ? 64 : 128;
 }
 
 template <int BN, int MT, class Loader, int EPI, class EpiParams>
 static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_tiles, const EpiParams& ep, cudaStream_t st) {
-    static bool done = false;
+    static SmemOptIn configured;
     auto kern = tc_gemm_kernel<BN, MT, Loader, EPI, EpiParams>;
-    if (!done) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcCfg<BN, MT>::BYTES) != cudaSuccess) return launch_status();
-        done = true;
-    }
+    if (int e = smem_opt_in(kern, TcCfg<BN, MT>::BYTES, configured)) return e;
     const int m_units = ceil_div(rows, TC_BM * MT);
     int per_nt = num_sms() / n_tiles;                 // CTAs per column tile
     if (per_nt < 1) per_nt = 1;
@@ -734,39 +634,10 @@ static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_til
     return launch_status();
 }
 
-// The same kernel as 2-CTA clusters: a unit is MT row tiles for each CTA of the pair.
-template <int BN, int MT, class Loader, int EPI, class EpiParams>
-static int tc_launch_pair(Loader ld, const float* wimg, int kpad, int rows, int n_tiles, const EpiParams& ep, cudaStream_t st) {
-    static bool done = false;
-    auto kern = tc_gemm_kernel<BN, MT, Loader, EPI, EpiParams, 1>;
-    if (!done) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcCfg<BN, MT>::BYTES) != cudaSuccess) return launch_status();
-        done = true;
-    }
-    const int m_units = ceil_div(rows, TC_BM * MT * 2);
-    int per_nt = (num_sms() / 2) / n_tiles;           // pairs per column tile
-    if (per_nt < 1) per_nt = 1;
-    if (per_nt > m_units) per_nt = m_units;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * per_nt * n_tiles);
-    cfg.blockDim = dim3(tc_threads(MT));
-    cfg.dynamicSmemBytes = TcCfg<BN, MT>::BYTES;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, ld, wimg, kpad, rows, n_tiles, m_units, ep) != cudaSuccess) return launch_status();
-    return launch_status();
-}
-
 template <class Loader>
 static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int rows, const TcLinearEpi& ep, bool long_k, cudaStream_t st) {
     const int bn = tc_bn_for(N, K), kpad = ceil_div(K, TC_BK) * TC_BK, npad = ceil_div(N, bn) * bn;
     const int n_tiles = npad / bn;
-    if (g_tc_pair == 2 && bn == 128) return tc_launch_pair<128, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
-    if (g_tc_pair == 1 && bn == 128 && !long_k) return tc_launch_pair<128, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     if (long_k && bn == 128) return tc_launch<128, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     if (long_k && bn == 64) return tc_launch<64, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     switch (bn) {
@@ -798,14 +669,28 @@ extern "C" int spgt_tc_weight_prepare(const float* w_kn, int ldw, int K, int N, 
     return launch_status();
 }
 
-#ifdef SPGT_TC_TRACE
-extern "C" int spgt_tc_trace_reset(void) { static long long z[64 * 32 + 32 * 8] = {}; return cudaMemcpyToSymbol(g_tc_trace, z, sizeof(z)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH; }
-extern "C" int spgt_tc_trace_read(long long* host_out) {   // 64 units x 16 slots of clock64() values of CTA 0
-    return cudaMemcpyFromSymbol(host_out, g_tc_trace, sizeof(long long) * (64 * 32 + 32 * 8)) == cudaSuccess ? 0 : SPGT_ERR_LAUNCH;
-}
-#endif
 
-namespace spgt { int attn_tc_status(); int ffn_tc_status(); }      // attention_tc.cu, tc_ffn.cu
+namespace spgt {
+int attn_tc_status(); int ffn_tc_status();          // attention_tc.cu, tc_ffn.cu
+int attn_tc_status_reset(); int ffn_tc_status_reset();
+
+// One warp waits on a barrier that nobody arrives at, with a limit of `limit_us` microseconds instead of the two
+// seconds of the production kernels: the wait gives up, latches `code` in the status word and the kernel returns.
+__global__ void tc_wait_expiry_kernel(int code, unsigned long long limit_ns, int* returned) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, code, &g_tc_status, limit_ns);
+        *returned = ok ? 1 : 2;
+    }
+}
+}  // namespace spgt
 
 extern "C" int spgt_tc_status(void) {
     int v = 0;
@@ -814,6 +699,20 @@ extern "C" int spgt_tc_status(void) {
     const int a = spgt::attn_tc_status();
     if (a != 0) return a > 0 ? 100 + a : a;     // 101..109: a wait of the attention kernel gave up
     return spgt::ffn_tc_status();               // 21..33: a wait of the fused feed-forward kernel gave up
+}
+
+extern "C" int spgt_tc_status_reset(void) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)) != cudaSuccess) return SPGT_ERR_LAUNCH;
+    if (int e = spgt::attn_tc_status_reset()) return e;
+    return spgt::ffn_tc_status_reset();
+}
+
+extern "C" int spgt_tc_selftest_wait_expiry(int code, int limit_us, int* returned_dev, spgt_stream_t stream) {
+    if (!returned_dev) return SPGT_ERR_NULL;
+    if (code <= 0 || limit_us <= 0 || limit_us > 100000) return SPGT_ERR_SHAPE;
+    tc_wait_expiry_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(code, (unsigned long long)limit_us * 1000ull, returned_dev);
+    return launch_status();
 }
 
 extern "C" int spgt_linear_tc_fwd(const float* x, int lda, const void* wprep, const float* bias, const float* residual,

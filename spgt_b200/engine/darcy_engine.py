@@ -81,10 +81,14 @@ class HostInference:
                 results.append(host)
             for _, _, out_done in pending:
                 out_done.synchronize()
+        from .. import ops
+        ops.check_tc_status('HostInference.run')      # a kernel that gave up on a wait left incomplete predictions
         return results
 
     def _host_out(self, i, shape):
-        key = (i & 3, tuple(shape))
+        """One pinned host tensor per batch index of a run (kept for the next run of the same length and shape): every
+        returned prediction stays valid until run() is called again."""
+        key = (i, tuple(shape))
         if key not in self._out_host:
             self._out_host[key] = torch.empty(shape, dtype=torch.float32, pin_memory=True)
         return self._out_host[key]

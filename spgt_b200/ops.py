@@ -400,7 +400,17 @@ class TcWeight:
 
 
 def tc_status() -> int:
+    """0, or the code of the first bounded wait of a tensor-core kernel that gave up since the last reset (synchronises)."""
     return int(lib.spgt_tc_status())
+
+
+def check_tc_status(where: str) -> None:
+    """Raise (and clear the latched code) if a kernel gave up on a wait: its outputs are incomplete and must be discarded.
+    Host loops call this at their synchronisation points."""
+    code = tc_status()
+    if code != 0:
+        lib.spgt_tc_status_reset()
+        raise RuntimeError(f'{where}: a tensor-core kernel gave up on a bounded wait (code {code}); results since the last check are invalid')
 
 
 def linear_tc(x: Tensor, w: TcWeight, bias: Optional[Tensor], act=None, residual: Optional[Tensor] = None) -> Tensor:

@@ -35,6 +35,8 @@ def validate_epoch_darcy(model, dataset: DarcyDataset, batch_size: int, device, 
         for b in batches[len(regular):]:
             p = model(b['node'].to(device), b['position'].to(device), b['grid'].to(device))
             total += float(relative_l2_metric(p, b['target'].to(device)))
+    from .. import ops
+    ops.check_tc_status('validate_epoch_darcy')
     return total / len(batches)
 
 

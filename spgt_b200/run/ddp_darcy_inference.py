@@ -65,9 +65,14 @@ def reduce_metric(metric_sum: torch.Tensor, count: torch.Tensor, world: int) -> 
 
 
 def run_sharded(forward: Callable[[Dict[str, torch.Tensor]], torch.Tensor], make_batch: Callable[[range], Dict[str, torch.Tensor]],
-                n_total: int, batch_size: int, rank: int, world: int, target_fn: Optional[Callable] = None):
+                n_total: int, batch_size: int, rank: int, world: int, target_fn: Optional[Callable] = None,
+                sample_shape: Optional[Tuple[int, ...]] = None, device=None):
     """Evaluate samples [0, n_total) sharded over ranks.  `make_batch(range)` builds the inputs of global sample
-    indices, `forward(batch)` returns predictions [n, ...].  Returns (all predictions in global order, metric or None)."""
+    indices, `forward(batch)` returns predictions [n, ...].  Returns (all predictions in global order, metric or None).
+
+    Every rank enters both collectives, also one whose slice is empty (n_total < world): it contributes a [0, ...]
+    block and a zero (sum, count).  Such a rank cannot learn the per-sample shape from a prediction of its own, so
+    callers that may shard fewer samples than ranks pass `sample_shape` (and `device`)."""
     from ..engine.metric import relative_l2_sums
     begin, end = shard_range(n_total, rank, world)
     preds, msum, cnt = [], None, None
@@ -80,9 +85,23 @@ def run_sharded(forward: Callable[[Dict[str, torch.Tensor]], torch.Tensor], make
             s, c = relative_l2_sums(pred, target_fn(idx, batch))
             msum = s if msum is None else msum + s
             cnt = c if cnt is None else cnt + c
-    local = torch.cat(preds, dim=0) if preds else None
+    if preds:
+        local = torch.cat(preds, dim=0)
+    else:
+        if sample_shape is None:
+            raise ValueError(f'rank {rank} has no samples (n_total={n_total}, world={world}): pass sample_shape so that it '
+                             'can still take part in the gather')
+        local = torch.empty((0, *sample_shape), dtype=torch.float32, device=device)
     full = gather_predictions(local, n_total, rank, world)
-    metric = reduce_metric(msum, cnt, world) if msum is not None else None
+    metric = None
+    if target_fn is not None:
+        if msum is None:
+            msum = torch.zeros((), dtype=torch.float32, device=local.device)
+            cnt = torch.zeros((), dtype=torch.float32, device=local.device)
+        metric = reduce_metric(msum, cnt, world)
+    if local.is_cuda:
+        from .. import ops
+        ops.check_tc_status('run_sharded')
     return full, metric
 
 
@@ -108,8 +127,9 @@ def darcy_inference_ddp(cfg: dict, checkpoint: Optional[dict] = None, num_sample
         return {k: v.to(device, non_blocking=True) for k, v in data.items()}
 
     t0 = time.time()
+    r = cfg['r_node']
     pred, _ = run_sharded(lambda b: model(b['node'], b['position'], b['grid']), make_batch, num_samples,
-                          2 * cfg['batch_size'], rank, world)
+                          2 * cfg['batch_size'], rank, world, sample_shape=(r, r, 1), device=device)
     torch.cuda.synchronize()
     if rank == 0:
         print(f'========== valid_time: {time.time() - t0:.6f} ==========')

@@ -9,8 +9,8 @@ The reference is imported unmodified as package ``SpGT`` (a temporary directory 
 named SpGT is put on sys.path; ``termcolor`` and ``h5py``, which its support modules import but the
 forward never uses, are stubbed).  The pure-PyTorch "GT" modules (network/layer.py,
 network/model.py) are run in fp32 on CPU with every drop rate 0, and inputs, weights (converted
-to the SpGT op conventions) and outputs are written as .npz files.  The GPU box has no reference
-checkout, so tests replay these files.
+to the SpGT op conventions) and outputs are written as .npz files.  Machines that run the GPU tests
+need no checkout of the reference: the tests replay these files.
 """
 from __future__ import annotations
 
@@ -59,7 +59,7 @@ def ref_config(oracle_cfg: dict, normalizer) -> dict:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', default=os.environ.get('SPGT_REFERENCE', os.path.join(os.sep, 'root', 'reference')))
+    ap.add_argument('--reference', default=os.environ.get('SPGT_REFERENCE'), required='SPGT_REFERENCE' not in os.environ)
     args = ap.parse_args()
     ref_layer, ref_model, ref_get_res, GaussNormalizer, DarcyDataset = import_reference(args.reference)
     from oracle import gt_oracle as O

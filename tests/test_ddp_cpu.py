@@ -29,7 +29,7 @@ def _worker(rank, world, port, n_total, batch, out_dir):
 
     forward = lambda b: b['node'] * 2.0 + 1.0                     # stands in for the model: sample i -> 2 i + 1
     target = lambda idx, b: b['node'] * 2.0 + 1.5                  # constant offset -> known relative error
-    pred, metric = run_sharded(forward, make_batch, n_total, batch, r, w, target_fn=target)
+    pred, metric = run_sharded(forward, make_batch, n_total, batch, r, w, target_fn=target, sample_shape=(3, 3, 1))
     torch.save({'pred': pred, 'metric': metric}, os.path.join(out_dir, f'rank{rank}.pt'))
     dist.destroy_process_group()
 
@@ -58,3 +58,8 @@ def test_two_ranks_even_split(tmp_path):
 
 def test_two_ranks_uneven_split(tmp_path):
     _run(7, 2, tmp_path)
+
+
+def test_two_ranks_one_sample(tmp_path):
+    """Fewer samples than ranks: the rank with an empty slice still enters the gather and the metric reduction."""
+    _run(1, 2, tmp_path)

@@ -34,26 +34,23 @@ def test_linear_tc(dev, rows, K, N, act, res):
     assert torch.equal(y, ops.linear_tc(x.to(dev), wt, b.to(dev), act, None if r is None else r.to(dev)))
 
 
-@pytest.mark.parametrize('pair', [1, 2])
-@pytest.mark.parametrize('rows,K,N,res', [(1, 128, 128, False), (300, 128, 256, False), (1000, 136, 128, True), (5000, 256, 128, True),
-                                          (70000, 160, 384, False)])
-def test_linear_tc_cta_pairs(dev, pair, rows, K, N, res):
-    """The experimental 2-CTA (cta_group::2) variants of the GEMM kernel give the same result as the default one."""
+def test_bounded_wait_expires_and_status_latches(dev):
+    """A wait on a barrier nothing arrives at gives up after its limit: the kernel returns, the code is latched until reset."""
     from spgt_b200 import ops
-    from spgt_b200._lib import lib
-    g = torch.Generator().manual_seed(rows + K + pair)
-    x, w, b = torch.randn(rows, K, generator=g), torch.randn(N, K, generator=g) / K ** 0.5, torch.randn(N, generator=g)
-    r = torch.randn(rows, N, generator=g).to(dev) if res else None
-    ref = torch.nn.functional.linear(x.double(), w.double(), b.double()) + (r.double().cpu() if res else 0)
-    base = ops.linear_tc(x.to(dev), ops.TcWeight(w.t().contiguous().to(dev)), b.to(dev), None, r)
-    try:
-        assert lib.spgt_set_tuning(b'tc_pair', pair) == 0        # also selects the weight image layout: prepare after it
-        y = ops.linear_tc(x.to(dev), ops.TcWeight(w.t().contiguous().to(dev)), b.to(dev), None, r)
-        torch.cuda.synchronize()
-    finally:
-        lib.spgt_set_tuning(b'tc_pair', 0)
+    from spgt_b200._lib import lib, check
+    torch.cuda.synchronize()
     assert ops.tc_status() == 0
-    assert rel_l2(y, ref) < TOL and rel_l2(base, ref) < TOL
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    check(lib.spgt_tc_selftest_wait_expiry(77, 500, flag.data_ptr(), torch.cuda.current_stream().cuda_stream), 'selftest')
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 2                       # the wait expired and the thread went on
+    assert ops.tc_status() == 77
+    with pytest.raises(RuntimeError):
+        ops.check_tc_status('test')
+    assert ops.tc_status() == 0                        # check_tc_status clears the code after reporting it
+    x = torch.randn(300, 128, device=dev)              # the context is still usable
+    y = ops.linear_tc(x, ops.TcWeight(torch.eye(128, device=dev)), None)
+    assert rel_l2(y, x.double().cpu()) < TOL and ops.tc_status() == 0
 
 
 @pytest.mark.parametrize('B,Hh,Ww,cin_pitch,cin_off,Cin,Cout,act', [(2, 9, 11, 128, 0, 128, 44, 'relu'), (1, 13, 13, 132, 44, 44, 44, 'relu'),
