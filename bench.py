@@ -1,19 +1,26 @@
 #!/usr/bin/env python
-"""Darcy Galerkin Transformer inference benchmark (211 x 211 fine grid, 53 x 53 attention grid).
+"""Darcy Galerkin Transformer inference benchmark (211 x 211 fine grid, 53 x 53 attention grid, global batch 64).
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-One rank per GPU (torchrun for N > 1).  A step is one forward of the full model over this rank's batch of
-synthetic Darcy coefficient fields; rank 0 prints one JSON line.  `value` is samples/s with the inputs resident
-in HBM, `e2e` the same metric through the host-facing API with pinned host buffers (upload and download inside
-the timed region), `roofline` the Galerkin attention kernel's achieved HBM bandwidth measured with CUDA events
-around its launches inside the timed steps, `cpu_baseline` the CPU oracle (a port of the reference's own CPU
-path) on a bounded sample.  `--impl reference` times that CPU path alone with all host threads.
+One rank per GPU (torchrun for N > 1).  A step is one forward of the full model over the GLOBAL batch of 64 synthetic
+Darcy coefficient fields, sharded 64/N per rank (strong scaling, no collective inside the forward); rank 0 prints one
+JSON line.
+  value         samples/s with the inputs resident in HBM: blocks of K replays of the captured forward, CUDA events, max
+                over ranks per block, median block.
+  e2e           the same metric through the host-facing API: per step every rank uploads its slice from pinned host
+                memory, runs the forward, all ranks all-gather the predictions and all-reduce the validation metric
+                (NCCL), rank 0 downloads the gathered predictions; uploads / downloads overlap the next / previous step.
+  roofline      the Galerkin attention kernel: CUDA events around each of its launches in a separate eagerly launched
+                pass over the same inputs; roofline_spectral the same for the spectral layer's launches.
+  cpu_baseline  the reference's own CPU model (or, where its files are not staged, the CPU restatement) on a bounded sample.
+`--impl reference` times that CPU path alone, with all host threads, on rank 0.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -28,9 +35,12 @@ import torch.distributed as dist  # noqa: E402
 
 METRIC = 'darcy_gt_inference_samples_per_s_211'
 FINE, SUB_NODE, SUB_ATTN, MODES, SEED = 421, 2, 8, 12, 4
-# DRAM bytes (read + write) of one galerkin_attn_tc_kernel launch at B=64, H=4, S=2809 from the ncu capture
-# summarised in profiles/ (None until a capture of the current kernel exists).
-ATTN_TRAFFIC_BYTES = 342_400_000   # dram read + write per launch from the ncu capture under profiles/ (342.1 - 342.6 MB)
+GLOBAL_BATCH = 64
+CPU_SAMPLE = 8                     # samples per forward of the CPU legs (a bounded sample of the 64-sample step)
+# DRAM bytes (read + write) of one launch at batch 64 from the committed ncu summaries of these kernels; they grow in
+# proportion to the batch, so a rank that holds 64/N samples is charged 1/N of them.
+ATTN_TRAFFIC_BYTES_B64 = 342_400_000
+SPECTRAL_TRAFFIC_BYTES_B64 = None
 
 
 def measured_peak():
@@ -94,25 +104,48 @@ class ClockSampler:
         return {'sm_mhz': sm[len(sm) // 2], 'sm_max_mhz': max(mx), 'reasons': sorted(reasons), 'samples': len(sm)}
 
 
-def oracle_setup(batch: int, seed: int = SEED):
-    from oracle import gt_oracle as O
-    from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
-    cfg = O.default_config(FINE, SUB_NODE, SUB_ATTN, MODES)
-    data = synthetic_darcy_batch(range(batch), FINE, SUB_NODE, SUB_ATTN, seed)
-    return O, cfg, data
-
-
-def oracle_params(seed: int = SEED):
-    """Random-init weights of the benchmark architecture in the SpGT layout (same construction as the GPU model)."""
-    from spgt_b200.config.config_accessor import get_darcy_config
-    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
-    torch.manual_seed(seed)
-    model = Sp_GalerkinTransformer2D(get_darcy_config(SUB_NODE, SUB_ATTN, num_frequence_mode=MODES))
-    return {k: v.detach().clone() for k, v in model.state_dict().items()}
-
-
 WORKLOAD = ('full Darcy Galerkin Transformer forward, fine grid 211x211, attention grid 53x53, 6 encoder '
             'layers (hidden 128, 4 heads, FFN 256), FNO2d regressor (2 spectral layers, width 32, 12 modes)')
+
+
+def random_state(seed: int = SEED, modes: int = MODES):
+    """Random-init weights of the benchmark architecture, keyed and laid out as the reference's Sp_GalerkinTransformer2D
+    state_dict (network/sp_model.py:67-89) and drawn with the reference's initialisers: torch's Linear / Conv2d defaults,
+    xavier_uniform(gain 0.01) + 0.01 I for the Q/K/V matrices with zero biases and unit LayerNorm (network/sp_layer.py:39-50),
+    xavier_normal with gain sqrt(in + out) / (in * out) for the Fourier weights (network/sp_layer.py:119-123).  Plain
+    torch, no package import: both arms of the benchmark build their weights from this one function."""
+    g = torch.Generator().manual_seed(seed)
+    st = {}
+
+    def dense(prefix, out_f, fan_in, shape):
+        bound = 1.0 / math.sqrt(fan_in)
+        st[prefix + '.weight'] = (torch.rand(*shape, generator=g) * 2 - 1) * bound
+        st[prefix + '.bias'] = (torch.rand(out_f, generator=g) * 2 - 1) * bound
+
+    for i, (co, ci) in enumerate(((128, 1), (42, 128), (42, 42), (44, 42))):
+        dense(f'down_scaler.conv{i}.conv_layer', co, ci * 9, (co, ci, 3, 3))
+    for l in range(6):
+        a = f'encoder_mixer.layers.{l}.attention_layer.'
+        for n in 'QKV':
+            st[a + 'weight_' + n] = torch.nn.init.xavier_uniform_(torch.empty(128, 128), gain=0.01, generator=g) + 0.01 * torch.eye(128)
+            st[a + 'bias_' + n] = torch.zeros(128)
+        for n in 'KV':
+            st[a + 'ln_weight_' + n], st[a + 'ln_bias_' + n] = torch.ones(4, 32), torch.zeros(4, 32)
+        dense(a + 'fc_layer', 128, 136, (128, 136))
+        f = f'encoder_mixer.layers.{l}.ffn_layer.'
+        dense(f + 'layer1', 256, 128, (256, 128))
+        dense(f + 'layer2', 128, 256, (128, 256))
+    dense('up_scaler.conv.conv_layer', 128, 128 * 9, (128, 128, 3, 3))
+    d = 'decoder_regressor.'
+    dense(d + 'spatial_fc_layer', 32, 130, (32, 130))
+    for l in range(2):
+        dense(d + f'layers.{l}.residual_layer', 32, 32, (32, 32))
+        for k in range(2):
+            st[d + f'layers.{l}.fourier_weight.{k}'] = torch.nn.init.xavier_normal_(
+                torch.empty(modes, modes, 32, 32, 2), gain=math.sqrt(64.0) / 1024.0, generator=g)
+    dense(d + 'ffn_layer.layer1', 128, 32, (128, 32))
+    dense(d + 'ffn_layer.layer2', 1, 128, (1, 128))
+    return st
 
 
 def use_all_host_threads() -> int:
@@ -125,34 +158,41 @@ def use_all_host_threads() -> int:
     return torch.get_num_threads()
 
 
-def time_oracle(sample_batch: int, steps: int, warmup: int):
-    O, cfg, data = oracle_setup(sample_batch)
-    p = oracle_params()
-    fwd = lambda: O.model_forward(data['node'], data['position'], data['grid'], p, cfg)
-    with torch.no_grad():
-        for _ in range(warmup):
-            fwd()
+def time_cpu_path(steps: int, warmup: int):
+    """The reference's CPU model (oracle/_ref, staged by oracle/build_ref.py) or, without it, the CPU restatement, on
+    CPU_SAMPLE of the benchmark's samples per forward.  Returns (samples/s, s per forward, kind, cores)."""
+    from oracle import gt_oracle as O
+    from oracle import ref_runner as R
+    cores = use_all_host_threads()
+    ocfg = O.default_config(FINE, SUB_NODE, SUB_ATTN, MODES)
+    data = R.synthetic_batch(range(CPU_SAMPLE), FINE, SUB_NODE, SUB_ATTN, SEED)
+    fwd, kind = R.make_forward(ocfg, random_state())
+    for _ in range(warmup):
+        fwd(data['node'], data['position'], data['grid'])
+    times = []
+    for _ in range(steps):
         t0 = time.perf_counter()
-        for _ in range(steps):
-            fwd()
-        dt = time.perf_counter() - t0
-    return sample_batch * steps / dt, dt / steps
+        fwd(data['node'], data['position'], data['grid'])
+        times.append(time.perf_counter() - t0)
+    per = sum(times) / len(times)
+    return CPU_SAMPLE / per, per, kind, cores
 
 
 def run_reference(args, rank):
+    """--impl reference: the CPU path alone on rank 0 (other ranks have nothing to do and return at once)."""
     if rank != 0:
         return
-    cores = use_all_host_threads()
-    sample = 8
-    sps, per_step = time_oracle(sample, args.steps, args.warmup)
+    sps, per_step, kind, cores = time_cpu_path(args.steps, args.warmup)
+    sample = (f'{CPU_SAMPLE} of the {GLOBAL_BATCH} samples of a step per timed forward, '
+              + ("the reference's GalerkinTransformer2D (network/model.py)" if kind == 'reference' else 'CPU restatement of the reference model')
+              + f', torch CPU fp32, {cores} threads')
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': sps, 'unit': 'samples/s', 'n_gpus': args.gpus, 'steps': args.steps,
-        'warmup': args.warmup, 'ms_per_step': per_step * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'warmup': args.warmup, 'ms_per_step': per_step * 1e3, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
         'dtype': 'f32', 'data': 'synthetic', 'gpu_launches': 0,
-        'config': {'workload': WORKLOAD, 'batch_per_gpu': 64, 'global_batch': 64 * args.gpus, 'parallelism': f'dp{args.gpus}', 'seed': SEED,
-                   'cpu_sample': f'{sample} of the 64 samples of a step per timed forward'},
-        'cpu_baseline': {'value': sps, 'unit': 'samples/s', 'cores': cores, 'kind': 'port',
-                         'sample': f'{sample} samples per step (1/8 of the 64-sample batch), torch CPU fp32, {cores} threads'},
+        'config': {'workload': WORKLOAD, 'global_batch': GLOBAL_BATCH, 'batch_per_gpu': GLOBAL_BATCH // max(1, args.gpus),
+                   'parallelism': f'dp{args.gpus}', 'seed': SEED, 'cpu_sample': sample},
+        'cpu_baseline': {'value': sps, 'unit': 'samples/s', 'cores': cores, 'kind': kind, 'sample': sample},
         'e2e': {'value': sps, 'unit': 'samples/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
     }
     print(json.dumps(line), flush=True)
@@ -303,9 +343,11 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='spgt_b200', choices=['spgt_b200', 'reference'])
-    ap.add_argument('--batch', type=int, default=64, help='samples per GPU per step')
+    ap.add_argument('--batch', type=int, default=GLOBAL_BATCH, help='global batch per step, sharded evenly over the ranks')
+    ap.add_argument('--min-seconds', type=float, default=1.0, help='repeat the K-step block until this much time has been measured')
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--no-graphs', action='store_true', help='end-to-end leg launches the kernels eagerly instead of replaying CUDA graphs')
+    ap.add_argument('--no-graphs', action='store_true', help='launch the kernels eagerly instead of replaying CUDA graphs')
+    ap.add_argument('--no-weak-leg', action='store_true', help='skip the secondary 64-samples-per-GPU measurement of multi-GPU runs')
     ap.add_argument('--breakdown', action='store_true', help='also print a per-entry-point time table to stderr')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != 'reference' else args.warmup
@@ -325,23 +367,33 @@ def main():
     from spgt_b200 import ops
     from spgt_b200.config.config_accessor import get_darcy_config
     from spgt_b200.dataset.darcy_dataset import GaussNormalizer, synthetic_darcy_batch
-    from spgt_b200.engine.darcy_engine import HostInference
+    from spgt_b200.engine.darcy_engine import GraphedForward, HostInference
     from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+    from spgt_b200.run.ddp_darcy_inference import ShardedGather, shard_range
 
     device = torch.device('cuda', local)
     torch.cuda.set_device(device)
     if world > 1:
         dist.init_process_group('nccl', init_method='env://', device_id=device)
+    if args.batch % world != 0:
+        raise SystemExit(f'--batch {args.batch} does not split evenly over {world} ranks')
 
     cfg = get_darcy_config(SUB_NODE, SUB_ATTN, num_frequence_mode=MODES)
     cfg['target_normalizer'] = GaussNormalizer()
-    torch.manual_seed(SEED)
-    model = Sp_GalerkinTransformer2D(cfg).to(device).eval()
-    B = args.batch
-    host = synthetic_darcy_batch(range(rank * B, (rank + 1) * B), FINE, SUB_NODE, SUB_ATTN, SEED)
-    host = {k: v.pin_memory() for k, v in host.items() if k != 'coeff'}
+    model = Sp_GalerkinTransformer2D(cfg)
+    model.load_state_dict(random_state(), strict=True)
+    model = model.to(device).eval()
+    G = args.batch
+    begin, end = shard_range(G, rank, world)
+    B = end - begin                                           # samples of this rank per step
+    r, S, H, DPK = cfg['r_node'], cfg['r_attn'] ** 2, cfg['num_head'], 34
+
+    def make_host(indices):
+        h = synthetic_darcy_batch(indices, FINE, SUB_NODE, SUB_ATTN, SEED)
+        h['target'] = h.pop('coeff') * 0.01                  # stands in for the PDE solution the validation metric compares with
+        return {k: v.pin_memory() for k, v in h.items()}
+    host = make_host(range(begin, end))
     dev = {k: v.to(device) for k, v in host.items()}
-    S, H, DPK = cfg['r_attn'] ** 2, cfg['num_head'], 34
 
     def barrier():
         if world > 1:
@@ -355,74 +407,143 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
+    def timed_blocks(step_fn, steps, min_seconds):
+        """Blocks of exactly `steps` calls, each bracketed by barrier + synchronize and timed with CUDA events on the
+        launching stream, max over ranks; repeated until min_seconds have been measured.  Returns the block times (ms)."""
+        blocks, total = [], 0.0
+        while True:
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                step_fn()
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1))
+            blocks.append(ms)
+            total += ms
+            if (total >= min_seconds * 1e3 and len(blocks) >= 3) or len(blocks) >= 200:
+                return blocks
+
+    def device_leg(inputs, steps, min_seconds):
+        if args.no_graphs:
+            fwd = lambda: model(inputs['node'], inputs['position'], inputs['grid'])
+        else:
+            graphed = GraphedForward(model, inputs['node'], inputs['position'], inputs['grid'], own_inputs=False)
+            fwd = lambda: graphed(inputs['node'], inputs['position'], inputs['grid'])
+        for _ in range(args.warmup):
+            fwd()
+        return timed_blocks(fwd, steps, min_seconds)
+
+    # ---------------- kernels per forward (counted on an eager pass) ----------------
+    for _ in range(2):
+        model(dev['node'], dev['position'], dev['grid'])     # weight images, tables and kernel attributes are set up here
+    l0 = ops.LAUNCHES
+    model(dev['node'], dev['position'], dev['grid'])
+    launches_per_forward = ops.LAUNCHES - l0
+
     # ---------------- device-resident throughput ----------------
-    for _ in range(args.warmup):
-        model(dev['node'], dev['position'], dev['grid'])
-    barrier()
-    launches0 = ops.LAUNCHES
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks, ops.profile_ops(only=['spgt_galerkin_attn_fwd']) as prof:
-        e0.record()
-        for _ in range(args.steps):
-            out = model(dev['node'], dev['position'], dev['grid'])
-        e1.record()
-        barrier()
-    elapsed_ms = max_over_ranks(e0.elapsed_time(e1))
-    launches = ops.LAUNCHES - launches0
-    attn_ms = prof.times_ms().get('spgt_galerkin_attn_fwd', [])
-    attn_avg_ms = sum(attn_ms) / max(1, len(attn_ms))
-    value = world * B * args.steps / (elapsed_ms * 1e-3)
+    with ClockSampler(local) as clocks:
+        blocks = device_leg(dev, args.steps, args.min_seconds)
+    blocks_sorted = sorted(blocks)
+    elapsed_ms = blocks_sorted[len(blocks_sorted) // 2]
+    value = G * args.steps / (elapsed_ms * 1e-3)
 
     # ---------------- end to end through the host-facing API ----------------
     engine = HostInference(model, device, use_graphs=not args.no_graphs)
-    outs = [torch.empty(B, cfg['r_node'], cfg['r_node'], 1, dtype=torch.float32, pin_memory=True) for _ in range(2)]
-    engine.run([host] * args.warmup, [outs[i & 1] for i in range(args.warmup)])
+    gather = ShardedGather(G, rank, world, (r, r, 1), device)
+    engine.run([host] * args.warmup, post=gather)
     barrier()
     t0 = time.perf_counter()
-    engine.run([host] * args.steps, [outs[i & 1] for i in range(args.steps)])
+    results = engine.run([host] * args.steps, post=gather)
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
-    nbytes = engine.bytes_per_batch(host)
-    e2e_value = world * B * args.steps / e2e_s
+    nb = engine.bytes_per_batch(host)
+    e2e_value = G * args.steps / e2e_s
+    metric_value = gather.metric(args.steps - 1)
 
-    # ---------------- roofline of the attention kernel ----------------
+    # ---------------- the gathered predictions, checked after the timed region ----------------
+    gather_check = None
+    pred_local = model(dev['node'], dev['position'], dev['grid'])
+    csum = pred_local.double().sum().reshape(1)
+    if world > 1:
+        sums = torch.empty(world, dtype=torch.float64, device=device)
+        dist.all_gather_into_tensor(sums, csum)
+    else:
+        sums = csum
+    if rank == 0:
+        full = results[-1]                                   # pinned host copy of the last step's gathered predictions
+        ok = torch.equal(full[begin:end], pred_local.cpu())
+        for rk in range(world):
+            b, e = shard_range(G, rk, world)
+            ok = ok and abs(float(full[b:e].double().sum()) - float(sums[rk])) <= 1e-9 * abs(float(sums[rk]))   # rank rk's block sits where the global order puts it
+        gather_check = 'ok' if ok else 'MISMATCH'
+
+    # ---------------- rooflines of the attention kernel and the spectral layer (separate eager pass) ----------------
+    names = ['spgt_galerkin_attn_fwd', 'spgt_spectral_conv2d_fwd']
+    with ops.profile_ops(only=names) as prof:
+        for _ in range(args.steps):
+            model(dev['node'], dev['position'], dev['grid'])
+    tm = prof.times_ms()
     peak, peak_kind = measured_peak()
-    algo_bytes = 4 * B * H * DPK * S * 4                      # read Q, K, V and write out, fp32
-    achieved = algo_bytes / (attn_avg_ms * 1e-3) / 1e9 if attn_avg_ms > 0 else None
-    roofline = {'kernel': 'galerkin_attn_tc_kernel', 'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'peak_kind': peak_kind,
-                'unit': 'GB/s', 'frac': (achieved / peak) if achieved else None, 'traffic': ATTN_TRAFFIC_BYTES,
-                'algorithmic_bytes': algo_bytes, 'avg_launch_ms': attn_avg_ms, 'launches_timed': len(attn_ms)}
+
+    def roofline(name, kernel, algo_bytes, traffic_b64):
+        t = tm.get(name, [])
+        avg = sum(t) / max(1, len(t))
+        achieved = algo_bytes / (avg * 1e-3) / 1e9 if avg > 0 else None
+        return {'kernel': kernel, 'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s',
+                'frac': (achieved / peak) if achieved else None,
+                'traffic': (traffic_b64 * B // 64) if traffic_b64 else None, 'algorithmic_bytes': algo_bytes,
+                'avg_launch_ms': avg, 'launches_timed': len(t)}
+    roof_attn = roofline('spgt_galerkin_attn_fwd', 'galerkin_attn_tc_kernel', 4 * B * H * DPK * S * 4, ATTN_TRAFFIC_BYTES_B64)
+    # spectral layer: read x once, write y once (fp32, 32 channels) + the complex mode weights; one entry-point call = all its kernels
+    roof_spec = roofline('spgt_spectral_conv2d_fwd', 'spectral layer (all kernels of one call)',
+                         2 * B * r * r * 32 * 4 + 2 * 2 * MODES * MODES * 32 * 32 * 8, SPECTRAL_TRAFFIC_BYTES_B64)
+
+    # ---------------- secondary: fixed 64 samples per GPU (weak scaling) ----------------
+    weak = None
+    if world > 1 and not args.no_weak_leg:
+        wdev = {k: v.to(device) for k, v in make_host(range(rank * 64, rank * 64 + 64)).items()}
+        wb = sorted(device_leg(wdev, args.steps, 0.0))
+        wms = wb[len(wb) // 2]
+        weak = {'batch_per_gpu': 64, 'global_batch': 64 * world, 'value': world * 64 * args.steps / (wms * 1e-3), 'ms_per_step': wms / args.steps}
+        del wdev
 
     if args.breakdown and rank == 0:
         with ops.profile_ops() as pall:
             model(dev['node'], dev['position'], dev['grid'])
-        tm = pall.times_ms()
-        tot = sum(sum(v) for v in tm.values())
-        for k, v in sorted(tm.items(), key=lambda kv: -sum(kv[1])):
+        tb = pall.times_ms()
+        tot = sum(sum(v) for v in tb.values())
+        for k, v in sorted(tb.items(), key=lambda kv: -sum(kv[1])):
             print(f'{k:34s} calls {len(v):3d}  total {sum(v):8.3f} ms  {100 * sum(v) / tot:5.1f} %', file=sys.stderr)
             if len(v) > 1:
                 print('    per call (us): ' + ' '.join(f'{1e3 * t:.0f}' for t in v), file=sys.stderr)
         print(f'{"sum":34s} {tot:8.3f} ms', file=sys.stderr)
 
+    ops.check_tc_status('bench')                              # a kernel that gave up on a wait would have produced garbage timings
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cores = use_all_host_threads()
-        sps, per_step = time_oracle(8, 3, 1)
-        cpu = {'value': sps, 'unit': 'samples/s', 'cores': cores, 'kind': 'port',
-               'sample': f'8 samples per forward (1/8 of the batch), 3 timed forwards after 1 warm-up, torch CPU fp32, {cores} threads'}
+        sps, per_step, kind, cores = time_cpu_path(5, 1)
+        cpu = {'value': sps, 'unit': 'samples/s', 'cores': cores, 'kind': kind,
+               'sample': f'{CPU_SAMPLE} samples per forward (1/8 of the global batch), 5 timed forwards after 1 warm-up, torch CPU fp32, {cores} threads'}
 
     if rank == 0:
         line = {
             'metric': METRIC, 'value': value, 'unit': 'samples/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
-            'ms_per_step': elapsed_ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'ms_per_step': elapsed_ms / args.steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
             'dtype': 'f32', 'data': 'synthetic',
-            'config': {'workload': WORKLOAD, 'batch_per_gpu': B, 'global_batch': B * world, 'parallelism': f'dp{world}', 'seed': SEED,
-                       'l2_policy': 'per-step working set (several GB of activations) is far larger than the 126 MB L2'},
-            'clocks': clocks.summary(), 'gpu_launches': launches,
-            'e2e': {'value': e2e_value, 'unit': 'samples/s', 'h2d_bytes_per_step': nbytes['h2d'], 'd2h_bytes_per_step': nbytes['d2h'],
-                    'ms_per_step': e2e_s * 1e3 / args.steps},
-            'roofline': roofline, 'cpu_baseline': cpu,
+            'config': {'workload': WORKLOAD, 'global_batch': G, 'batch_per_gpu': B, 'parallelism': f'dp{world}', 'seed': SEED,
+                       'forward': 'eager launches' if args.no_graphs else 'CUDA graph replay',
+                       'l2_policy': f'per-step working set ({B * 47} MB of activations per rank) is larger than the 126 MB L2',
+                       'timing': f'median of {len(blocks)} blocks of {args.steps} steps (CUDA events, max over ranks per block)'},
+            'clocks': clocks.summary(), 'gpu_launches': launches_per_forward * args.steps, 'launches_per_forward': launches_per_forward,
+            'block_ms': {'min': blocks_sorted[0], 'median': elapsed_ms, 'max': blocks_sorted[-1], 'n': len(blocks)},
+            'e2e': {'value': e2e_value, 'unit': 'samples/s', 'h2d_bytes_per_step': nb['h2d'] * world, 'd2h_bytes_per_step': G * r * r * 4 + 16 * world,
+                    'ms_per_step': e2e_s * 1e3 / args.steps,
+                    'collectives_per_step': 0 if world == 1 else 2, 'gather_check': gather_check, 'metric': metric_value},
+            'roofline': roof_attn, 'roofline_spectral': roof_spec, 'cpu_baseline': cpu, 'weak_64_per_gpu': weak,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -41,7 +41,8 @@ int spgt_last_cuda_error(void);
 /* Library ABI version (bumped when a signature changes). */
 int spgt_abi_version(void);
 /* Experiment knobs: "attn_cluster" = 0 (heuristic), 1, 2, 4 or 8 CTAs per (batch, head) in spgt_galerkin_attn_fwd;
- * "attn_impl" = 0 (tcgen05 kernel, default) or 1 (warp-MMA kernel). */
+ * "attn_impl" = 0 (tcgen05 kernel, default) or 1 (warp-MMA kernel);
+ * "spectral_chunk_mb" = megabytes of x per chunk of the spectral layer (0 = whole batch, default). */
 int spgt_set_tuning(const char* key, int value);
 
 /* ---------------------------------------------------------------------------------------------
@@ -106,7 +107,10 @@ int spgt_projpos_bwd_elementwise(const float* grad_out, const float* h, const fl
                                  size_t workspace_bytes, spgt_stream_t stream);
 
 /* C[b] = alpha * A[b] * B[b] with A [batch,M,K], B [batch,K,N], C [batch,M,N], all row-major; K is the long
- * dimension.  Split-K with per-split partial tiles in `workspace`, summed in split order (deterministic).
+ * dimension.  N % 4 == 0: one launch of a persistent kernel that cuts the k range of all (batch, 32x32 tile) items
+ * evenly over one CTA per SM; items that span several CTAs leave partial tiles (and a ticket count) in `workspace`
+ * and the CTA that finishes last adds them in CTA order.  Other N: split-K in two passes with per-split partial
+ * tiles in `workspace`, summed in split order.  Both are deterministic (bit-identical from run to run).
  * Replaces batched_skinny_gemm (extension/bind/galerkin_attention.cu:175-198, GEMM_Order::RRR). */
 size_t spgt_skinny_gemm_workspace_bytes(int M, int N, int K, int batch);
 int spgt_batched_skinny_gemm(const float* A, const float* B, float* C, float alpha, int M, int N, int K, int batch,
@@ -114,13 +118,16 @@ int spgt_batched_skinny_gemm(const float* A, const float* B, float* C, float alp
 
 /* The same product for callers that can neither pass a workspace nor allocate one (plugin callbacks, real-time
  * loops, hosts whose device allocator is out of reach at call time).  No counterpart in the reference, whose
- * binding allocates its split-K buffer through torch on every call.  The partial tiles live in a fixed
- * 8 MiB array inside the library image (one per device); the call allocates nothing.
+ * binding allocates its split-K buffer through torch on every call.  The scratch (partial tiles and ticket
+ * counts) lives in a fixed 8 MiB array inside the library image (one per device); the call allocates nothing and
+ * runs the same kernels on the same plan as spgt_batched_skinny_gemm (bit-identical result).
  *  - Limit: spgt_skinny_gemm_workspace_bytes(M,N,K,batch) must not exceed spgt_skinny_gemm_noalloc_max_bytes();
  *    otherwise SPGT_ERR_TOO_LARGE is returned and nothing is launched.
- *  - The first call on each device (that device current) looks up the array's device address; make it before any
- *    stream capture.  Later calls only launch kernels.
- *  - Nothing has to be zeroed: every partial tile that is read is written earlier in the same call.
+ *  - The first call on each device (that device current) looks up the array's device address and sets kernel
+ *    attributes; with lazy module loading it may also be the call that loads the module holding the array.  Make it
+ *    before any stream capture.  Later calls only clear the ticket counts (a memset on the stream) and launch kernels.
+ *  - The array keeps the last call's contents.  Partial tiles need no clearing (every tile that is read is written
+ *    earlier in the same call); the ticket counts must start at zero and are cleared by each call.
  *  - One array per device: calls that may overlap on a device (different streams) race; keep them on one stream
  *    or order them with events. */
 size_t spgt_skinny_gemm_noalloc_max_bytes(void);
@@ -284,11 +291,17 @@ int spgt_decoder_head_tc_fwd(const float* x, const void* w1prep, const float* b1
  * fw0, fw1 [m,m,C,C,2] (the SpGT fourier_weight layout); 1 <= m <= 16, 2m <= r.
  * tables: spgt_spectral_tables_bytes(r,m) bytes filled once by spgt_spectral_tables_init.
  * workspace: spgt_spectral_workspace_bytes(B,r,m,C) bytes of scratch (contents undefined afterwards).
+ * The batch can be processed in chunks of spgt_spectral_chunk_samples(r) samples (tuning key "spectral_chunk_mb",
+ * megabytes of x per chunk; 0 = the whole batch, the default) so that the second pass over a chunk's x is served by
+ * the L2 cache; the scratch is sized for one chunk, so query it after setting the key.
  * Replaces batched_transpose + torch.fft.rfft2 + transpose_gather_dual + complex matmul + transpose_scatter_dual
  * + torch.fft.irfft2 + batched_transpose + residual Linear + activation. */
 size_t spgt_spectral_tables_bytes(int r, int m);
 int spgt_spectral_tables_init(void* tables, size_t tables_bytes, int r, int m, spgt_stream_t stream);
 size_t spgt_spectral_workspace_bytes(int B, int r, int m, int C);
+int spgt_spectral_chunk_samples(int r);
+/* Kernels one spgt_spectral_conv2d_fwd call launches for these sizes (launch accounting of benchmarks). */
+int spgt_spectral_launches(int B, int r, int m);
 int spgt_spectral_conv2d_fwd(const float* x, const float* wr, const float* br, const float* fw0, const float* fw1,
                              const void* tables, void* workspace, size_t workspace_bytes, float* y,
                              int B, int r, int C, int m, int act, spgt_stream_t stream);

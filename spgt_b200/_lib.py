@@ -66,6 +66,8 @@ SIGNATURES = {
     'spgt_spectral_tables_bytes': (_sz, [_i, _i]),
     'spgt_spectral_tables_init': (_i, [_f, _sz, _i, _i, _st]),
     'spgt_spectral_workspace_bytes': (_sz, [_i, _i, _i, _i]),
+    'spgt_spectral_chunk_samples': (_i, [_i]),
+    'spgt_spectral_launches': (_i, [_i, _i, _i]),
     'spgt_spectral_conv2d_fwd': (_i, [_f, _f, _f, _f, _f, _f, _f, _sz, _f, _i, _i, _i, _i, _i, _st]),
 }
 

@@ -456,6 +456,203 @@ skinny_reduce_kernel(const float* __restrict__ ws, float* __restrict__ C, float 
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// The same product in ONE launch with the k range of all (batch, tile) items cut evenly over one persistent CTA
+// per SM ("stream-K"): the items' 32-wide k slices form one long list, CTA c takes the c-th equal share of it, so a
+// CTA works on the end of one item, possibly some whole items, and the start of another.  An item that lies
+// inside one CTA is scaled and stored directly.  The pieces of an item that spans several CTAs go to a small
+// scratch (two 32x32 slots per CTA); every CTA that finishes a piece takes a ticket on the item's counter and the
+// one that takes the last ticket adds the pieces in CTA order - a fixed order, so the result is bit-identical from
+// run to run - scales the sum and stores it.  Nothing ever waits for another CTA.
+// Rows of A are only 4-byte aligned (K is arbitrary): a row piece is fetched as nine 16-byte cp.async chunks that
+// start at the aligned element at or below its first column; the wanted elements then sit (element index of the
+// piece start) mod 4 floats into the shared-memory row.  Requires N % 4 == 0 (16-byte chunks of the B rows).
+// ------------------------------------------------------------------------------------------------------------
+constexpr int SKS_WARPS = 6, SKS_STAGES = 3;
+constexpr int SKS_AP = 36;   // A tile row: 32 wanted floats + up to 3 of shift, nine 16-byte chunks; == 4 (mod 32)
+constexpr int SKS_BP = 40;   // B tile row pitch, == 8 (mod 32)
+constexpr int SKS_STAGE = 32 * SKS_AP + 32 * SKS_BP;
+constexpr int SKS_WARP_FLOATS = SKS_STAGES * SKS_STAGE;
+constexpr size_t SKS_SMEM = (size_t)SKS_WARPS * SKS_WARP_FLOATS * sizeof(float);
+static_assert(SKS_WARP_FLOATS >= 1024, "a warp's region also holds its 32x32 partial tile");
+
+struct SksPlan { int64_t total; int nsub; int tiles, tiles_n; int P; };
+// CTA that owns unit u of the list: the c with floor(c * total / P) <= u < floor((c + 1) * total / P)
+__host__ __device__ inline int sks_owner(int64_t u, int64_t total, int P) { return (int)(((u + 1) * P - 1) / total); }
+
+__global__ void __launch_bounds__(SKS_WARPS * 32, 1)
+skinny_streamk_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, float alpha,
+                      int M, int N, int K, SksPlan pl, float* __restrict__ pieces, unsigned int* __restrict__ tickets) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ int s_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int c = blockIdx.x, P = pl.P, nsub = pl.nsub;
+    const int64_t u_begin = ((int64_t)c * pl.total) / P, u_end = ((int64_t)(c + 1) * pl.total) / P;
+    float* wreg = smem + warp * SKS_WARP_FLOATS;
+
+    for (int64_t u0 = u_begin; u0 < u_end;) {
+        const int64_t item = u0 / nsub;
+        const int sub0 = (int)(u0 - item * nsub);
+        const int sub1 = (int)((u_end - item * nsub) < nsub ? (u_end - item * nsub) : nsub);     // this CTA's slices [sub0, sub1) of the item
+        const int tile = (int)(item % pl.tiles);
+        const int64_t b = item / pl.tiles;
+        const int tm = tile / pl.tiles_n, tn = tile % pl.tiles_n;
+        const float* Bg = B + b * (int64_t)K * N;
+        const int64_t a_row0 = (b * M + (int64_t)tm * 32) * K;          // element index of A[b][tm * 32][0]
+        const int nmine = (sub1 - sub0 - warp + SKS_WARPS - 1) / SKS_WARPS;
+
+        // per-lane copy plan of an A tile: chunk idx = lane + 32 n -> (row, chunk in row)
+        int a_sh[2][2];                                                  // shift of rows 16 i + g and 16 i + g + 8
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) a_sh[i][h] = (int)((a_row0 + (int64_t)(16 * i + g + 8 * h) * K) & 3);
+
+        auto load = [&](int it, int stage) {
+            const int k0 = (sub0 + warp + it * SKS_WARPS) * 32;
+            float* as = wreg + stage * SKS_STAGE;
+            float* bs = as + 32 * SKS_AP;
+#pragma unroll
+            for (int n = 0; n < 9; ++n) {
+                const int idx = lane + 32 * n, row = idx / 9, ch = idx - 9 * row;
+                const int m = tm * 32 + row;
+                const int64_t e = a_row0 + (int64_t)row * K + k0;        // element index of the first wanted element
+                const int64_t start = (e & ~(int64_t)3) + 4 * ch;
+                int64_t valid = (m < M) ? (a_row0 + (int64_t)row * K + K - start) : 0;   // elements up to the end of the row
+                valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(as + row * SKS_AP + 4 * ch)),
+                             "l"(valid > 0 ? A + start : A), "r"((int)valid * 4) : "memory");
+            }
+            {
+                const int r4 = lane >> 3, c4 = (lane & 7) * 4;
+                const int n = tn * 32 + c4;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int k = k0 + i * 4 + r4;
+                    const bool ok = k < K && n < N;                      // N % 4 == 0: a chunk is all inside or all outside
+                    cp_async_zfill<16>(bs + (i * 4 + r4) * SKS_BP + c4, Bg + (int64_t)(ok ? k : 0) * N + (ok ? n : 0), ok);
+                }
+            }
+            cp_async_commit();
+        };
+
+        // Two levels of accumulation: the tensor cores add into `acc` for eight slices (96 MMAs per element), then `acc` is
+        // added to `tot` with ordinary fp32 additions.  The accumulate step of an MMA truncates, so the error of one long
+        // chain grows with its length; short chains keep sums of 10^4 .. 10^5 cancelling terms at fp32 accuracy.
+        float acc[2][4][4], tot[2][4][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { acc[i][j][q] = 0.0f; tot[i][j][q] = 0.0f; }
+
+        if (nmine > 0) load(0, 0);
+        if (nmine > 1) load(1, 1);
+        for (int it = 0; it < nmine; ++it) {
+            if ((it & 7) == 0 && it > 0) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) { tot[i][j][q] += acc[i][j][q]; acc[i][j][q] = 0.0f; }
+            }
+            if (it + 2 < nmine) { load(it + 2, (it + 2) % SKS_STAGES); cp_async_wait<2>(); }
+            else if (it + 1 < nmine) cp_async_wait<1>();
+            else cp_async_wait<0>();
+            __syncwarp();
+            const float* as = wreg + (it % SKS_STAGES) * SKS_STAGE;
+            const float* bs = as + 32 * SKS_AP;
+#pragma unroll
+            for (int k8 = 0; k8 < 4; ++k8) {
+                const int kk = k8 * 8 + t;
+                uint32_t ahi[2][4], alo[2][4];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const float* p0 = as + (16 * i + g) * SKS_AP + kk + a_sh[i][0];
+                    const float* p1 = as + (16 * i + g + 8) * SKS_AP + kk + a_sh[i][1];
+                    split_tf32(p0[0], ahi[i][0], alo[i][0]);
+                    split_tf32(p1[0], ahi[i][1], alo[i][1]);
+                    split_tf32(p0[4], ahi[i][2], alo[i][2]);
+                    split_tf32(p1[4], ahi[i][3], alo[i][3]);
+                }
+                uint32_t bhi[4][2], blo[4][2];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float* p = bs + kk * SKS_BP + 8 * j + g;
+                    split_tf32(p[0], bhi[j][0], blo[j][0]);
+                    split_tf32(p[4 * SKS_BP], bhi[j][1], blo[j][1]);
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], alo[i], bhi[j]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ahi[i], blo[j]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ahi[i], bhi[j]);
+            }
+            __syncwarp();
+        }
+        // warp partial -> shared [32][32] (all copies of this warp have landed and been read), CTA sum in warp order
+        float* tw = wreg;
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r0 = 16 * i + g, c0 = 8 * j + 2 * t;
+                tw[r0 * 32 + c0] = tot[i][j][0] + acc[i][j][0];
+                tw[r0 * 32 + c0 + 1] = tot[i][j][1] + acc[i][j][1];
+                tw[(r0 + 8) * 32 + c0] = tot[i][j][2] + acc[i][j][2];
+                tw[(r0 + 8) * 32 + c0 + 1] = tot[i][j][3] + acc[i][j][3];
+            }
+        __syncthreads();
+        const bool whole = sub0 == 0 && sub1 == nsub;                    // the item lies inside this CTA
+        const int c_first = sks_owner(item * nsub, pl.total, P), c_last = sks_owner((item + 1) * nsub - 1, pl.total, P);
+        float* piece = pieces + ((int64_t)2 * c + (c == c_first ? 1 : 0)) * 1024;
+        float* Cb = C + b * (int64_t)M * N;
+        for (int e = threadIdx.x; e < 1024; e += SKS_WARPS * 32) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < SKS_WARPS; ++w) sum += smem[w * SKS_WARP_FLOATS + e];
+            if (whole) {
+                const int m = tm * 32 + e / 32, n = tn * 32 + e % 32;
+                if (m < M && n < N) Cb[(int64_t)m * N + n] = alpha * sum;
+            } else {
+                __stcg(piece + e, sum);
+            }
+        }
+        if (!whole) {
+            __threadfence();                                             // this thread's piece elements are visible device-wide
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const unsigned int ticket = atomicAdd(tickets + c_first, 1u);
+                s_last = (ticket == (unsigned int)(c_last - c_first)) ? 1 : 0;
+            }
+            __syncthreads();
+            if (s_last) {                                                // every piece of the item has been written
+                __threadfence();
+                for (int e = threadIdx.x; e < 1024; e += SKS_WARPS * 32) {
+                    float sum = 0.0f;
+                    for (int cc = c_first; cc <= c_last; ++cc)
+                        sum += __ldcg(pieces + ((int64_t)2 * cc + (cc == c_first ? 1 : 0)) * 1024 + e);
+                    const int m = tm * 32 + e / 32, n = tn * 32 + e % 32;
+                    if (m < M && n < N) Cb[(int64_t)m * N + n] = alpha * sum;
+                }
+                if (threadIdx.x == 0) tickets[c_first] = 0u;             // ready for the next call
+            }
+        }
+        __syncthreads();                                                 // the warp regions are reused by the next item
+        u0 = item * nsub + sub1;
+    }
+}
+
 static SmemOptIn g_skinny_smem;           // shared-memory opt-in of skinny_splitk_kernel, per device
 static int g_attn_cluster_override = 0;   // 0 = heuristic; set through spgt_set_tuning("attn_cluster", n)
 static int g_attn_impl = 0;               // 0 = tcgen05 kernel (attention_tc.cu, default), 1 = warp-MMA kernel of this file
@@ -463,6 +660,8 @@ static int g_attn_impl = 0;               // 0 = tcgen05 kernel (attention_tc.cu
 // defined in attention_tc.cu
 int launch_attn_tc(const float* Q, const float* K, const float* V, float* out, float* t_out, int64_t BH, int H, int dpk,
                    int S, int merged, int cluster, cudaStream_t stream);
+
+void spectral_set_chunk_mb(int mb);       // spectral.cu
 
 }  // namespace spgt
 
@@ -539,10 +738,56 @@ static int skinny_splits(int M, int N, int K, int batch) {
     return (int)s;
 }
 
-extern "C" size_t spgt_skinny_gemm_workspace_bytes(int M, int N, int K, int batch) {
-    if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+// Scratch of the two-pass kernels: one partial tile per (batch, tile, split).
+static size_t skinny_twopass_bytes(int M, int N, int K, int batch) {
     const size_t tiles = (size_t)ceil_div(M, 32) * ceil_div(N, 32);
     return tiles * (size_t)batch * (size_t)skinny_splits(M, N, K, batch) * 1024 * sizeof(float);
+}
+// The one-launch kernel takes the shapes its 16-byte B chunks allow; its plan: P persistent CTAs over the k slices of all items.
+static bool skinny_streamk_ok(int N) { return N % 4 == 0; }
+static SksPlan skinny_plan(int M, int N, int K, int batch) {
+    SksPlan pl;
+    pl.tiles_n = ceil_div(N, 32); pl.tiles = ceil_div(M, 32) * pl.tiles_n; pl.nsub = ceil_div(K, 32);
+    pl.total = (int64_t)batch * pl.tiles * pl.nsub;
+    const int64_t want = ceil_div(pl.total, (int64_t)(2 * SKS_WARPS));      // at least two slices per warp
+    pl.P = (int)(want < num_sms() ? (want < 1 ? 1 : want) : num_sms());
+    return pl;
+}
+// layout: pieces [2 P][1024] floats, then P tickets
+static size_t skinny_streamk_bytes(const SksPlan& pl) { return (size_t)pl.P * (2 * 1024 * sizeof(float) + sizeof(unsigned int)); }
+
+extern "C" size_t spgt_skinny_gemm_workspace_bytes(int M, int N, int K, int batch) {
+    if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+    if (skinny_streamk_ok(N)) return skinny_streamk_bytes(skinny_plan(M, N, K, batch));
+    return skinny_twopass_bytes(M, N, K, batch);
+}
+
+// Both entry points below run the same kernels on a scratch area: the one-launch kernel where the shape allows it,
+// the two-pass kernels otherwise.  `scratch` holds at least spgt_skinny_gemm_workspace_bytes(M, N, K, batch) bytes.
+static int skinny_launch(const float* A, const float* B, float* C, float alpha, int M, int N, int K, int batch, void* scratch,
+                         cudaStream_t st) {
+    if (skinny_streamk_ok(N)) {
+        const SksPlan pl = skinny_plan(M, N, K, batch);
+        static SmemOptIn configured;
+        if (int e = smem_opt_in(skinny_streamk_kernel, SKS_SMEM, configured)) return e;
+        float* pieces = (float*)scratch;
+        unsigned int* tickets = (unsigned int*)(pieces + (size_t)pl.P * 2 * 1024);
+        // The tickets count the finished pieces of an item and must start at zero.  The kernel leaves them at zero, but a
+        // fresh workspace holds anything, so they are cleared on the stream before every launch (a few hundred bytes).
+        if (cudaMemsetAsync(tickets, 0, (size_t)pl.P * sizeof(unsigned int), st) != cudaSuccess) return launch_status();
+        skinny_streamk_kernel<<<pl.P, SKS_WARPS * 32, SKS_SMEM, st>>>(A, B, C, alpha, M, N, K, pl, pieces, tickets);
+        return launch_status();
+    }
+    const int tiles_n = ceil_div(N, 32), tiles = ceil_div(M, 32) * tiles_n;
+    const int splits = skinny_splits(M, N, K, batch);
+    const int64_t blocks = (int64_t)tiles * splits * batch;
+    if (blocks > 0x7fffffffLL) return SPGT_ERR_SHAPE;
+    const size_t smem = (size_t)SK_WARPS * SK_WARP_FLOATS * sizeof(float);
+    if (int e = smem_opt_in(skinny_splitk_kernel, smem, g_skinny_smem)) return e;
+    skinny_splitk_kernel<<<(unsigned)blocks, SK_WARPS * 32, smem, st>>>(A, B, (float*)scratch, M, N, K, tiles_n, tiles, splits, 0);
+    if (int e = launch_status()) return e;
+    skinny_reduce_kernel<<<(unsigned)((int64_t)tiles * batch), 256, 0, st>>>((const float*)scratch, C, alpha, M, N, tiles_n, tiles, splits);
+    return launch_status();
 }
 
 extern "C" int spgt_batched_skinny_gemm(const float* A, const float* B, float* C, float alpha, int M, int N, int K,
@@ -553,20 +798,7 @@ extern "C" int spgt_batched_skinny_gemm(const float* A, const float* B, float* C
     const size_t need = spgt_skinny_gemm_workspace_bytes(M, N, K, batch);
     if (!workspace || workspace_bytes < need) return SPGT_ERR_WORKSPACE;
     if (!aligned16(workspace)) return SPGT_ERR_ALIGN;
-    const int tiles_n = ceil_div(N, 32), tiles = ceil_div(M, 32) * tiles_n;
-    const int splits = skinny_splits(M, N, K, batch);
-    const int64_t blocks = (int64_t)tiles * splits * batch;
-    if (blocks > 0x7fffffffLL) return SPGT_ERR_SHAPE;
-    const size_t smem = (size_t)SK_WARPS * SK_WARP_FLOATS * sizeof(float);
-    if (int e = smem_opt_in(skinny_splitk_kernel, smem, g_skinny_smem)) return e;
-    cudaStream_t st = (cudaStream_t)stream;
-    const int vecB = (N % 4 == 0) ? 1 : 0;
-    skinny_splitk_kernel<<<(unsigned)blocks, SK_WARPS * 32, smem, st>>>(A, B, (float*)workspace, M, N, K, tiles_n, tiles,
-                                                                     splits, vecB);
-    if (int e = launch_status()) return e;
-    skinny_reduce_kernel<<<(unsigned)((int64_t)tiles * batch), 256, 0, st>>>((const float*)workspace, C, alpha, M, N,
-                                                                             tiles_n, tiles, splits);
-    return launch_status();
+    return skinny_launch(A, B, C, alpha, M, N, K, batch, workspace, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -576,19 +808,22 @@ extern "C" int spgt_batched_skinny_gemm(const float* A, const float* B, float* C
 // pool it does not own often has no way to obtain device memory at call time (its allocator may take a lock, may
 // synchronise the device, or may simply be out of reach from the calling layer), and no place to keep a buffer
 // between calls.  spgt_batched_skinny_gemm() asks such a caller for a workspace it cannot provide.  The entry
-// point below has the same arithmetic, but takes its split-K partial tiles from a fixed array that is part of
-// the loaded library image on every device.  It never calls cudaMalloc, cudaFree or any other allocating routine.
+// point below runs the same kernels on the same plan - so its result is bit-identical - but takes the scratch
+// (the partial tiles of the split k range and the tickets that count them) from a fixed array that is part of the
+// loaded library image on every device.  It never calls cudaMalloc, cudaFree or any other allocating routine.
 //
-// Limit: the partial tiles must fit SPGT_SKINNY_NOALLOC_BYTES (8 MiB).  Larger problems are refused with
+// Limit: the scratch must fit SPGT_SKINNY_NOALLOC_BYTES (8 MiB).  Larger problems are refused with
 // SPGT_ERR_TOO_LARGE; nothing is launched in that case.  spgt_skinny_gemm_workspace_bytes() gives the size a
 // problem needs, spgt_skinny_gemm_noalloc_max_bytes() the limit.
 //
 // Set-up: the first call on a device (with that device current) looks up the device address of the array once
-// and caches it.  That lookup is a runtime query, so make one call on every device you use before you start
-// capturing a stream; later calls only launch the two kernels.
+// and caches it, and opts the kernels in to their shared-memory size.  Those are runtime queries - with lazy module
+// loading that first call may also be what loads the module that holds the array - so make one call on every
+// device you use before you start capturing a stream; later calls only clear the tickets and launch.
 //
-// Initial contents: nothing has to start at zero.  Pass 1 writes every element of every partial tile that pass 2
-// reads, in the same call, so stale contents of an earlier call are never observed and no clearing kernel runs.
+// Initial contents: every call shares the array and finds what the last call left.  The partial tiles need no
+// clearing: each call writes every element of every tile it later reads.  The tickets must start at zero and are
+// cleared on the stream (cudaMemsetAsync, no allocation) before each launch.
 //
 // Concurrency: there is one array per device.  Two calls whose kernels can overlap on the same device (different
 // streams, or different host threads on different streams) would write the same partial tiles and race; issue
@@ -597,8 +832,7 @@ extern "C" int spgt_batched_skinny_gemm(const float* A, const float* B, float* C
 constexpr size_t SKINNY_NOALLOC_FLOATS = (size_t)2 * 1024 * 1024;                 // 8 MiB
 static __device__ __align__(256) float g_skinny_noalloc_scratch[SKINNY_NOALLOC_FLOATS];
 
-constexpr int SKINNY_MAX_DEVICES = 64;
-static float* g_skinny_noalloc_ptr[SKINNY_MAX_DEVICES] = {};   // device address of the array, per device; 0 = not looked up
+static float* g_skinny_noalloc_ptr[SPGT_MAX_DEVICES] = {};   // device address of the array, per device; 0 = not looked up
 
 extern "C" size_t spgt_skinny_gemm_noalloc_max_bytes(void) { return SKINNY_NOALLOC_FLOATS * sizeof(float); }
 
@@ -607,30 +841,18 @@ extern "C" int spgt_batched_skinny_gemm_noalloc(const float* A, const float* B, 
     if (!A || !B || !C) return SPGT_ERR_NULL;
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return SPGT_ERR_SHAPE;
     if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return SPGT_ERR_ALIGN;
-    const int tiles_n = ceil_div(N, 32), tiles = ceil_div(M, 32) * tiles_n;
-    const int splits = skinny_splits(M, N, K, batch);
-    const int64_t blocks = (int64_t)tiles * splits * batch;
-    if (blocks > 0x7fffffffLL) return SPGT_ERR_SHAPE;
-    if ((size_t)blocks * 1024 > SKINNY_NOALLOC_FLOATS) return SPGT_ERR_TOO_LARGE;
+    if (spgt_skinny_gemm_workspace_bytes(M, N, K, batch) > SKINNY_NOALLOC_FLOATS * sizeof(float)) return SPGT_ERR_TOO_LARGE;
 
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess) return launch_status();
-    if (dev < 0 || dev >= SKINNY_MAX_DEVICES) return SPGT_ERR_SHAPE;
+    if (dev < 0 || dev >= SPGT_MAX_DEVICES) return SPGT_ERR_SHAPE;
     float* scratch = g_skinny_noalloc_ptr[dev];
-    const size_t smem = (size_t)SK_WARPS * SK_WARP_FLOATS * sizeof(float);
-    if (!scratch) {   // once per device: address of this device's copy of the array, and the kernel's shared-memory opt-in
+    if (!scratch) {   // once per device: the address of this device's copy of the array
         cudaError_t e = cudaGetSymbolAddress((void**)&scratch, g_skinny_noalloc_scratch);
         if (e != cudaSuccess || !scratch) { g_last_cuda_error = (int)e; (void)cudaGetLastError(); return SPGT_ERR_LAUNCH; }
-        e = cudaFuncSetAttribute(skinny_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { g_last_cuda_error = (int)e; (void)cudaGetLastError(); return SPGT_ERR_LAUNCH; }
         g_skinny_noalloc_ptr[dev] = scratch;
     }
-    cudaStream_t st = (cudaStream_t)stream;
-    const int vecB = (N % 4 == 0) ? 1 : 0;
-    skinny_splitk_kernel<<<(unsigned)blocks, SK_WARPS * 32, smem, st>>>(A, B, scratch, M, N, K, tiles_n, tiles, splits, vecB);
-    if (int e = launch_status()) return e;
-    skinny_reduce_kernel<<<(unsigned)((int64_t)tiles * batch), 256, 0, st>>>(scratch, C, alpha, M, N, tiles_n, tiles, splits);
-    return launch_status();
+    return skinny_launch(A, B, C, alpha, M, N, K, batch, scratch, (cudaStream_t)stream);
 }
 
 extern "C" int spgt_set_tuning(const char* key, int value) {
@@ -639,6 +861,11 @@ extern "C" int spgt_set_tuning(const char* key, int value) {
     if (eq("attn_cluster")) {
         if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return SPGT_ERR_SHAPE;
         g_attn_cluster_override = value;
+        return SPGT_OK;
+    }
+    if (eq("spectral_chunk_mb")) {
+        if (value < 0 || value > 65536) return SPGT_ERR_SHAPE;
+        spectral_set_chunk_mb(value);
         return SPGT_OK;
     }
     if (eq("attn_impl")) {

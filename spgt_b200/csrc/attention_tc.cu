@@ -33,6 +33,7 @@ __device__ int g_attn_status = 0;
 constexpr int AT_THREADS = 320;                 // warps 0-3 loaders, 4-7 converters, 8-9 MMA issuers
 constexpr int AT_NP = 48;                       // N (and B-tile rows) padded to a multiple of 16
 constexpr int AT_SUB = 32;                      // columns per phase-A stage
+constexpr int AT_FLUSH = 16;                    // sub-tiles whose products one tensor-memory accumulator sums before it is flushed
 constexpr int AT_NR = 7;                        // raw K / V stages
 constexpr int AT_RROWS = 36;                    // rows allocated per raw matrix (dpk <= 35)
 constexpr int AT_RP = 36;                       // floats per raw row: 32 wanted + up to 3 of shift, in 16-byte chunks
@@ -83,6 +84,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
     auto a2_empty = [&](int s) { return bars + 8u * (21 + s); };     // [2] MMA commit -> Q producers
     auto d_full = [&](int b) { return bars + 8u * (23 + b); };       // [2] MMA commit -> epilogue
     auto d_empty = [&](int b) { return bars + 8u * (25 + b); };      // [2] epilogue -> MMA
+    const uint32_t acc_free = bars + 8u * 27;                        //     T flush done -> MMA issuers
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 256);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 264);
 
@@ -105,6 +107,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         for (int s = 0; s < AT_NR; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
         for (int s = 0; s < 2; ++s) { mbar_init(op_full(s), 128); mbar_init(op_empty(s), 2); }
         mbar_init(t_done, 2);
+        mbar_init(acc_free, D > 32 ? 64 : 32);
         for (int s = 0; s < 2; ++s) { mbar_init(a2_full(s), 128); mbar_init(a2_empty(s), 1); mbar_init(d_full(s), 1); mbar_init(d_empty(s), 128); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -114,6 +117,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid < AT_RROWS) sh_tab[tid] = tid < D ? ((sh_bh + tid * S) & 3) : 0;
+    for (int i = tid; i < AT_TP * AT_TP; i += AT_THREADS) Tc[i] = 0.0f;
     for (int i = tid; i < 4 * AT_TILE / 16; i += AT_THREADS)            // rows of the V tiles beyond dpk are never written: keep them finite
         reinterpret_cast<uint4*>(opr)[i] = make_uint4(0u, 0u, 0u, 0u);
     tc_fence_before();
@@ -172,6 +176,26 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         for (int it = 0; it < nmine; ++it) {
             const uint32_t st = (uint32_t)(it % AT_NR), ph = (uint32_t)((it / AT_NR) & 1);
             const uint32_t so = (uint32_t)(it & 1), po = (uint32_t)((it >> 1) & 1);
+            if (k_warp && it > 0 && it % AT_FLUSH == 0) {
+                // The accumulate step of an MMA truncates, so the error of one long chain grows with its length (worst for
+                // the all-positive position rows).  Every AT_FLUSH sub-tiles the two accumulators are added to the fp32
+                // partial sum in shared memory with ordinary additions and the issuers start a new chain.
+                if (!mbar_wait(t_done, (uint32_t)((it / AT_FLUSH - 1) & 1), abort_flag, 4, &g_attn_status)) break;
+                tc_fence_after();
+#pragma unroll 1
+                for (int a = 0; a < 2; ++a) {                        // the two issuers' accumulators, one after the other
+                    float v[32], w[16];
+                    tc_ld32(tmem_base + lane_addr + a * AT_NP, v);
+                    tc_ld16(tmem_base + lane_addr + a * AT_NP + 32, w);
+                    if (a == 1) { tc_fence_before(); mbar_arrive(acc_free); }
+                    if (krow < D) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (j < D) Tc[krow * AT_TP + j] += v[j];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (32 + j < D) Tc[krow * AT_TP + 32 + j] += w[j];
+                    }
+                }
+            }
             if (!mbar_wait(raw_full(st), ph, abort_flag, 2, &g_attn_status)) break;
             if (!mbar_wait(op_empty(so), po ^ 1, abort_flag, 9, &g_attn_status)) break;    // MMAs two sub-tiles back are done
             const float* kraw = reinterpret_cast<const float*>(smem + st * AT_RAW_STAGE);
@@ -217,6 +241,8 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         const uint32_t d = tmem_base + (uint32_t)(iw * AT_NP);
         for (int it = 0; it < nmine; ++it) {
             const uint32_t so = (uint32_t)(it & 1), po = (uint32_t)((it >> 1) & 1);
+            if (it > 0 && it % AT_FLUSH == 0 &&
+                !mbar_wait(acc_free, (uint32_t)((it / AT_FLUSH - 1) & 1), abort_flag, 10, &g_attn_status)) break;   // the flushed accumulator has been read
             if (!mbar_wait(op_full(so), po, abort_flag, 3, &g_attn_status)) break;
             tc_fence_after();
             if (lane == 0) {
@@ -227,12 +253,12 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                     const int k8 = 2 * iw + kk;
                     const uint32_t ah = tmem_base + AT_A1_COL + so * 64 + k8 * 8, al = ah + 32;
                     const uint64_t adv = (uint64_t)(k8 * 2);
-                    tc_mma_tf32_ts(d, al, dbh + adv, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_tf32_ts(d, al, dbh + adv, idesc, (it % AT_FLUSH != 0 || kk > 0) ? 1u : 0u);
                     tc_mma_tf32_ts(d, ah, dbl + adv, idesc, 1u);
                     tc_mma_tf32_ts(d, ah, dbh + adv, idesc, 1u);
                 }
                 tc_commit(op_empty(so));
-                if (it == nmine - 1) tc_commit(t_done);
+                if (it == nmine - 1 || (it + 1) % AT_FLUSH == 0) tc_commit(t_done);
             }
             __syncwarp();
         }
@@ -244,7 +270,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         if (q * 32 < D) {                                               // warps that hold valid rows of T
             float v[32], w[16];
             bool have = false;
-            if (nmine > 0) have = mbar_wait(t_done, 0, abort_flag, 4, &g_attn_status);
+            if (nmine > 0) have = mbar_wait(t_done, (uint32_t)(((nmine - 1) / AT_FLUSH) & 1), abort_flag, 4, &g_attn_status);
             tc_fence_after();
             if (have) {
                 float v2[32], w2[16];
@@ -260,9 +286,9 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             const int row = q * 32 + lane;
             if (row < D) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) if (j < D) Tc[row * AT_TP + j] = have ? v[j] : 0.0f;
+                for (int j = 0; j < 32; ++j) if (j < D && have) Tc[row * AT_TP + j] += v[j];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) if (32 + j < D) Tc[row * AT_TP + 32 + j] = have ? w[j] : 0.0f;
+                for (int j = 0; j < 16; ++j) if (32 + j < D && have) Tc[row * AT_TP + 32 + j] += w[j];
             }
         }
     }

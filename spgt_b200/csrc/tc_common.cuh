@@ -148,6 +148,16 @@ __host__ __device__ constexpr uint32_t tc_idesc(int bn) {
 }
 // byte offset of 16-byte chunk `c` (0..7) of row `r` inside a swizzled tile
 __host__ __device__ __forceinline__ uint32_t tc_swz(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
+// One element of a W stage image: the stage holds W_hi then W_lo, each [bn rows (n)][32 k] K-major with the 128-byte
+// swizzle; v = W[k][n], kk = k % 32.  W_lo is rounded to tf32 (the tensor core would truncate it).
+__device__ __forceinline__ void tc_img_store(float* stage, int bn, int n, int kk, float v) {
+    uint32_t h, l, l2;
+    split_tf32(v, h, l);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l2) : "f"(__uint_as_float(l)));
+    const int off = (int)(tc_swz(n, kk >> 2) >> 2) + (kk & 3);
+    stage[off] = __uint_as_float(h);
+    stage[bn * TC_BK + off] = __uint_as_float(l2);
+}
 // Store 8 consecutive 32-bit columns of this thread's TMEM lane.
 __device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&u)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"

@@ -49,8 +49,28 @@ struct TcRing {
 
 // ---- A-operand loaders.  A loader thread copies 16-byte chunk (t & 7) of rows (t >> 3) + 16 i of every tile:
 // per-row state is computed once per work unit, per-k-block state once per k-block.
-struct TcDense {
+// Every loader also says where a work unit's W stages come from (w_src; W_PER_UNIT = true: another image per unit, W is
+// then streamed and never resident), which output row a GEMM row is stored to (out_row; -1 = padding row, not stored), and
+// whether the splitter threads read a row of the raw tile each (the tile rows are the GEMM rows) or a column each
+// (COLUMN_SPLIT: the tile holds A transposed, 32 k-values as its rows).
+// Ring depths, 0 = the default of the tile shape: RAW_STAGES raw A stages and W_STAGES W stages in shared memory, A_STAGES A
+// stages in tensor memory.  STAGING = false: the epilogue needs no shared-memory staging rows.  CONST_A: the A operand of
+// the LAST k-block is the same for every work unit and stays in tensor memory (the loader's const_row() gives its rows);
+// REVERSE_UNITS: work units are taken from the last to the first.
+// W_CONVERT: the W stage of the last k-block is not copied from a prepared image but split and laid out by the W-loader
+// warp from a plain [w_plain_rows()][32] fp32 block per unit (w_plain(unit)), so the producer of that block can store it
+// coalesced and it takes no more memory than its values.  ACC_BUFS: accumulator buffers (0 = default of the tile shape).
+struct TcLoaderDefaults {
+    static constexpr bool W_PER_UNIT = false, COLUMN_SPLIT = false, STAGING = true, CONST_A = false, REVERSE_UNITS = false, W_CONVERT = false;
+    static constexpr int RAW_STAGES = 0, W_STAGES = 0, A_STAGES = 0, ACC_BUFS = 0;
+    __device__ __forceinline__ const float* const_row(int) const { return nullptr; }
+    __device__ __forceinline__ const float* w_plain(int) const { return nullptr; }
+    __device__ __forceinline__ int w_plain_rows() const { return 0; }
+};
+struct TcDense : TcLoaderDefaults {
     const float* x; int lda; int rows; int K;
+    __device__ __forceinline__ const float* w_src(const float* wtile, int, int kb, int stage_floats) const { return wtile + (int64_t)kb * stage_floats; }
+    __device__ __forceinline__ int64_t out_row(int row) const { return row < rows ? row : -1; }
     struct Row { const float* p; bool ok; };
     struct Kst { int kc; bool ok; };
     __device__ __forceinline__ Row row_state(int row) const {
@@ -61,8 +81,10 @@ struct TcDense {
     }
     __device__ __forceinline__ const float* ptr(const Row& r, const Kst& k, bool& ok) const { ok = r.ok && k.ok; return r.p + k.kc; }
 };
-struct TcConv {          // 3x3, padding 1, NHWC; k = tap * Cin + c with Cin % 4 == 0
+struct TcConv : TcLoaderDefaults {          // 3x3, padding 1, NHWC; k = tap * Cin + c with Cin % 4 == 0
     const float* x; int cin_pitch, cin_off, Cin, Hh, Ww; int rows; int K;
+    __device__ __forceinline__ const float* w_src(const float* wtile, int, int kb, int stage_floats) const { return wtile + (int64_t)kb * stage_floats; }
+    __device__ __forceinline__ int64_t out_row(int row) const { return row < rows ? row : -1; }
     struct Row { const float* p; uint32_t mask; };     // bit tap of mask: the tap's source pixel lies inside the image
     struct Kst { int off; int tap; };
     __device__ __forceinline__ Row row_state(int row) const {
@@ -95,6 +117,93 @@ struct TcConv {          // 3x3, padding 1, NHWC; k = tap * Cin + c with Cin % 4
     }
 };
 
+// Spectral layer, inverse transform along y plus the residual linear layer, as one GEMM per image row (b, x):
+//   out[y][o] = sum_i X[y][i] Wr[i][o] + sum_j F3[y][j] P[j][o]            K = 32 channels + 32 (the 2m <= 32 kept modes, zero padded)
+// The GEMM rows of an image row are padded to `upr` units of 256 (two 128-row tiles): GEMM row R lies in unit u = R / 256,
+// image row u / upr, y = (u % upr) * 256 + R % 256.  k-block 0 takes its A rows from X and its W stage from the prepared
+// image of Wr; k-block 1 takes its A rows from the F3 table ([upr * 256][32], zero beyond r and beyond 2m) and its W
+// stage from the image of the row's P block, which the x-transform kernel writes in the W stage layout.
+struct TcSpecInv : TcLoaderDefaults {
+    static constexpr bool W_PER_UNIT = true;
+    const float* x; const float* f3; const float* wr_img; const float* p_img; int r, upr; int rows; int K;
+    __device__ __forceinline__ const float* w_src(const float*, int unit, int kb, int stage_floats) const {
+        return kb == 0 ? wr_img : p_img + (int64_t)(unit / upr) * stage_floats;
+    }
+    __device__ __forceinline__ int64_t out_row(int row) const {
+        const int u = row >> 8, img = u / upr, y = (u - img * upr) * 256 + (row & 255);
+        return (row < rows && y < r) ? (int64_t)img * r + y : -1;
+    }
+    struct Row { const float* px; const float* pf; bool ok; };
+    struct Kst { int kb; int c4; };
+    __device__ __forceinline__ Row row_state(int row) const {
+        const int u = row >> 8, img = u / upr, y = (u - img * upr) * 256 + (row & 255);
+        Row s; s.ok = row < rows && y < r;
+        s.px = s.ok ? x + ((int64_t)img * r + y) * 32 : x;
+        s.pf = f3 + (int64_t)y * 32;
+        return s;
+    }
+    __device__ __forceinline__ Kst k_state(int kb, int chunk) const { Kst k; k.kb = kb; k.c4 = chunk * 4; return k; }
+    __device__ __forceinline__ const float* ptr(const Row& s, const Kst& k, bool& ok) const {
+        if (k.kb == 0) { ok = s.ok; return s.px + k.c4; }
+        ok = true; return s.pf + k.c4;
+    }
+};
+// The same for r <= 256 (one unit per image row): the F3 rows are the same for every image row, so they are split once
+// and kept in tensor memory as the A operand of k-block 1; only X passes through the raw ring (four stages of 32 KB).
+// The row's P block arrives as plain fp32 [J][32] and is laid out by the W-loader warp.  Tensor memory holds two
+// accumulator buffers, one A stage and the constant block (measured: 222 us for 64 x 211 image rows against 281 us with one
+// accumulator buffer and two A stages).  Image rows are taken from the last to the first: the ones the forward transform
+// read last are the ones still in L2.
+struct TcSpecInvC : TcLoaderDefaults {
+    static constexpr bool W_PER_UNIT = true, CONST_A = true, REVERSE_UNITS = true, W_CONVERT = true;
+    static constexpr int RAW_STAGES = 4, W_STAGES = 4, A_STAGES = 1;
+    const float* x; const float* f3; const float* wr_img; const float* p; int J; int r; int rows; int K;
+    __device__ __forceinline__ const float* w_src(const float*, int, int, int) const { return wr_img; }
+    __device__ __forceinline__ const float* w_plain(int unit) const { return p + (int64_t)unit * J * 32; }
+    __device__ __forceinline__ int w_plain_rows() const { return J; }
+    __device__ __forceinline__ int64_t out_row(int row) const {
+        const int y = row & 255;
+        return (row < rows && y < r) ? (int64_t)(row >> 8) * r + y : -1;
+    }
+    __device__ __forceinline__ const float* const_row(int row_in_unit) const { return f3 + (int64_t)row_in_unit * 32; }
+    struct Row { const float* px; bool ok; };
+    struct Kst { int c4; };
+    __device__ __forceinline__ Row row_state(int row) const {
+        const int y = row & 255;
+        Row s; s.ok = row < rows && y < r;
+        s.px = s.ok ? x + ((int64_t)(row >> 8) * r + y) * 32 : x;
+        return s;
+    }
+    __device__ __forceinline__ Kst k_state(int, int chunk) const { Kst k; k.c4 = chunk * 4; return k; }
+    __device__ __forceinline__ const float* ptr(const Row& s, const Kst& k, bool& ok) const { ok = s.ok; return s.px + k.c4; }
+};
+// Spectral layer, forward transform along y: Y1[x][j][c] = sum_y F1[j][y] X[x][y][c] as the GEMM D[(x, c)][j] with
+// A[(x, c)][k = y] = X[x][y][c].  A is stored transposed in memory (c contiguous), so a raw tile holds, for four image rows,
+// 32 consecutive y as its rows (tile row = x_local * 32 + y_local, 32 channels each) and splitter thread (x_local, c)
+// reads column c of the 32 tile rows of its image row.  W is the prepared image of F1^T ([y][j]).
+struct TcSpecFwd : TcLoaderDefaults {
+    // The kernel is bound by the bytes it keeps in flight: five raw stages of 32 KB; seven W stages keep the image of F1^T
+    // resident up to r = 224; the epilogue stores straight from registers.
+    static constexpr bool COLUMN_SPLIT = true, STAGING = false;
+    static constexpr int RAW_STAGES = 5, W_STAGES = 7;
+    const float* x; int r; int64_t nimg; int rows; int K;
+    __device__ __forceinline__ const float* w_src(const float* wtile, int, int kb, int stage_floats) const { return wtile + (int64_t)kb * stage_floats; }
+    __device__ __forceinline__ int64_t out_row(int row) const { return row < rows ? row : -1; }
+    struct Row { const float* p; int y; bool ok; };
+    struct Kst { int kb; int c4; };
+    __device__ __forceinline__ Row row_state(int row) const {
+        const int64_t img = (int64_t)(row >> 7) * 4 + ((row & 127) >> 5);
+        Row s; s.y = row & 31; s.ok = img < nimg;
+        s.p = x + ((s.ok ? img : 0) * r + s.y) * 32;
+        return s;
+    }
+    __device__ __forceinline__ Kst k_state(int kb, int chunk) const { Kst k; k.kb = kb; k.c4 = chunk * 4; return k; }
+    __device__ __forceinline__ const float* ptr(const Row& s, const Kst& k, bool& ok) const {
+        ok = s.ok && k.kb * TC_BK + s.y < r;
+        return ok ? s.p + (int64_t)k.kb * (TC_BK * 32) + k.c4 : x;
+    }
+};
+
 // ---- epilogue parameter blocks ------------------------------------------------------------------------------
 struct TcLinearEpi {
     const float* bias; const float* residual; int ldr; float* y; int ldc; int N; int act;
@@ -107,32 +216,37 @@ struct TcHeadEpi {
     const float* b1; const float* w2; float b2, scale, shift; const float* scale_map; const float* shift_map;
     int dirichlet, Hh, Ww, act; float* out;
 };
-enum { EPI_LINEAR = 0, EPI_PROJ = 1, EPI_HEAD = 2 };
+struct TcSpecFwdEpi { float* y1; int J; int64_t nimg; };     // Y1 [image row][J][32 channels]
+enum { EPI_LINEAR = 0, EPI_PROJ = 1, EPI_HEAD = 2, EPI_SPECF = 3 };
 
-template <int BN, int MT> struct TcCfg {
+template <int BN, int MT, class Loader = TcDense> struct TcCfg {
     // Column tiles of up to 64: W_hi and W_lo of a k-block lie one after the other in shared memory, so one MMA of
     // twice the width computes A_hi W_hi and A_hi W_lo side by side (two partial accumulators, summed by the epilogue)
     // and a k-step of 8 takes two MMA instructions instead of three; the issuing thread is what limits these tiles.
     static constexpr bool MERGE = BN <= 64;
     static constexpr int ACCW = MERGE ? 2 * BN : BN;                // accumulator columns of one row tile
-    static constexpr int NBUF = (MT == 1 || ACCW <= 64) ? 2 : 1;    // accumulator buffers
+    static constexpr int NBUF = Loader::ACC_BUFS ? Loader::ACC_BUFS : ((MT == 1 || ACCW <= 64) ? 2 : 1);    // accumulator buffers
     static constexpr int ACC_COLS = NBUF * MT * ACCW;
-    static constexpr int SA = (MT == 1) ? 4 : 2;                    // A stages in TMEM, 64 columns (hi|lo) per tile
-    static_assert(ACC_COLS + SA * MT * 64 <= 512, "tensor memory budget");
+    static constexpr int SA = Loader::A_STAGES ? Loader::A_STAGES : ((MT == 1) ? 4 : 2);   // A stages in TMEM, 64 columns (hi|lo) per tile
+    static constexpr int CONST_COLS = Loader::CONST_A ? MT * 64 : 0;                      // the constant A k-block (hi|lo per tile)
+    static_assert(ACC_COLS + SA * MT * 64 + CONST_COLS <= 512, "tensor memory budget");
     static constexpr int B_BYTES = 2 * BN * TC_BK * 4;              // W_hi | W_lo image of one k-block
-    static constexpr int SB = (BN == 128) ? (MT == 1 ? 4 : 3) : (MT == 1 ? 8 : 6);  // W stages in shared memory
+    static constexpr int SB = Loader::W_STAGES ? Loader::W_STAGES
+                                               : ((BN == 128) ? (MT == 1 ? 4 : 3) : ((MT == 1 || BN == 32) ? 8 : 6));  // W stages in shared memory
     static constexpr int RAW_BYTES = MT * TC_BM * TC_BK * 4;        // raw fp32 A tile(s) of one k-block
-    static constexpr int SR = (MT == 1) ? 3 : 2;                    // raw A stages in shared memory
-    static constexpr int STAGING_BYTES = 32 * TC_EPI_WARPS * TC_SLOT_BYTES;
+    static constexpr int SR = Loader::RAW_STAGES ? Loader::RAW_STAGES : ((MT == 1) ? 3 : 2);   // raw A stages in shared memory
+    static constexpr int STAGING_BYTES = Loader::STAGING ? 32 * TC_EPI_WARPS * TC_SLOT_BYTES : 0;
     static constexpr int CONST_BYTES = 2048;                        // per-CTA epilogue constants (bias, LayerNorm affine, head vectors)
     static constexpr int BAR_BYTES = 384;
-    static constexpr size_t BYTES = 1024 + (size_t)SB * B_BYTES + SR * RAW_BYTES + STAGING_BYTES + CONST_BYTES + BAR_BYTES;
+    static constexpr int PLAIN_BYTES = Loader::W_CONVERT ? 4 * 32 * 32 * 4 : 0;       // ring of plain W blocks (after the barriers)
+    static constexpr size_t BYTES = 1024 + (size_t)SB * B_BYTES + SR * RAW_BYTES + STAGING_BYTES + CONST_BYTES + BAR_BYTES + PLAIN_BYTES;
+    static_assert(BYTES <= 227 * 1024, "shared memory budget");
 };
 
 template <int BN, int MT, class Loader, int EPI, class EpiParams>
 __global__ void __launch_bounds__(tc_threads(MT), 1)
 tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_units, EpiParams ep) {
-    using C = TcCfg<BN, MT>;
+    using C = TcCfg<BN, MT, Loader>;
     constexpr int SA = C::SA, NBUF = C::NBUF, SR = C::SR;
     constexpr int SB = C::SB;
     constexpr uint32_t B_STAGE = C::B_BYTES;
@@ -153,15 +267,16 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     auto b_empty = [&](int s) { return bars + 8u * (16 + s); };         // [8]
     auto acc_full = [&](int b) { return bars + 8u * (24 + b); };        // [2]
     auto acc_empty = [&](int b) { return bars + 8u * (26 + b); };       // [2]
-    auto raw_full = [&](int s) { return bars + 8u * (28 + s); };        // [3]
-    auto raw_empty = [&](int s) { return bars + 8u * (31 + s); };       // [3]
-    static_assert(SA <= 4 && SB <= 8 && SR <= 3 && NBUF <= 2, "barrier slots");
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 288);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 296);
+    auto raw_full = [&](int s) { return bars + 8u * (28 + s); };        // [8]
+    auto raw_empty = [&](int s) { return bars + 8u * (36 + s); };       // [8]
+    static_assert(SA <= 4 && SB <= 8 && SR <= 8 && NBUF <= 2, "barrier slots");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 352);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 360);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int KB = kpad / TC_BK;
-    const bool resident = KB <= SB;          // the whole column tile of W stays in shared memory
+    const int KBA = Loader::CONST_A ? KB - 1 : KB;                   // k-blocks whose A operand passes through the rings
+    const bool resident = !Loader::W_PER_UNIT && KB <= SB;          // the whole column tile of W stays in shared memory
 
     if (tid == 0) {
         for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), NIWARPS); }
@@ -177,7 +292,9 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     }
     // Epilogue constants of this CTA's column tile go to shared memory once: a global load issued from the epilogue
     // queues behind the producers' traffic and costs microseconds of latency per use.
-    if constexpr (EPI == EPI_HEAD) {
+    if constexpr (EPI == EPI_SPECF) {
+        // no epilogue constants
+    } else if constexpr (EPI == EPI_HEAD) {
         for (int i = tid; i < 256; i += TC_THREADS) consts[i] = i < 128 ? __ldg(ep.b1 + i) : __ldg(ep.w2 + i - 128);
     } else if constexpr (EPI == EPI_LINEAR) {
         const int ntc = blockIdx.x % n_tiles;
@@ -198,6 +315,34 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + C::ACC_COLS;
+    const uint32_t tmem_c = tmem_a + SA * MT * 64;                   // the constant A k-block, 64 columns (hi|lo) per tile
+    if constexpr (Loader::CONST_A) {
+        // the splitter warps write the constant A rows (one row of 32 floats per thread and tile) once
+        if (warp >= 4 && warp < 8) {
+            const int q = warp & 3;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const float4* src = reinterpret_cast<const float4*>(ld.const_row(m * TC_BM + q * 32 + lane));
+                const uint32_t dst = tmem_c + ((uint32_t)(q * 32) << 16) + m * 64;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 w = __ldg(src + 4 * h + j);
+                        split_tf32(w.x, hi[4 * j], lo[4 * j]); split_tf32(w.y, hi[4 * j + 1], lo[4 * j + 1]);
+                        split_tf32(w.z, hi[4 * j + 2], lo[4 * j + 2]); split_tf32(w.w, hi[4 * j + 3], lo[4 * j + 3]);
+                    }
+                    tc_st16(dst + 16 * h, hi);
+                    tc_st16(dst + 32 + 16 * h, lo);
+                }
+            }
+            tc_wait_st();
+        }
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
 
     // Work distribution: this CTA keeps one column tile (so a resident W is loaded once) and strides over row units.
     const int sched_id = blockIdx.x, sched_n = gridDim.x;
@@ -206,8 +351,9 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     const int u0 = sched_id / n_tiles;
     const int n_my_units = (u0 < m_units) ? (m_units - u0 + ctas_per_nt - 1) / ctas_per_nt : 0;
     const float* wtile = wimg + (int64_t)nt * KB * (C::B_BYTES / 4);
-    // first row tile of unit ui (MT tiles follow each other)
-    auto unit_tile0 = [&](int ui) { return (u0 + ui * ctas_per_nt) * MT; };
+    // index of this CTA's ui-th work unit, and its first row tile (MT tiles follow each other)
+    auto unit_index = [&](int ui) { const int u = u0 + ui * ctas_per_nt; return Loader::REVERSE_UNITS ? m_units - 1 - u : u; };
+    auto unit_tile0 = [&](int ui) { return unit_index(ui) * MT; };
 
     if (warp < 4) {
         // ------------------------------------------ A loaders ------------------------------------------
@@ -225,7 +371,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) rs[m][i] = ld.row_state(row0 + m * TC_BM + 16 * i);
-            for (int kb = 0; kb < KB; ++kb, rr.template next<SR>()) {
+            for (int kb = 0; kb < KBA; ++kb, rr.template next<SR>()) {
                 const uint32_t sr = rr.s, ph = rr.ph;
                 bool okw; okw = mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1, &g_tc_status);
                 if (!okw) { alive = false; break; }
@@ -253,7 +399,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         uint32_t roff[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) roff[c] = tc_swz(r, c);
-        const int64_t total = (int64_t)n_my_units * KB;
+        const int64_t total = (int64_t)n_my_units * KBA;
         TcRing rr, ra;
         for (int64_t slot = 0; slot < total; ++slot, rr.template next<SR>(), ra.template next<SA>()) {
             const uint32_t sr = rr.s, pr = rr.ph;
@@ -268,8 +414,17 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             for (int m = 0; m < MT; ++m) {
                 const uint8_t* src = raw + sr * C::RAW_BYTES + m * (TC_BM * TC_BK * 4);
                 float4 v[8];
+                if constexpr (Loader::COLUMN_SPLIT) {
+                    // element k of this thread's row of A is float `lane` of tile row q * 32 + k (consecutive lanes read
+                    // consecutive floats of one 128-byte tile row: no bank conflicts)
+                    float* vf = reinterpret_cast<float*>(v);
+#pragma unroll
+                    for (int k = 0; k < 32; ++k)
+                        vf[k] = *reinterpret_cast<const float*>(src + tc_swz(q * 32 + k, lane >> 2) + (lane & 3) * 4);
+                } else {
 #pragma unroll
                 for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(src + roff[c]);
+                }
                 const uint32_t a_hi = tmem_a + lane_addr + (sa * MT + m) * 64;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -291,19 +446,67 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         }
     } else if (warp == TC_BLOAD_WARP) {
         // ------------------------------------------ W loader ------------------------------------------
+        if constexpr (Loader::W_CONVERT) {
+            // The whole warp works: lane 0 bulk-copies the prepared image of every k-block but the last; for the last one the
+            // unit's plain [rows][32] block is fetched with cp.async into a small ring three units ahead (a global load
+            // takes longer than a unit), then lane n splits column n and stores it as row n of the W stage image (k = row of
+            // the block; the k padding of the stages is cleared once).
+            for (int i = lane; i < SB * (int)B_STAGE / 16; i += 32)
+                reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+            __syncwarp();
+            const int prow = ld.w_plain_rows();
+            float* praw = reinterpret_cast<float*>(bar_mem + C::BAR_BYTES);           // [4][32 rows][32] plain blocks
+            auto fetch = [&](int ui_) {
+                if (ui_ < n_my_units) {
+                    const float* src = ld.w_plain(unit_index(ui_));
+                    float* dst = praw + (ui_ & 3) * 1024;
+                    for (int i = lane; i < prow * 8; i += 32) cp_async_zfill<16>(dst + 4 * i, src + 4 * i, true);
+                }
+                cp_async_commit();                              // one group per unit slot, empty past the end
+            };
+            fetch(0); fetch(1); fetch(2);
+            TcRing rb;
+            bool alive = true;
+            for (int ui = 0; ui < n_my_units && alive; ++ui) {
+                for (int kb = 0; kb < KB - 1; ++kb, rb.template next<SB>()) {
+                    if (!mbar_wait(b_empty(rb.s), rb.ph ^ 1, abort_flag, 6, &g_tc_status)) { alive = false; break; }
+                    if (lane == 0) {
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(rb.s)), "r"((uint32_t)C::B_BYTES) : "memory");
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(smem_base + rb.s * B_STAGE), "l"(ld.w_src(wtile, unit_index(ui), kb, C::B_BYTES / 4)),
+                                       "r"((uint32_t)C::B_BYTES), "r"(b_full(rb.s)) : "memory");
+                    }
+                }
+                if (!alive) break;
+                cp_async_wait<2>();                             // this unit's block has landed (two younger groups may be in flight)
+                __syncwarp();
+                if (!mbar_wait(b_empty(rb.s), rb.ph ^ 1, abort_flag, 6, &g_tc_status)) break;
+                float* stage = reinterpret_cast<float*>(smem + rb.s * B_STAGE);
+                const float* blk = praw + (ui & 3) * 1024 + lane;
+#pragma unroll 8
+                for (int j = 0; j < prow; ++j) tc_img_store(stage, BN, lane, j, blk[j * 32]);
+                fence_proxy_async();                            // generic-proxy stores before the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_full(rb.s));
+                rb.template next<SB>();
+                fetch(ui + 3);                                  // into the slot of unit ui - 1, which has been stored
+            }
+            cp_async_wait_all();
+        } else
         if (lane == 0 && n_my_units > 0) {
             const uint32_t bytes = C::B_BYTES;
             const int64_t total = resident ? KB : (int64_t)n_my_units * KB;
             TcRing rb;
-            int kbw = 0;
+            int kbw = 0, uiw = 0;
             for (int64_t slot = 0; slot < total; ++slot, rb.template next<SB>()) {
                 const uint32_t sb = rb.s, ph = rb.ph;
                 if (!mbar_wait(b_empty(sb), ph ^ 1, abort_flag, 6, &g_tc_status)) break;
                 const int kb = kbw;
-                if (++kbw == KB) kbw = 0;
+                const float* wsrc = ld.w_src(wtile, unit_index(uiw), kb, C::B_BYTES / 4);
+                if (++kbw == KB) { kbw = 0; ++uiw; }
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(sb)), "r"(bytes) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(smem_base + sb * B_STAGE), "l"(wtile + (int64_t)kb * (C::B_BYTES / 4)), "r"(bytes), "r"(b_full(sb)) : "memory");
+                             ::"r"(smem_base + sb * B_STAGE), "l"(wsrc), "r"(bytes), "r"(b_full(sb)) : "memory");
             }
         }
         __syncwarp();
@@ -333,11 +536,12 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 if (!okc) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * MT * C::ACCW + d_off;
-                for (int kb = 0; kb < KB; ++kb, ra.template next<SA>(), rb.template next<SB>()) {
+                for (int kb = 0; kb < KB; ++kb, rb.template next<SB>()) {
                     const uint32_t sa = ra.s, pa = ra.ph;
                     const uint32_t sb = resident ? (uint32_t)kb : rb.s;
-                    bool oka, okb = true;
-                    oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status);
+                    const bool a_ring = kb < KBA;                     // else: the constant A k-block
+                    bool oka = true, okb = true;
+                    if (a_ring) oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status);
                     if (!oka) { alive = false; break; }
                     if (!resident || ui == 0) {
                         okb = mbar_wait(b_full(sb), resident ? 0u : rb.ph, abort_flag, 7, &g_tc_status);
@@ -345,7 +549,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     }
                     tc_fence_after();
                     const uint32_t bh = desc_lo0 + sb * (B_STAGE >> 4), bl = bh + (B_STAGE >> 5);
-                    const uint32_t ah = tmem_a + sa * MT * 64 + a_off, al = ah + 32;
+                    const uint32_t ah = (a_ring ? tmem_a + sa * MT * 64 : tmem_c) + a_off, al = ah + 32;
                     if constexpr (C::MERGE) {
                         constexpr uint32_t idesc2 = tc_idesc(2 * NI);           // [W_hi | W_lo] as one operand of twice the rows
                         tc_mma_tf32_ts_p(d, ah, bh, desc_hi, idesc2, kb > 0 ? 1u : 0u);
@@ -367,7 +571,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     }
                     }
                     // the A stage (and a streamed W stage) is reusable once every issuer's MMAs have read it
-                    tc_commit(a_empty(sa));
+                    if (a_ring) { tc_commit(a_empty(sa)); ra.template next<SA>(); }
                     if (!resident) tc_commit(b_empty(sb));
                 }
                 if (alive) tc_commit(acc_full(buf));
@@ -399,9 +603,9 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 const int col_ = nt * BN + c0_ + (lane % EP_LPR) * 4;
 #pragma unroll
                 for (int i = 0; i < EP_NIT; ++i) {
-                    const int orow = row0_ + i * EP_RPI;
-                    rres[i] = (col_ < e.N && orow < rows) ? __ldg(reinterpret_cast<const float4*>(e.residual + (int64_t)orow * e.ldr + col_))
-                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const int64_t orow = ld.out_row(row0_ + i * EP_RPI);
+                    rres[i] = (col_ < e.N && orow >= 0) ? __ldg(reinterpret_cast<const float4*>(e.residual + orow * e.ldr + col_))
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
         };
@@ -443,13 +647,33 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 constexpr int RPI = 32 / LPR;                    // rows per store instruction
                 const uint8_t* warp_stage = staging + (warp - TC_EPI_WARP0) * 32 * TC_SLOT_BYTES;
                 const int tile_row0 = tile * TC_BM + q * 32;
+                // One pass (at most 32 columns per thread): the thread first takes its whole accumulator row into registers
+                // and frees the buffer, so the next unit's MMAs start while this one is finished and stored.
+                constexpr bool EARLY = CPT <= 32;
+                float vall[EARLY ? CPT : 16];
+                if constexpr (EARLY) {
+#pragma unroll
+                    for (int cc = 0; cc < CPT; cc += 16) {
+                        float v16[16];
+                        if constexpr (C::MERGE) tc_ld16_sum(taddr + col_lo + cc, BN, v16); else tc_ld16(taddr + col_lo + cc, v16);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) vall[cc + j] = v16[j];
+                    }
+                    tc_fence_before();
+                    mbar_arrive(acc_empty(buf));
+                }
 #pragma unroll 1
                 for (int c0 = col_lo; c0 < col_lo + CPT; c0 += PASS) {
                     // phase 1: each thread finishes its own row (bias, activation) into its padded staging slot
-#pragma unroll 1
+#pragma unroll (EARLY ? 2 : 1)
                     for (int cc = 0; cc < PASS; cc += 16) {
                         float v[16];
-                        if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + cc, BN, v); else tc_ld16(taddr + c0 + cc, v);
+                        if constexpr (EARLY) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = vall[cc + j];
+                        } else {
+                            if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + cc, BN, v); else tc_ld16(taddr + c0 + cc, v);
+                        }
                         // one branch on the activation per 16 columns, not per element (padding columns beyond N carry a
                         // zero bias and are never stored)
                         auto finish = [&](auto actf) {
@@ -474,20 +698,20 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
 #pragma unroll
                             for (int i = 0; i < 32 / RPI; ++i) {
                                 const int rr = i * RPI + lane / LPR;
-                                const int orow = tile_row0 + rr;
-                                if (orow < rows) {
+                                const int64_t orow = ld.out_row(tile_row0 + rr);
+                                if (orow >= 0) {
                                     float4 o = *reinterpret_cast<const float4*>(warp_stage + rr * TC_SLOT_BYTES + (lane % LPR) * 16);
                                     o.x += rres[i].x; o.y += rres[i].y; o.z += rres[i].z; o.w += rres[i].w;
-                                    *reinterpret_cast<float4*>(e.y + (int64_t)orow * e.ldc + col) = o;
+                                    *reinterpret_cast<float4*>(e.y + orow * e.ldc + col) = o;
                                 }
                             }
                         } else {
 #pragma unroll 4
                             for (int i = 0; i < 32 / RPI; ++i) {
                                 const int rr = i * RPI + lane / LPR;
-                                const int orow = tile_row0 + rr;
-                                if (orow < rows)
-                                    *reinterpret_cast<float4*>(e.y + (int64_t)orow * e.ldc + col) =
+                                const int64_t orow = ld.out_row(tile_row0 + rr);
+                                if (orow >= 0)
+                                    *reinterpret_cast<float4*>(e.y + orow * e.ldc + col) =
                                         *reinterpret_cast<const float4*>(warp_stage + rr * TC_SLOT_BYTES + (lane % LPR) * 16);
                             }
                         }
@@ -497,6 +721,22 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                         else if (ui + 1 < n_my_units) res_fetch(ui + 1, col_lo);
                     }
                     __syncwarp();
+                }
+            } else if constexpr (EPI == EPI_SPECF) {
+                // accumulator lane (x_local = q, c = lane), column j: Y1[image row][j][c]; a warp stores 128 contiguous bytes per j
+                static_assert(EPI != EPI_SPECF || (C::MERGE && BN == 32 && MT == 2), "forward y-transform tile shape");
+                const TcSpecFwdEpi& e = ep;
+                const int64_t img = (int64_t)tile * 4 + q;
+#pragma unroll
+                for (int cc = 0; cc < 32; cc += 16) {
+                    float v[16];
+                    tc_ld16_sum(taddr + cc, BN, v);
+                    if (img < e.nimg) {
+                        float* dst = e.y1 + (img * e.J + cc) * 32 + lane;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (cc + j < e.J) dst[j * 32] = v[j];
+                    }
                 }
             } else if constexpr (EPI == EPI_PROJ) {
                 const TcProjEpi& e = ep;
@@ -575,8 +815,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     e.out[row] = head_edge ? 0.0f : (acc + e.b2) * head_sc + head_sh;
                 }
             }
-            tc_fence_before();
-            mbar_arrive(acc_empty(buf));
+            if constexpr (!(EPI == EPI_LINEAR && CPT <= 32)) {     // (the one-pass LINEAR epilogue has freed the buffer already)
+                tc_fence_before();
+                mbar_arrive(acc_empty(buf));
+            }
         }
     }
     // teardown: everyone meets, then the allocating warp frees the tensor memory
@@ -597,15 +839,8 @@ __global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, i
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int n = (int)(i / kpad), k = (int)(i % kpad);
         const float v = (n < N && k < K) ? __ldg(w + (int64_t)k * ldw + n) : 0.0f;
-        uint32_t h, l;
-        split_tf32(v, h, l);
-        uint32_t l2;
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l2) : "f"(__uint_as_float(l)));
-        const int nt = n / bn, r = n % bn, kb = k / TC_BK, kk = k % TC_BK;
-        const int64_t blk = ((int64_t)nt * KB + kb) * (2 * bn * TC_BK);
-        const int off = (int)(tc_swz(r, kk >> 2) >> 2) + (kk & 3);
-        img[blk + off] = __uint_as_float(h);
-        img[blk + bn * TC_BK + off] = __uint_as_float(l2);
+        const int nt = n / bn, kb = k / TC_BK;
+        tc_img_store(img + ((int64_t)nt * KB + kb) * (2 * bn * TC_BK), bn, n % bn, k % TC_BK, v);
     }
 }
 
@@ -624,13 +859,13 @@ template <int BN, int MT, class Loader, int EPI, class EpiParams>
 static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_tiles, const EpiParams& ep, cudaStream_t st) {
     static SmemOptIn configured;
     auto kern = tc_gemm_kernel<BN, MT, Loader, EPI, EpiParams>;
-    if (int e = smem_opt_in(kern, TcCfg<BN, MT>::BYTES, configured)) return e;
+    if (int e = smem_opt_in(kern, TcCfg<BN, MT, Loader>::BYTES, configured)) return e;
     const int m_units = ceil_div(rows, TC_BM * MT);
     int per_nt = num_sms() / n_tiles;                 // CTAs per column tile
     if (per_nt < 1) per_nt = 1;
     if (per_nt > m_units) per_nt = m_units;
     const int grid = per_nt * n_tiles;
-    kern<<<grid, tc_threads(MT), TcCfg<BN, MT>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
+    kern<<<grid, tc_threads(MT), TcCfg<BN, MT, Loader>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
     return launch_status();
 }
 
@@ -645,6 +880,41 @@ static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int r
         case 64: return tc_launch<64, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
         default: return tc_launch<128, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     }
+}
+
+// ---- spectral layer: the two y-transforms as tcgen05 GEMMs (called from spectral.cu) ------------------------------
+// W image of a [K][N <= 32] matrix (pitch ldw) for 32-wide column tiles: 2 * 32 * ceil(K / 32) * 32 floats.
+int spectral_tc_prepare(const float* w_kn, int ldw, int K, int N, float* img, cudaStream_t st) {
+    const int kpad = ceil_div(K, TC_BK) * TC_BK;
+    tc_weight_prepare_kernel<<<ceil_div(32 * kpad, 256), 256, 0, st>>>(w_kn, ldw, K, N, kpad, 32, 32, img);
+    return launch_status();
+}
+// Y1[image row][j][c] = sum_y F1[j][y] X[image row][y][c] for nimg image rows of r x 32 floats; f1_img = image of F1^T.
+int spectral_fwd_y_tc(const float* x, const float* f1_img, float* y1, int r, int J, int64_t nimg, cudaStream_t st) {
+    const int64_t units = ceil_div(nimg, (int64_t)8);
+    if (units * 256 > 0x7fffffffLL) return SPGT_ERR_SHAPE;
+    TcSpecFwd ld;
+    ld.x = x; ld.r = r; ld.nimg = nimg; ld.rows = (int)(units * 256); ld.K = r;
+    TcSpecFwdEpi ep{y1, J, nimg};
+    return tc_launch<32, 2, TcSpecFwd, EPI_SPECF, TcSpecFwdEpi>(ld, f1_img, ceil_div(r, TC_BK) * TC_BK, ld.rows, 1, ep, st);
+}
+// out[image row][y][o] = act( X[y][:] Wr + F3[y][:] P[image row] + br[o] ); f3 = [upr * 256][32] table, wr_img = W stage image
+// of Wr.  r <= 256: p_plain = the P blocks as plain fp32 [image row][J][32]; larger r: p_img = one W stage image (2048
+// floats) per image row.
+int spectral_inv_y_tc(const float* x, const float* f3, const float* wr_img, const float* p_img, const float* p_plain, int J,
+                      const float* br, float* out, int r, int64_t nimg, int act, cudaStream_t st) {
+    const int upr = ceil_div(r, 256);
+    if (nimg * upr * 256 > 0x7fffffffLL) return SPGT_ERR_SHAPE;
+    TcLinearEpi epc{br, nullptr, 0, out, 32, 32, act};
+    if (upr == 1) {
+        TcSpecInvC ldc;
+        ldc.x = x; ldc.f3 = f3; ldc.wr_img = wr_img; ldc.p = p_plain; ldc.J = J; ldc.r = r; ldc.rows = (int)(nimg * 256); ldc.K = 64;
+        return tc_launch<32, 2, TcSpecInvC, EPI_LINEAR, TcLinearEpi>(ldc, wr_img, 64, ldc.rows, 1, epc, st);
+    }
+    TcSpecInv ld;
+    ld.x = x; ld.f3 = f3; ld.wr_img = wr_img; ld.p_img = p_img; ld.r = r; ld.upr = upr; ld.rows = (int)(nimg * upr * 256); ld.K = 64;
+    TcLinearEpi ep{br, nullptr, 0, out, 32, 32, act};
+    return tc_launch<32, 2, TcSpecInv, EPI_LINEAR, TcLinearEpi>(ld, wr_img, 64, ld.rows, 1, ep, st);
 }
 
 }  // namespace spgt

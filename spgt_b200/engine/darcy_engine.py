@@ -4,7 +4,7 @@ Mirrors what the reference's validate_epoch_darcy does per batch (engine/darcy_e
 copies of node / position / grid, forward, result back) with the copies on a side stream so that the upload of
 batch i+1 and the download of batch i-1 overlap the kernels of batch i.
 """
-from typing import Dict, Iterable, List
+from typing import Callable, Dict, Iterable, List, Optional
 
 import torch
 
@@ -12,8 +12,11 @@ import torch
 class HostInference:
     """Runs model.forward over host batches with double-buffered device staging.
 
-    Each batch is a dict with float32 tensors 'node' [n,r,r,1], 'position' [n,ra,ra,2], 'grid' [n,r,r,2] in pinned
-    host memory; the result for each batch is written into a pinned host tensor [n,r,r,1]."""
+    Each batch is a dict with float32 tensors 'node' [n,r,r,1], 'position' [n,ra,ra,2], 'grid' [n,r,r,2] (and optionally
+    'target' [n,r,r,1], staged for a `post` hook that computes a metric) in pinned host memory; the result for each
+    batch is written into a pinned host tensor."""
+
+    KEYS = ('node', 'position', 'grid', 'target')
 
     def __init__(self, model, device, use_graphs: bool = False):
         """use_graphs: capture the forward of each staging slot into a CUDA graph on its first use (one batch shape)."""
@@ -26,19 +29,26 @@ class HostInference:
         self._slot_out_done = [None, None]
 
     def _stage(self, slot: Dict, batch: Dict[str, torch.Tensor]):
-        for k in ('node', 'position', 'grid'):
+        for k in self.KEYS:
+            if k not in batch:
+                continue
             t = batch[k]
             if k not in slot or slot[k].shape != t.shape:
                 slot[k] = torch.empty(t.shape, dtype=torch.float32, device=self.device)
-                slot['fresh'] = True                     # a graph captured on the old buffers is stale
+                if k != 'target':
+                    slot['fresh'] = True                 # a graph captured on the old buffers is stale
             slot[k].copy_(t, non_blocking=True)
 
     def bytes_per_batch(self, batch) -> Dict[str, int]:
         n, r = batch['node'].shape[0], batch['node'].shape[1]
-        return dict(h2d=sum(batch[k].numel() * 4 for k in ('node', 'position', 'grid')), d2h=n * r * r * 4)
+        return dict(h2d=sum(batch[k].numel() * 4 for k in self.KEYS if k in batch), d2h=n * r * r * 4)
 
-    def run(self, batches: Iterable[Dict[str, torch.Tensor]], outputs: List[torch.Tensor] = None) -> List[torch.Tensor]:
-        """Returns one pinned host tensor per batch.  `outputs`, if given, supplies the destination tensors."""
+    def run(self, batches: Iterable[Dict[str, torch.Tensor]], outputs: List[torch.Tensor] = None,
+            post: Optional[Callable] = None) -> List[torch.Tensor]:
+        """Returns one pinned host tensor per batch.  `outputs`, if given, supplies the destination tensors.
+        `post(pred, slot, i)`, if given, runs on the compute stream right after the forward of batch i (slot = the staged
+        device tensors of that batch) and returns the device tensor to download instead of the prediction; buffers it
+        owns are safe to reuse every second batch (the download of batch i-2 is awaited before batch i starts)."""
         batches = list(batches)
         compute = torch.cuda.current_stream(self.device)
         results, pending = [], []
@@ -58,23 +68,25 @@ class HostInference:
                             self.copy_in.wait_event(pending[-1][1])     # slot nxt was read by batch i-1: wait for it
                         self._stage(self._slots[nxt], batches[i + 1])
                         ready[nxt] = self.copy_in.record_event()
+                if self._slot_out_done[i & 1] is not None:
+                    compute.wait_event(self._slot_out_done[i & 1])   # the buffers of batch i-2 are still being downloaded
                 if self.use_graphs:
                     if slot.pop('fresh', False):
                         self._graphs[i & 1] = None
                     if self._graphs[i & 1] is None:
                         compute.synchronize()        # the capture below warms up on a side stream
                         self._graphs[i & 1] = GraphedForward(self.model, slot['node'], slot['position'], slot['grid'], own_inputs=False)
-                    if self._slot_out_done[i & 1] is not None:
-                        compute.wait_event(self._slot_out_done[i & 1])   # the captured output buffer is still being downloaded
                     pred = self._graphs[i & 1](slot['node'], slot['position'], slot['grid'])
                 else:
+                    slot.pop('fresh', None)
                     pred = self.model(slot['node'], slot['position'], slot['grid'])
+                result = post(pred, slot, i) if post is not None else pred
                 done = compute.record_event()
-                host = outputs[i] if outputs is not None else self._host_out(i, pred.shape)
+                host = outputs[i] if outputs is not None else self._host_out(i, result.shape, result.dtype)
                 with torch.cuda.stream(self.copy_out):
                     self.copy_out.wait_event(done)
-                    host.copy_(pred, non_blocking=True)
-                    pred.record_stream(self.copy_out)
+                    host.copy_(result, non_blocking=True)
+                    result.record_stream(self.copy_out)
                     out_done = self.copy_out.record_event()
                 self._slot_out_done[i & 1] = out_done
                 pending.append((host, done, out_done))
@@ -85,12 +97,12 @@ class HostInference:
         ops.check_tc_status('HostInference.run')      # a kernel that gave up on a wait left incomplete predictions
         return results
 
-    def _host_out(self, i, shape):
+    def _host_out(self, i, shape, dtype=torch.float32):
         """One pinned host tensor per batch index of a run (kept for the next run of the same length and shape): every
         returned prediction stays valid until run() is called again."""
-        key = (i, tuple(shape))
+        key = (i, tuple(shape), dtype)
         if key not in self._out_host:
-            self._out_host[key] = torch.empty(shape, dtype=torch.float32, pin_memory=True)
+            self._out_host[key] = torch.empty(shape, dtype=dtype, pin_memory=True)
         return self._out_host[key]
 
 

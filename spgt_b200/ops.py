@@ -29,12 +29,13 @@ def _stream() -> int:
 
 
 # kernels launched by one call of each entry point (everything else launches one)
-_KERNELS_PER_CALL = {'spgt_batched_skinny_gemm': 2, 'spgt_spectral_conv2d_fwd': 5, 'spgt_galerkin_attn_bwd': 2, 'spgt_projpos_bwd_elementwise': 2}
+_KERNELS_PER_CALL = {'spgt_batched_skinny_gemm': 2, 'spgt_galerkin_attn_bwd': 2, 'spgt_projpos_bwd_elementwise': 2}
 LAUNCHES = 0          # running count of kernels launched through this module
 _PROFILE = None       # None, or a dict name -> list of (start_event, end_event) filled while profiling
 
 
-def _call(name: str, *args) -> None:
+def _call(name: str, *args, kernels: int = None) -> None:
+    """`kernels`: how many kernels this call launches when that depends on the arguments."""
     global LAUNCHES
     fn = getattr(lib, name)
     prof = _PROFILE
@@ -47,7 +48,7 @@ def _call(name: str, *args) -> None:
     else:
         code = fn(*args)
     check(code, name)
-    LAUNCHES += _KERNELS_PER_CALL.get(name, 1)
+    LAUNCHES += kernels if kernels is not None else _KERNELS_PER_CALL.get(name, 1)
 
 
 class profile_ops:
@@ -515,5 +516,6 @@ def spectral_conv2d(x: Tensor, wr_kn: Tensor, br: Tensor, fw0: Tensor, fw1: Tens
     with torch.cuda.device(x.device):
         _call('spgt_spectral_conv2d_fwd', x.data_ptr(), wr_kn.data_ptr(), br.data_ptr(), fw0.data_ptr(), fw1.data_ptr(),
                                            tab.data_ptr(), workspace.data_ptr(), workspace.numel(), y.data_ptr(),
-                                           B, r, Cc, mode, act_code(act), _stream())
+                                           B, r, Cc, mode, act_code(act), _stream(),
+              kernels=int(lib.spgt_spectral_launches(B, r, mode)))
     return y

@@ -64,6 +64,46 @@ def reduce_metric(metric_sum: torch.Tensor, count: torch.Tensor, world: int) -> 
     return float(packed[0] / packed[1].clamp_min(1.0))
 
 
+class ShardedGather:
+    """`post` hook of HostInference for a rank of a sharded run: after the forward of the rank's slice of a global batch it
+    gathers all ranks' predictions into the global batch (one all_gather_into_tensor) and sums the per-sample metric over
+    all ranks (one all_reduce of (sum, count)), both on the compute stream.  Rank 0 gets the gathered predictions as the
+    tensor to download, the other ranks the reduced (sum, count); `metric(i)` gives the global mean of batch i afterwards.
+    The global batch must split evenly over the ranks (collectives need equal block sizes)."""
+
+    def __init__(self, n_total: int, rank: int, world: int, sample_shape, device):
+        if n_total % world != 0:
+            raise ValueError('ShardedGather needs a global batch that is a multiple of the number of ranks')
+        self.n_total, self.rank, self.world = n_total, rank, world
+        self.full = [torch.empty((n_total, *sample_shape), dtype=torch.float32, device=device) for _ in range(2)] if world > 1 else None
+        self.packed = [torch.zeros(2, dtype=torch.float64, device=device) for _ in range(2)]
+        self.packed_host = {}
+
+    def __call__(self, pred: torch.Tensor, slot: Dict[str, torch.Tensor], i: int) -> torch.Tensor:
+        # Everything here is enqueued on the compute stream without a host synchronisation (no Python scalars are
+        # turned into device tensors): the host loop must stay ahead of the device to overlap the next upload.
+        from ..engine.metric import relative_l2_per_sample
+        packed = self.packed[i & 1]
+        if 'target' in slot:
+            packed[0:1].copy_(relative_l2_per_sample(pred, slot['target']).sum().reshape(1))
+            packed[1:2].fill_(float(pred.shape[0]))
+        if self.world > 1:
+            full = self.full[i & 1]
+            dist.all_gather_into_tensor(full, pred.contiguous())
+            dist.all_reduce(packed, op=dist.ReduceOp.SUM)
+        else:
+            full = pred
+        if i not in self.packed_host:
+            self.packed_host[i] = torch.empty(2, dtype=torch.float64, pin_memory=pred.is_cuda)
+        self.packed_host[i].copy_(packed, non_blocking=True)
+        return full if self.rank == 0 else packed
+
+    def metric(self, i: int) -> float:
+        """Global mean of the per-sample metric of batch i (valid once the run has returned)."""
+        p = self.packed_host[i]
+        return float(p[0] / max(float(p[1]), 1.0))
+
+
 def run_sharded(forward: Callable[[Dict[str, torch.Tensor]], torch.Tensor], make_batch: Callable[[range], Dict[str, torch.Tensor]],
                 n_total: int, batch_size: int, rank: int, world: int, target_fn: Optional[Callable] = None,
                 sample_shape: Optional[Tuple[int, ...]] = None, device=None):

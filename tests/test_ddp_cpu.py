@@ -63,3 +63,33 @@ def test_two_ranks_uneven_split(tmp_path):
 def test_two_ranks_one_sample(tmp_path):
     """Fewer samples than ranks: the rank with an empty slice still enters the gather and the metric reduction."""
     _run(1, 2, tmp_path)
+
+
+def _gather_worker(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    from spgt_b200.run.ddp_darcy_inference import ShardedGather, distributed_initialize, shard_range
+    r, w, _ = distributed_initialize('gloo')
+    n_total = 6
+    b, e = shard_range(n_total, r, w)
+    gather = ShardedGather(n_total, r, w, (3, 3, 1), 'cpu')
+    outs = []
+    for step in range(3):                                   # three steps: the two internal buffers are reused
+        pred = (torch.arange(b, e, dtype=torch.float32) + 10 * step).view(-1, 1, 1, 1).expand(-1, 3, 3, 1).contiguous()
+        slot = {'target': pred + 0.5}
+        outs.append(gather(pred, slot, step).clone())
+    torch.save({'outs': outs, 'metrics': [gather.metric(i) for i in range(3)]}, os.path.join(out_dir, f'g{rank}.pt'))
+    dist.destroy_process_group()
+
+
+def test_sharded_gather_hook_two_ranks(tmp_path):
+    """The post-forward hook of the host loop: rank 0 receives the global batch in order, the others the reduced metric sums."""
+    world = 2
+    mp.spawn(_gather_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    res = [torch.load(os.path.join(tmp_path, f'g{r}.pt')) for r in range(world)]
+    for step in range(3):
+        expect = (torch.arange(6, dtype=torch.float32) + 10 * step).view(-1, 1, 1, 1).expand(-1, 3, 3, 1)
+        assert torch.equal(res[0]['outs'][step], expect)
+        ref_metric = float((0.5 / (torch.arange(6, dtype=torch.float64) + 10 * step + 0.5)).mean())
+        assert res[1]['outs'][step].shape == (2,) and abs(float(res[1]['outs'][step][0] / res[1]['outs'][step][1]) - ref_metric) < 1e-6
+        for r in range(world):
+            assert abs(res[r]['metrics'][step] - ref_metric) < 1e-6

@@ -113,3 +113,27 @@ def test_checkpoint_conversion_roundtrip_and_shapes():
             assert torch.equal(gt[k][3, 5, 7, 2], sp[k][7, 2, 3, 5])
         else:
             assert torch.equal(gt[k], sp[k])
+
+
+def test_benchmark_weights_fit_the_model_and_the_cpu_baseline():
+    """bench.random_state() is a complete state dict of the benchmark model; the CPU baseline of the benchmark (the
+    reference's own model when its files are staged, else the restatement) accepts it and both agree with the oracle."""
+    import bench
+    from oracle import gt_oracle as O, ref_runner as R
+    from spgt_b200.config.config_accessor import get_darcy_config
+    from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
+    state = bench.random_state()
+    model = Sp_GalerkinTransformer2D(get_darcy_config(2, 8, num_frequence_mode=12))
+    model.load_state_dict(state, strict=True)
+    # a small shape for the forward check: the same keys minus four encoder layers
+    small = {k: v for k, v in bench.random_state(modes=4).items() if not any(f'layers.{i}.attention' in k or f'encoder_mixer.layers.{i}.' in k for i in range(2, 6))}
+    ocfg = O.default_config(85, 3, 6, 4, 2, 2)
+    data = R.synthetic_batch(range(2), 85, 3, 6, seed=4)
+    fwd, kind = R.make_forward(ocfg, small)
+    out = fwd(data['node'], data['position'], data['grid'])
+    ref = O.model_forward(data['node'], data['position'], data['grid'], small, ocfg)
+    assert kind in ('reference', 'port')
+    assert float((out - ref).norm() / ref.norm()) < 1e-5
+    from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
+    mine = synthetic_darcy_batch(range(2), 85, 3, 6, 4)
+    assert all(torch.equal(mine[k], data[k]) for k in ('node', 'position', 'grid'))      # both arms see the same samples

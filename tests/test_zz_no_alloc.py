@@ -1,10 +1,10 @@
 """The no-allocation skinny GEMM entry point, called through the C ABI (collected last: the file name sorts after
 every other test file, so it runs both alone and after the rest of the GPU suite has used the library).
 
-spgt_batched_skinny_gemm_noalloc keeps its split-K partial tiles in a fixed array inside the library instead of a
-caller-provided workspace.  It launches the same two kernels with the same split count as
-spgt_batched_skinny_gemm, so the results must be bit-identical, on the first call (which also does the per-device
-set-up) and on a second call that finds the array dirty from the first one.
+spgt_batched_skinny_gemm_noalloc keeps its scratch (the partial tiles of the split k range and the tickets that count
+them) in a fixed array inside the library instead of a caller-provided workspace.  It launches the same kernels on the
+same plan as spgt_batched_skinny_gemm, so the results must be bit-identical, on the first call (which also does the
+per-device set-up) and on a second call that finds the array dirty from the first one.
 """
 import ctypes as C
 
@@ -52,7 +52,8 @@ def test_no_alloc_matches_workspace_entry_point_twice_in_a_row():
     assert lib.spgt_skinny_gemm_noalloc_max_bytes() == 8 << 20
     g = torch.Generator().manual_seed(20)
     # second problem is smaller and differently shaped, so it reads a scratch array left dirty by the first
-    for call, (batch, M, N, K) in enumerate([(64, 32, 32, 1849), (3, 40, 34, 5000)]):
+    # (one-launch kernel, then the two-pass kernels: N = 34 is not a multiple of 4, then the one-launch kernel on the dirty array)
+    for call, (batch, M, N, K) in enumerate([(64, 32, 32, 1849), (3, 40, 34, 5000), (5, 40, 36, 7001)]):
         A = torch.randn(batch, M, K, generator=g).to(dev)
         Bm = torch.randn(batch, K, N, generator=g).to(dev)
         alpha = 1.0 / K
@@ -72,7 +73,7 @@ def test_no_alloc_rejects_what_does_not_fit_and_bad_arguments():
     from spgt_b200._lib import lib
     dev = torch.device('cuda:0')
     torch.cuda.set_device(dev)
-    batch, M, N, K = 4096, 64, 64, 64          # 4 tiles x 4096 batches x 4 KiB = 64 MiB of partial tiles
+    batch, M, N, K = 4096, 64, 66, 64          # two-pass kernels (N % 4 != 0): 6 tiles x 4096 batches x 4 KiB = 96 MiB of partial tiles
     assert lib.spgt_skinny_gemm_workspace_bytes(M, N, K, batch) > lib.spgt_skinny_gemm_noalloc_max_bytes()
     A = torch.zeros(batch, M, K, device=dev)
     Bm = torch.zeros(batch, K, N, device=dev)
