@@ -458,20 +458,23 @@ skinny_reduce_kernel(const float* __restrict__ ws, float* __restrict__ C, float 
 
 // ------------------------------------------------------------------------------------------------------------
 // The same product in ONE launch with the k range of all (batch, tile) items cut evenly over one persistent CTA
-// per SM ("stream-K"): the items' 32-wide k slices form one long list, CTA c takes the c-th equal share of it, so a
+// per SM ("stream-K"): the items' 16-wide k slices form one long list, CTA c takes the c-th equal share of it, so a
 // CTA works on the end of one item, possibly some whole items, and the start of another.  An item that lies
 // inside one CTA is scaled and stored directly.  The pieces of an item that spans several CTAs go to a small
 // scratch (two 32x32 slots per CTA); every CTA that finishes a piece takes a ticket on the item's counter and the
 // one that takes the last ticket adds the pieces in CTA order - a fixed order, so the result is bit-identical from
 // run to run - scales the sum and stores it.  Nothing ever waits for another CTA.
-// Rows of A are only 4-byte aligned (K is arbitrary): a row piece is fetched as nine 16-byte cp.async chunks that
+// Rows of A are only 4-byte aligned (K is arbitrary): a row piece is fetched as five 16-byte cp.async chunks that
 // start at the aligned element at or below its first column; the wanted elements then sit (element index of the
 // piece start) mod 4 floats into the shared-memory row.  Requires N % 4 == 0 (16-byte chunks of the B rows).
 // ------------------------------------------------------------------------------------------------------------
-constexpr int SKS_WARPS = 6, SKS_STAGES = 3;
-constexpr int SKS_AP = 36;   // A tile row: 32 wanted floats + up to 3 of shift, nine 16-byte chunks; == 4 (mod 32)
+// The kernel is bound by latency, not by a pipe (measured with 6 warps per SM: tensor pipe 33 %, issue slots 35 %, DRAM 41 %
+// busy, top stall "wait"), so the slices are 16 wide: a warp's three-stage ring takes 15 KB and twelve warps fit an SM.
+constexpr int SKS_WARPS = 12, SKS_STAGES = 3;
+constexpr int SKS_K = 16;    // k slice of one stage
+constexpr int SKS_AP = 20;   // A tile row: 16 wanted floats + up to 3 of shift, five 16-byte chunks; rows 20 floats apart: conflict-free fragments
 constexpr int SKS_BP = 40;   // B tile row pitch, == 8 (mod 32)
-constexpr int SKS_STAGE = 32 * SKS_AP + 32 * SKS_BP;
+constexpr int SKS_STAGE = 32 * SKS_AP + SKS_K * SKS_BP;
 constexpr int SKS_WARP_FLOATS = SKS_STAGES * SKS_STAGE;
 constexpr size_t SKS_SMEM = (size_t)SKS_WARPS * SKS_WARP_FLOATS * sizeof(float);
 static_assert(SKS_WARP_FLOATS >= 1024, "a warp's region also holds its 32x32 partial tile");
@@ -502,7 +505,6 @@ skinny_streamk_kernel(const float* __restrict__ A, const float* __restrict__ B, 
         const int64_t a_row0 = (b * M + (int64_t)tm * 32) * K;          // element index of A[b][tm * 32][0]
         const int nmine = (sub1 - sub0 - warp + SKS_WARPS - 1) / SKS_WARPS;
 
-        // per-lane copy plan of an A tile: chunk idx = lane + 32 n -> (row, chunk in row)
         int a_sh[2][2];                                                  // shift of rows 16 i + g and 16 i + g + 8
 #pragma unroll
         for (int i = 0; i < 2; ++i)
@@ -510,12 +512,12 @@ skinny_streamk_kernel(const float* __restrict__ A, const float* __restrict__ B, 
             for (int h = 0; h < 2; ++h) a_sh[i][h] = (int)((a_row0 + (int64_t)(16 * i + g + 8 * h) * K) & 3);
 
         auto load = [&](int it, int stage) {
-            const int k0 = (sub0 + warp + it * SKS_WARPS) * 32;
+            const int k0 = (sub0 + warp + it * SKS_WARPS) * SKS_K;
             float* as = wreg + stage * SKS_STAGE;
             float* bs = as + 32 * SKS_AP;
 #pragma unroll
-            for (int n = 0; n < 9; ++n) {
-                const int idx = lane + 32 * n, row = idx / 9, ch = idx - 9 * row;
+            for (int n = 0; n < 5; ++n) {                                 // chunk idx = lane + 32 n -> (row, chunk in row)
+                const int idx = lane + 32 * n, row = idx / 5, ch = idx - 5 * row;
                 const int m = tm * 32 + row;
                 const int64_t e = a_row0 + (int64_t)row * K + k0;        // element index of the first wanted element
                 const int64_t start = (e & ~(int64_t)3) + 4 * ch;
@@ -528,7 +530,7 @@ skinny_streamk_kernel(const float* __restrict__ A, const float* __restrict__ B, 
                 const int r4 = lane >> 3, c4 = (lane & 7) * 4;
                 const int n = tn * 32 + c4;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < SKS_K / 4; ++i) {
                     const int k = k0 + i * 4 + r4;
                     const bool ok = k < K && n < N;                      // N % 4 == 0: a chunk is all inside or all outside
                     cp_async_zfill<16>(bs + (i * 4 + r4) * SKS_BP + c4, Bg + (int64_t)(ok ? k : 0) * N + (ok ? n : 0), ok);
@@ -537,7 +539,7 @@ skinny_streamk_kernel(const float* __restrict__ A, const float* __restrict__ B, 
             cp_async_commit();
         };
 
-        // Two levels of accumulation: the tensor cores add into `acc` for eight slices (96 MMAs per element), then `acc` is
+        // Two levels of accumulation: the tensor cores add into `acc` for sixteen slices (96 MMAs per element), then `acc` is
         // added to `tot` with ordinary fp32 additions.  The accumulate step of an MMA truncates, so the error of one long
         // chain grows with its length; short chains keep sums of 10^4 .. 10^5 cancelling terms at fp32 accuracy.
         float acc[2][4][4], tot[2][4][4];
@@ -551,7 +553,7 @@ skinny_streamk_kernel(const float* __restrict__ A, const float* __restrict__ B, 
         if (nmine > 0) load(0, 0);
         if (nmine > 1) load(1, 1);
         for (int it = 0; it < nmine; ++it) {
-            if ((it & 7) == 0 && it > 0) {
+            if ((it & 15) == 0 && it > 0) {
 #pragma unroll
                 for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -566,7 +568,7 @@ skinny_streamk_kernel(const float* __restrict__ A, const float* __restrict__ B, 
             const float* as = wreg + (it % SKS_STAGES) * SKS_STAGE;
             const float* bs = as + 32 * SKS_AP;
 #pragma unroll
-            for (int k8 = 0; k8 < 4; ++k8) {
+            for (int k8 = 0; k8 < SKS_K / 8; ++k8) {
                 const int kk = k8 * 8 + t;
                 uint32_t ahi[2][4], alo[2][4];
 #pragma unroll
@@ -747,7 +749,7 @@ static size_t skinny_twopass_bytes(int M, int N, int K, int batch) {
 static bool skinny_streamk_ok(int N) { return N % 4 == 0; }
 static SksPlan skinny_plan(int M, int N, int K, int batch) {
     SksPlan pl;
-    pl.tiles_n = ceil_div(N, 32); pl.tiles = ceil_div(M, 32) * pl.tiles_n; pl.nsub = ceil_div(K, 32);
+    pl.tiles_n = ceil_div(N, 32); pl.tiles = ceil_div(M, 32) * pl.tiles_n; pl.nsub = ceil_div(K, SKS_K);
     pl.total = (int64_t)batch * pl.tiles * pl.nsub;
     const int64_t want = ceil_div(pl.total, (int64_t)(2 * SKS_WARPS));      // at least two slices per warp
     pl.P = (int)(want < num_sms() ? (want < 1 ? 1 : want) : num_sms());

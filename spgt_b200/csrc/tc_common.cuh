@@ -41,16 +41,21 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 // of the CTA gave up; the first code that expires is also latched in *status (device global, read by the host).
 // The non-blocking test comes first: in steady state most waits find their phase already complete, and a successful
 // test_wait costs the waiting thread ~120 cycles against ~300 for a successful try_wait (measured on B200), which
-// matters for the single thread that issues the MMAs.  Each try_wait may sleep up to its 100 us hint, so the clock
-// is read after every unsuccessful one.
+// matters for the single thread that issues the MMAs.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status = nullptr,
                                           unsigned long long limit_ns = TC_WAIT_LIMIT_NS) {
     if (mbar_test_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    for (;;) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > limit_ns) break;
+        // The abort flag and the clock are looked at every 64th unsuccessful poll only: a waiting warp shares its
+        // scheduler with the warps that do the work, and every instruction of the polling loop takes an issue slot.
+        if ((i & 63u) == 0u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = globaltimer_ns();
+            if (i == 0u) t0 = now;
+            else if (now - t0 > limit_ns) break;
+        }
     }
     *abort_flag = code;
     if (status != nullptr) atomicCAS(status, 0, code);

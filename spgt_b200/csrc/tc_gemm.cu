@@ -155,7 +155,7 @@ struct TcSpecInv : TcLoaderDefaults {
 // accumulator buffer and two A stages).  Image rows are taken from the last to the first: the ones the forward transform
 // read last are the ones still in L2.
 struct TcSpecInvC : TcLoaderDefaults {
-    static constexpr bool W_PER_UNIT = true, CONST_A = true, REVERSE_UNITS = true, W_CONVERT = true;
+    static constexpr bool W_PER_UNIT = true, CONST_A = true, REVERSE_UNITS = true, W_CONVERT = true;     // (W_CONVERT needs 32-wide column tiles: lane = image row)
     static constexpr int RAW_STAGES = 4, W_STAGES = 4, A_STAGES = 1;
     const float* x; const float* f3; const float* wr_img; const float* p; int J; int r; int rows; int K;
     __device__ __forceinline__ const float* w_src(const float*, int, int, int) const { return wr_img; }
@@ -481,10 +481,24 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 cp_async_wait<2>();                             // this unit's block has landed (two younger groups may be in flight)
                 __syncwarp();
                 if (!mbar_wait(b_empty(rb.s), rb.ph ^ 1, abort_flag, 6, &g_tc_status)) break;
-                float* stage = reinterpret_cast<float*>(smem + rb.s * B_STAGE);
+                // lane n writes row n of the image: per 16-byte chunk (four k values) one store of the hi and one of the lo part
+                // (this warp's instruction count per unit is on the critical path of the whole pipeline)
+                uint8_t* stage = smem + rb.s * B_STAGE;
                 const float* blk = praw + (ui & 3) * 1024 + lane;
-#pragma unroll 8
-                for (int j = 0; j < prow; ++j) tc_img_store(stage, BN, lane, j, blk[j * 32]);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    if (4 * c < prow) {
+                        uint32_t h[4], l[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float v = (4 * c + e < prow) ? blk[(4 * c + e) * 32] : 0.0f;
+                            split_tf32_rn(v, h[e], l[e]);
+                        }
+                        const uint32_t off = tc_swz(lane, c);
+                        *reinterpret_cast<uint4*>(stage + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(stage + BN * TC_BK * 4 + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                    }
+                }
                 fence_proxy_async();                            // generic-proxy stores before the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(b_full(rb.s));
@@ -649,7 +663,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 const int tile_row0 = tile * TC_BM + q * 32;
                 // One pass (at most 32 columns per thread): the thread first takes its whole accumulator row into registers
                 // and frees the buffer, so the next unit's MMAs start while this one is finished and stored.
-                constexpr bool EARLY = CPT <= 32;
+                constexpr bool EARLY = CPT <= 32 && NBUF == 1;     // (with two buffers the next unit does not wait for this one anyway)
                 float vall[EARLY ? CPT : 16];
                 if constexpr (EARLY) {
 #pragma unroll
@@ -815,7 +829,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     e.out[row] = head_edge ? 0.0f : (acc + e.b2) * head_sc + head_sh;
                 }
             }
-            if constexpr (!(EPI == EPI_LINEAR && CPT <= 32)) {     // (the one-pass LINEAR epilogue has freed the buffer already)
+            if constexpr (!(EPI == EPI_LINEAR && CPT <= 32 && NBUF == 1)) {     // (else the LINEAR epilogue has freed the buffer already)
                 tc_fence_before();
                 mbar_arrive(acc_empty(buf));
             }

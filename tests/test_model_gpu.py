@@ -149,23 +149,53 @@ def test_graph_captured_forward_is_bit_identical():
 
 
 def test_host_inference_with_and_without_graphs_agree():
-    """The host-facing loop (pinned batches in, pinned predictions out) gives the same bits eagerly and with replayed graphs."""
+    """The host-facing loop (pinned batches in, pinned predictions out) gives the same bits eagerly and with replayed graphs,
+    and every one of its returned predictions - more batches than it has staging slots or ever had output buffers - is the
+    prediction of its own batch."""
     from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
     from spgt_b200.engine.darcy_engine import HostInference
     cfg, model = _random_model(3, 10, 12, seed=6)
     model = model.cuda()
     batches = []
-    for i in range(5):
+    for i in range(7):
         d = synthetic_darcy_batch(range(2 * i, 2 * i + 2), 421, 3, 10, seed=6)
         batches.append({k: d[k].pin_memory() for k in ('node', 'position', 'grid')})
     with torch.no_grad():
-        eager = [t.clone() for t in HostInference(model, 'cuda:0').run(batches)]
-        graphed = [t.clone() for t in HostInference(model, 'cuda:0', use_graphs=True).run(batches)]
-        direct = model(batches[3]['node'].cuda(), batches[3]['position'].cuda(), batches[3]['grid'].cuda()).cpu()
-    assert len(eager) == len(graphed) == 5
-    for a, b in zip(eager, graphed):
-        assert torch.equal(a, b)
-    assert torch.equal(eager[3], direct)
+        eager = HostInference(model, 'cuda:0').run(batches)
+        graphed = HostInference(model, 'cuda:0', use_graphs=True).run(batches)
+        direct = [model(b['node'].cuda(), b['position'].cuda(), b['grid'].cuda()).cpu() for b in batches]
+    assert len(eager) == len(graphed) == 7
+    assert len({t.data_ptr() for t in eager}) == 7            # one host tensor per batch: no prediction overwrites another
+    for a, b, c in zip(eager, graphed, direct):
+        assert torch.equal(a, b) and torch.equal(a, c)
+
+
+def test_host_inference_static_inputs_are_uploaded_once_and_refreshed_when_they_change():
+    """static_keys: node coordinates that stay the same host tensors are not copied again, new tensors are."""
+    from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
+    from spgt_b200.engine.darcy_engine import HostInference
+    cfg, model = _random_model(3, 10, 12, seed=7)
+    model = model.cuda()
+    d = synthetic_darcy_batch(range(8), 421, 3, 10, seed=7)
+    pos, grid = d['position'][:2].contiguous().pin_memory(), d['grid'][:2].contiguous().pin_memory()
+    batches = [{'node': d['node'][2 * i:2 * i + 2].contiguous().pin_memory(), 'position': pos, 'grid': grid} for i in range(4)]
+    eng = HostInference(model, 'cuda:0', use_graphs=True, static_keys=('position', 'grid'))
+    assert eng.bytes_per_batch(batches[0])['h2d'] == batches[0]['node'].numel() * 4
+    with torch.no_grad():
+        got = [t.clone() for t in eng.run(batches)]
+        direct = [model(b['node'].cuda(), pos.cuda(), grid.cuda()).cpu() for b in batches]
+        for a, c in zip(got, direct):
+            assert torch.equal(a, c)
+        grid2 = (grid * 0.5).pin_memory()                      # another discretisation: must reach the device
+        got2 = eng.run([dict(b, grid=grid2) for b in batches])
+        direct2 = [model(b['node'].cuda(), pos.cuda(), grid2.cuda()).cpu() for b in batches]
+        for a, c in zip(got2, direct2):
+            assert torch.equal(a, c)
+        assert not torch.equal(got2[0], got[0])
+        grid2.mul_(2.0)                                        # changed in place: the version counter tells
+        got3 = eng.run([dict(b, grid=grid2) for b in batches])
+        for a, c in zip(got3, direct):
+            assert torch.equal(a, c)
 
 
 def test_real_data_inference_driver(tmp_path):
@@ -176,13 +206,13 @@ def test_real_data_inference_driver(tmp_path):
     from spgt_b200.dataset.darcy_dataset import DarcyDataset
     from spgt_b200.network.sp_model import Sp_GalerkinTransformer2D
     from spgt_b200.run.darcy_inference import darcy_inference
-    R, n = 85, 7
+    R, n = 85, 15
     rng = np.random.default_rng(8)
     a = np.where(rng.standard_normal((n, R, R)) >= 0, 12.0, 3.0)
     u = rng.standard_normal((n, R, R)) * 0.01
     path = str(tmp_path / 'darcy_small.mat')
     savemat(path, {'a': a, 'u': u})
-    cfg = get_darcy_config(3, 6, num_frequence_mode=4, clamp_attn=False, fine_resolution=R, batch_size=1, num_data=5)
+    cfg = get_darcy_config(3, 6, num_frequence_mode=4, clamp_attn=False, fine_resolution=R, batch_size=1, num_data=13)
     torch.manual_seed(3)
     ckpt = {'Module': Sp_GalerkinTransformer2D(dict(cfg, target_normalizer=None)).state_dict()}
     torch.save(ckpt, str(tmp_path / 'm.pt'))
@@ -190,7 +220,7 @@ def test_real_data_inference_driver(tmp_path):
     metric = darcy_inference(cfg, ckpt, path, path, use_graphs=True)
     # oracle: same normalisers, same batches of 2, mean over batches of the per-batch mean relative L2
     train = DarcyDataset(path, 3, is_training=True)
-    valid = DarcyDataset(path, 3, 6, 5, R, is_training=False, node_normalizer=train.node_normalizer)
+    valid = DarcyDataset(path, 3, 6, 13, R, is_training=False, node_normalizer=train.node_normalizer)
     ocfg = O.default_config(R, 3, 6, 4)
     ocfg['target_std'] = torch.from_numpy(np.asarray(train.target_normalizer.std)).float()
     ocfg['target_mean'] = torch.from_numpy(np.asarray(train.target_normalizer.mean)).float()
@@ -199,5 +229,5 @@ def test_real_data_inference_driver(tmp_path):
         pred = O.model_forward(b['node'], b['position'], b['grid'], ckpt['Module'], ocfg)
         total += float(O.relative_l2_metric(pred, b['target']))
         nb += 1
-    assert nb == 3
+    assert nb == 7          # six full batches (more than the host loop has staging slots) and a ragged one
     assert abs(metric - total / nb) < 1e-4 * (total / nb)
