@@ -29,8 +29,10 @@ def test_argument_validation_without_gpu():
     assert lib.spgt_galerkin_attn_fwd(16, 16, 16, 20, None, 1, 1, 34, 8, 0, None) == -3   # misaligned out
     assert lib.spgt_projpos_fwd(16, 16, None, 16, 16, 1, 8, 128, 2, 64, 2, None) == -2    # d_head != 32
     assert lib.spgt_spectral_tables_bytes(211, 12) > 0 and lib.spgt_spectral_tables_bytes(10, 17) == 0
-    assert lib.spgt_spectral_workspace_bytes(8, 211, 12, 32) == (2 * 8 * 211 * 24 * 32 + 4 * 8 * 24 * 12 * 32) * 4
-    assert lib.spgt_skinny_gemm_workspace_bytes(32, 32, 1849, 64) % 4096 == 0
+    # Y1 and P [8, 211, 24, 32] + Zr, Zi, Or, Oi [8, 24, 12, 32] + the 2048-float image of the residual weight
+    assert lib.spgt_spectral_workspace_bytes(8, 211, 12, 32) == (2 * 8 * 211 * 24 * 32 + 4 * 8 * 24 * 12 * 32 + 2048) * 4
+    assert lib.spgt_spectral_launches(8, 211, 12) == 5 and lib.spgt_spectral_chunk_samples(211) >= 8
+    assert lib.spgt_skinny_gemm_workspace_bytes(32, 32, 1849, 64) % 4 == 0 and lib.spgt_skinny_gemm_workspace_bytes(32, 30, 1849, 64) % 4096 == 0
     assert lib.spgt_set_tuning(b'no_such_key', 1) == -2
 
 
