@@ -226,12 +226,12 @@ spectral_inv_x_kernel(const float* __restrict__ Or, const float* __restrict__ Oi
 // S2c as a real GEMM:  P[x][n] = sum_k Gt[k][x] * Bm[k][n],  k < 2J,
 //                      Bm[q] = (Or[q] | Oi[q]),  Bm[J+q] = (Oi[q] | -Or[q]);  n < 32 -> P[.., ky, :], else P[.., m + ky, :].
 // Both stage the whole G table ([2J][r], zero padded) and their Y1 / O block in shared memory, then every warp
-// owns a slice of the output (S2a: 16 columns, S2c: every fourth 16-row tile).
+// owns a slice of the output (S2a: 8 columns, S2c: every eighth 16-row tile); eight warps per CTA.
 // ------------------------------------------------------------------------------------------------------------
 constexpr int SP_YP = 72;         // pitch of the [x][64] / [k][64] B operands, == 8 (mod 32)
 
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 spectral_fwd_x_mma_kernel(const float* __restrict__ Y1, const float* __restrict__ tab, float* __restrict__ Zr,
                           float* __restrict__ Zi, int r, int m) {
     extern __shared__ __align__(16) float smem[];
@@ -246,30 +246,30 @@ spectral_fwd_x_mma_kernel(const float* __restrict__ Y1, const float* __restrict_
     const int g = lane >> 2, t = lane & 3;
     // Y block: 16 float4 per x (8 from the real row, 8 from the imaginary row)
     const float* yb = Y1 + b * (int64_t)r * J * SP_C;
-    for (int i = tid; i < r8 * 16; i += 128) {
+    for (int i = tid; i < r8 * 16; i += 256) {
         const int x = i >> 4, c4 = i & 15;
         const bool ok = x < r;
         const float* src = yb + ((int64_t)(ok ? x : 0) * J + (c4 < 8 ? ky : m + ky)) * SP_C + (c4 & 7) * 4;
         cp_async_zfill<16>(ys + x * SP_YP + c4 * 4, src, ok);
     }
     cp_async_commit();
-    for (int i = tid; i < 16 * MT * GP / 4; i += 128) cp_async_zfill<16>(gs + 4 * i, tab + T.ga + 4 * i, true);   // padded G, as stored
+    for (int i = tid; i < 16 * MT * GP / 4; i += 256) cp_async_zfill<16>(gs + 4 * i, tab + T.ga + 4 * i, true);   // padded G, as stored
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
 
-    float acc[4][2][4];
+    float acc[4][1][4];             // eight warps, eight columns each
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 1; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
-    const int n0 = warp * 16;
+    const int n0 = warp * 8;
     for (int k0 = 0; k0 < r8; k0 += 8) {
-        uint32_t bhi[2][2], blo[2][2];
+        uint32_t bhi[1][2], blo[1][2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < 1; ++j) {
             const float* p = ys + (k0 + t) * SP_YP + n0 + 8 * j + g;
             split_tf32(p[0], bhi[j][0], blo[j][0]);
             split_tf32(p[4 * SP_YP], bhi[j][1], blo[j][1]);
@@ -284,7 +284,7 @@ spectral_fwd_x_mma_kernel(const float* __restrict__ Y1, const float* __restrict_
                 split_tf32(p[4], ahi[2], alo[2]);
                 split_tf32(p[8 * GP + 4], ahi[3], alo[3]);
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
+                for (int j = 0; j < 1; ++j) {
                     mma_tf32(acc[i][j], alo, bhi[j]);
                     mma_tf32(acc[i][j], ahi, blo[j]);
                     mma_tf32(acc[i][j], ahi, bhi[j]);
@@ -298,14 +298,14 @@ spectral_fwd_x_mma_kernel(const float* __restrict__ Y1, const float* __restrict_
     for (int i = 0; i < 4; ++i)
         if (i < MT) {
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int j = 0; j < 1; ++j) {
                 const int row = 16 * i + g, col = n0 + 8 * j + 2 * t;
                 *reinterpret_cast<float2*>(rs + row * SP_YP + col) = make_float2(acc[i][j][0], acc[i][j][1]);
                 *reinterpret_cast<float2*>(rs + (row + 8) * SP_YP + col) = make_float2(acc[i][j][2], acc[i][j][3]);
             }
         }
     __syncthreads();
-    for (int e = tid; e < J * SP_C; e += 128) {
+    for (int e = tid; e < J * SP_C; e += 256) {
         const int q = e >> 5, c = e & 31;
         const int64_t o = ((b * J + q) * m + ky) * SP_C + c;
         Zr[o] = rs[q * SP_YP + c] - rs[(J + q) * SP_YP + 32 + c];
@@ -313,7 +313,7 @@ spectral_fwd_x_mma_kernel(const float* __restrict__ Y1, const float* __restrict_
     }
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 spectral_inv_x_mma_kernel(const float* __restrict__ Or, const float* __restrict__ Oi, const float* __restrict__ tab,
                           float* __restrict__ P, int r, int m) {
     extern __shared__ __align__(16) float smem[];
@@ -326,9 +326,9 @@ spectral_inv_x_mma_kernel(const float* __restrict__ Or, const float* __restrict_
     const int ky = blockIdx.x; const int64_t b = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    for (int i = tid; i < K8 * GP / 4; i += 128) cp_async_zfill<16>(gs + 4 * i, tab + T.gc + 4 * i, true);     // padded G, as stored
+    for (int i = tid; i < K8 * GP / 4; i += 256) cp_async_zfill<16>(gs + 4 * i, tab + T.gc + 4 * i, true);     // padded G, as stored
     cp_async_commit();
-    for (int i = tid; i < K8 * 64; i += 128) {
+    for (int i = tid; i < K8 * 64; i += 256) {
         const int k = i >> 6, n = i & 63;
         float v = 0.0f;
         if (k < M2) {
@@ -342,7 +342,7 @@ spectral_inv_x_mma_kernel(const float* __restrict__ Or, const float* __restrict_
     cp_async_wait<0>();
     __syncthreads();
     float* pb = P + (b * r) * (int64_t)J * SP_C;
-    for (int mt = warp; mt < r16 / 16; mt += 4) {
+    for (int mt = warp; mt < r16 / 16; mt += 8) {
         float acc[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -471,7 +471,7 @@ extern "C" int spgt_spectral_conv2d_fwd(const float* x, const float* wr, const f
             const int MT = ceil_div(2 * (int)J, 16), r8 = ceil_div(r, 8) * 8;
             const size_t smem_a = ((size_t)16 * MT * sp_round_pitch(r8, 4) + (size_t)(r8 > 16 * MT ? r8 : 16 * MT) * SP_YP) * sizeof(float);
             if ((e = smem_opt_in(spectral_fwd_x_mma_kernel, smem_a, cfg_am))) return e;
-            spectral_fwd_x_mma_kernel<<<dim3(m, nb), 128, smem_a, st>>>(Y1, tab, Zr, Zi, r, m);
+            spectral_fwd_x_mma_kernel<<<dim3(m, nb), 256, smem_a, st>>>(Y1, tab, Zr, Zi, r, m);
         } else {
             if ((e = smem_opt_in(spectral_fwd_x_kernel, gsmem, cfg_a))) return e;
             spectral_fwd_x_kernel<<<dim3(m, nb), 256, gsmem, st>>>(Y1, tab, Zr, Zi, r, m);
@@ -483,7 +483,7 @@ extern "C" int spgt_spectral_conv2d_fwd(const float* x, const float* wr, const f
             const int K8 = ceil_div(2 * (int)J, 8) * 8, r16 = ceil_div(r, 16) * 16;
             const size_t smem_c = ((size_t)K8 * sp_round_pitch(r16, 8) + (size_t)K8 * SP_YP) * sizeof(float);
             if ((e = smem_opt_in(spectral_inv_x_mma_kernel, smem_c, cfg_cm))) return e;
-            spectral_inv_x_mma_kernel<<<dim3(m, nb), 128, smem_c, st>>>(Or, Oi, tab, P, r, m);
+            spectral_inv_x_mma_kernel<<<dim3(m, nb), 256, smem_c, st>>>(Or, Oi, tab, P, r, m);
         } else {
             if ((e = smem_opt_in(spectral_inv_x_kernel, gsmem, cfg_c))) return e;
             spectral_inv_x_kernel<<<dim3(m, nb), 256, gsmem, st>>>(Or, Oi, tab, P, r, m);

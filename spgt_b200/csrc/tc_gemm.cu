@@ -468,16 +468,6 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             TcRing rb;
             bool alive = true;
             for (int ui = 0; ui < n_my_units && alive; ++ui) {
-                for (int kb = 0; kb < KB - 1; ++kb, rb.template next<SB>()) {
-                    if (!mbar_wait(b_empty(rb.s), rb.ph ^ 1, abort_flag, 6, &g_tc_status)) { alive = false; break; }
-                    if (lane == 0) {
-                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(rb.s)), "r"((uint32_t)C::B_BYTES) : "memory");
-                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                     ::"r"(smem_base + rb.s * B_STAGE), "l"(ld.w_src(wtile, unit_index(ui), kb, C::B_BYTES / 4)),
-                                       "r"((uint32_t)C::B_BYTES), "r"(b_full(rb.s)) : "memory");
-                    }
-                }
-                if (!alive) break;
                 cp_async_wait<2>();                             // this unit's block has landed (two younger groups may be in flight)
                 __syncwarp();
                 if (!mbar_wait(b_empty(rb.s), rb.ph ^ 1, abort_flag, 6, &g_tc_status)) break;
@@ -504,6 +494,15 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 if (lane == 0) mbar_arrive(b_full(rb.s));
                 rb.template next<SB>();
                 fetch(ui + 3);                                  // into the slot of unit ui - 1, which has been stored
+                for (int kb = 0; kb < KB - 1; ++kb, rb.template next<SB>()) {
+                    if (!mbar_wait(b_empty(rb.s), rb.ph ^ 1, abort_flag, 6, &g_tc_status)) { alive = false; break; }
+                    if (lane == 0) {
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(rb.s)), "r"((uint32_t)C::B_BYTES) : "memory");
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(smem_base + rb.s * B_STAGE), "l"(ld.w_src(wtile, unit_index(ui), kb, C::B_BYTES / 4)),
+                                       "r"((uint32_t)C::B_BYTES), "r"(b_full(rb.s)) : "memory");
+                    }
+                }
             }
             cp_async_wait_all();
         } else
@@ -550,7 +549,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 if (!okc) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * MT * C::ACCW + d_off;
-                for (int kb = 0; kb < KB; ++kb, rb.template next<SB>()) {
+                for (int ki = 0; ki < KB; ++ki, rb.template next<SB>()) {
+                    // With a constant A block its k-block comes first: it needs no A stage, so its MMAs are issued while
+                    // the splitters still work on the unit (the W loader fills the stages in the same order).
+                    const int kb = Loader::CONST_A ? (ki == 0 ? KB - 1 : ki - 1) : ki;
                     const uint32_t sa = ra.s, pa = ra.ph;
                     const uint32_t sb = resident ? (uint32_t)kb : rb.s;
                     const bool a_ring = kb < KBA;                     // else: the constant A k-block
@@ -566,7 +568,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     const uint32_t ah = (a_ring ? tmem_a + sa * MT * 64 : tmem_c) + a_off, al = ah + 32;
                     if constexpr (C::MERGE) {
                         constexpr uint32_t idesc2 = tc_idesc(2 * NI);           // [W_hi | W_lo] as one operand of twice the rows
-                        tc_mma_tf32_ts_p(d, ah, bh, desc_hi, idesc2, kb > 0 ? 1u : 0u);
+                        tc_mma_tf32_ts_p(d, ah, bh, desc_hi, idesc2, ki > 0 ? 1u : 0u);
                         tc_mma_tf32_ts_acc(d, al, bh, desc_hi, idesc);
 #pragma unroll
                         for (int k8 = 1; k8 < TC_BK / 8; ++k8) {
@@ -574,7 +576,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                             tc_mma_tf32_ts_acc(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc);
                         }
                     } else {
-                    tc_mma_tf32_ts_p(d, al, bh, desc_hi, idesc, kb > 0 ? 1u : 0u);
+                    tc_mma_tf32_ts_p(d, al, bh, desc_hi, idesc, ki > 0 ? 1u : 0u);
                     tc_mma_tf32_ts_acc(d, ah, bl, desc_hi, idesc);
                     tc_mma_tf32_ts_acc(d, ah, bh, desc_hi, idesc);
 #pragma unroll

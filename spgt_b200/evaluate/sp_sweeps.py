@@ -1,8 +1,10 @@
-"""Op-level timing sweeps over resolution and batch, after the reference's evaluate/sp_galerkin.py and
-evaluate/sp_fno2d.py: each op of this library ("Exts") next to the plain PyTorch formulation the reference calls
-"Orig" (torch.matmul / nn.functional on the same GPU, TF32 off), forward only.
+"""Timing sweeps over resolution and batch, after the reference's evaluate/sp_galerkin.py, evaluate/sp_fno2d.py and
+evaluate/sp_darcy_breakdown.py: each op of this library ("Exts") next to the plain PyTorch formulation the reference
+calls "Orig" (torch.matmul / nn.functional on the same GPU, TF32 off), forward only; and the four components of the
+whole model (down-scaler, encoder layers, up-scaler, spectral regressor) on the fused kernels next to the
+reference-structure path (this library's attention / projection / data-movement ops, library ops for the rest).
 
-    python -m spgt_b200.evaluate.sp_sweeps [skinny_resolution skinny_batch projpos attention fno2d ...]
+    python -m spgt_b200.evaluate.sp_sweeps [skinny_resolution skinny_batch projpos attention fno2d breakdown ...]
 
 Timing: CUDA events around each call after warm-up, median of `repeat` calls, a 256 MB buffer written between calls so
 that no call finds its inputs in L2.  Output: one markdown table per sweep on stdout.
@@ -115,8 +117,40 @@ def time_fno2d_wrt_resolution(resolution_list=(32, 64, 128, 211, 256), batch=4, 
     _table(f'spectral layer (FNO2d block), batch {batch}, width {width}', 'resolution', rows)
 
 
+def time_model_breakdown_wrt_resolution(resolution_list=(128, 211, 256, 64), batch=4):
+    """Forward time of the model's four components at fine grid R x R (every node kept) and attention grid R/2, as the
+    reference's breakdown sweep sets them up (evaluate/sp_darcy_breakdown.py:21-40); Fourier modes ceil(sqrt(R)) capped at
+    the 16 the fused spectral kernels take.  "Orig" = the reference-structure path, "Exts" = the fused kernels."""
+    from ..config.config_accessor import get_darcy_config
+    from ..dataset.darcy_dataset import GaussNormalizer
+    from ..network.sp_model import Sp_GalerkinTransformer2D
+    for R in resolution_list:
+        modes = min(16, math.ceil(math.sqrt(R)))
+        cfg = get_darcy_config(1, 2, num_frequence_mode=modes, clamp_attn=False, fine_resolution=R)
+        cfg['target_normalizer'] = GaussNormalizer()
+        torch.manual_seed(R)
+        model = Sp_GalerkinTransformer2D(cfg).cuda().eval()
+        r, ra = cfg['r_node'], cfg['r_attn']
+        node, grid = torch.rand(batch, r, r, 1, device='cuda'), torch.rand(batch, r, r, 2, device='cuda')
+        pos = torch.rand(batch, ra, ra, 2, device='cuda')
+        rows = []
+        with torch.no_grad():
+            xd = model.down_scaler(node)
+            xe = model.encoder_mixer(xd, pos)
+            xu = model.up_scaler(xe)
+            rows.append(dict(key='down-scaler', orig=_time(lambda: model.down_scaler.forward_train(node)), exts=_time(lambda: model.down_scaler(node))))
+            rows.append(dict(key=f'{len(model.encoder_mixer.layers)} encoder layers', orig=_time(lambda: model.encoder_mixer.forward_train(xd, pos)),
+                             exts=_time(lambda: model.encoder_mixer(xd, pos))))
+            rows.append(dict(key='up-scaler', orig=_time(lambda: model.up_scaler.forward_train(xe)), exts=_time(lambda: model.up_scaler(xe))))
+            rows.append(dict(key='spectral regressor', orig=_time(lambda: model.decoder_regressor.forward_train(xu, grid)),
+                             exts=_time(lambda: model.decoder_regressor(xu, grid))))
+            rows.append(dict(key='whole model', orig=_time(lambda: model.forward_train(node, pos, grid)), exts=_time(lambda: model(node, pos, grid))))
+        _table(f'model components, fine grid {r} x {r}, attention grid {ra} x {ra}, {modes} modes, batch {batch}', 'component', rows)
+
+
 SWEEPS = {'skinny_resolution': time_skinny_gemm_wrt_resolution, 'skinny_batch': time_skinny_gemm_wrt_batch,
-          'projpos': time_projpos_lnorm_wrt_resolution, 'attention': time_attention_wrt_resolution, 'fno2d': time_fno2d_wrt_resolution}
+          'projpos': time_projpos_lnorm_wrt_resolution, 'attention': time_attention_wrt_resolution, 'fno2d': time_fno2d_wrt_resolution,
+          'breakdown': time_model_breakdown_wrt_resolution}
 
 
 def main(argv):

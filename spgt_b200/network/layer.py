@@ -1,7 +1,11 @@
-"""Shared layers of the Darcy model with the reference's parameter names (network/layer.py), inference only.
+"""Shared layers of the Darcy model with the reference's parameter names (network/layer.py).
 
 Each module keeps ordinary torch Parameters (so a reference state_dict loads unchanged) and a cache of the same
-weights re-laid-out for the kernels ([K, N] row-major, column count padded to a multiple of 4).
+weights re-laid-out for the kernels ([K, N] row-major, column count padded to a multiple of 4).  `forward` is the
+inference path on the fused kernels; `forward_train` is the differentiable path of the training loop, which - like
+the reference's own SpGT training - runs the convolutions, interpolations, dense layers and FFTs as library ops
+under torch autograd and the attention / projection / data-movement steps on this library's ops and their backward
+kernels.
 """
 import torch
 from torch import Tensor
@@ -22,10 +26,15 @@ class _KernelWeights(torch.nn.Module):
         return super()._apply(fn, *args, **kwargs)
 
     def _cached(self, key, make):
-        if key not in self._kw:
+        """Derived layout of the module's weights, rebuilt when a parameter has been modified in place since it was
+        made (an optimizer step bumps the parameters' version counters)."""
+        tag = sum(p._version for p in self.parameters())
+        hit = self._kw.get(key)
+        if hit is None or hit[0] != tag:
             with torch.no_grad():
-                self._kw[key] = make()
-        return self._kw[key]
+                hit = (tag, make())
+            self._kw[key] = hit
+        return hit[1]
 
 
 def _linear_kn(weight: Tensor) -> Tensor:
@@ -69,6 +78,10 @@ class ConvResBlock2D(_KernelWeights):
     def kernel_weight(self):
         return self._cached('w', lambda: _conv_kn(self.conv_layer.weight))
 
+    def forward_train(self, X: Tensor) -> Tensor:
+        """NCHW in and out, differentiable (network/layer.py:16-24 with drop rate 0)."""
+        return _act(self.activation)(self.conv_layer(X))
+
     def forward_nhwc(self, X: Tensor, cin_off: int, out: Tensor, cout_off: int, act=None) -> Tensor:
         """Generic path (any even channel counts / offsets): warp-MMA implicit GEMM."""
         w = self.conv_layer.weight
@@ -82,6 +95,11 @@ class ConvResBlock2D(_KernelWeights):
                              lambda: _conv_tc(self.conv_layer.weight, self.conv_layer.bias, cin_pad, cout_pad))
         out = torch.empty(*X.shape[:3], cout_pad, device=X.device, dtype=X.dtype)
         return ops.conv3x3_tc(X, 0, cin_pad, wt, b, out, 0, cout_pad, self.activation if act is None else act)
+
+
+def _act(name):
+    """The reference selects SiLU for 'silu' and ReLU for any other string (network/layer.py:14,163)."""
+    return torch.nn.functional.silu if name == 'silu' else torch.relu
 
 
 class FeedForward(_KernelWeights):
@@ -103,3 +121,6 @@ class FeedForward(_KernelWeights):
             return ops.ffn_tc(X, w1, self.layer1.bias.detach(), w2, self.layer2.bias.detach(), self.activation, residual)
         h = ops.linear_tc(X, w1, self.layer1.bias.detach(), self.activation)
         return ops.linear_tc(h, w2, self.layer2.bias.detach(), None, residual)
+
+    def forward_train(self, X: Tensor) -> Tensor:
+        return self.layer2(_act(self.activation)(self.layer1(X)))

@@ -1,9 +1,10 @@
-"""DownScaler2D / UpScaler2D with the reference's parameter names (network/model.py:7-65), inference only."""
+"""DownScaler2D / UpScaler2D with the reference's parameter names (network/model.py:7-65)."""
 import torch
 from torch import Tensor
+from torch.nn.functional import interpolate
 
 from .. import ops
-from .layer import ConvResBlock2D, _KernelWeights
+from .layer import ConvResBlock2D, _KernelWeights, _act
 
 
 class DownScaler2D(_KernelWeights):
@@ -39,6 +40,19 @@ class DownScaler2D(_KernelWeights):
         X3 = self.conv3.forward_tc(X2, pad4(d2), pad4(d3))
         return ops.bilinear_concat3(X1, X2, X3, d1, d2, d3, ra[0], ra[1], self.activation)
 
+    def forward_train(self, X: Tensor) -> Tensor:
+        """Differentiable path, the reference's op sequence (network/model.py:23-39, drop rate 0)."""
+        act = _act(self.activation)
+        X = X.permute(0, 3, 1, 2)
+        X = self.conv0.forward_train(X)
+        X = act(interpolate(X, size=self.resolution_size[1], mode='bilinear', align_corners=True))
+        X1 = self.conv1.forward_train(X)
+        X2 = self.conv2.forward_train(X1)
+        X3 = self.conv3.forward_train(X2)
+        X = torch.concat([X1, X2, X3], dim=1)
+        X = act(interpolate(X, size=self.resolution_size[2], mode='bilinear', align_corners=True))
+        return X.permute(0, 2, 3, 1).contiguous()
+
 
 class UpScaler2D(_KernelWeights):
     """[N,r_attn,r_attn,in_dim] -> [N,r,r,out_dim]: bilinear to r_mid -> conv+act -> act -> bilinear to r.
@@ -66,3 +80,11 @@ class UpScaler2D(_KernelWeights):
     def forward(self, X: Tensor) -> Tensor:
         r = self.resolution_size[4]
         return ops.bilinear(self.forward_mid(X), r[0], r[1], None)
+
+    def forward_train(self, X: Tensor) -> Tensor:
+        """Differentiable path (network/model.py:53-65): the activation is applied inside the block and once more."""
+        X = X.permute(0, 3, 1, 2)
+        X = interpolate(X, size=self.resolution_size[3], mode='bilinear', align_corners=True)
+        X = _act(self.activation)(self.conv.forward_train(X))
+        X = interpolate(X, size=self.resolution_size[4], mode='bilinear', align_corners=True)
+        return X.permute(0, 2, 3, 1).contiguous()

@@ -1,5 +1,7 @@
 """Sp_GalerkinAttention / Sp_EncoderLayer / Sp_SpectralConv2D: same constructors, parameter names and forward
-signatures as the reference's network/sp_layer.py, inference only, every step on the sm_100a kernels.
+signatures as the reference's network/sp_layer.py.  `forward` is the inference path, every step on the sm_100a kernels;
+`forward_train` is the differentiable path the training loop uses (the reference's own op sequence: this library's
+attention / projection / data-movement ops with their backward kernels, library ops for the rest).
 
 Dropout: the reference calls F.dropout without `training=`, which keeps it active under model.eval()
 (network/sp_layer.py:76,133).  These modules treat every drop rate as 0; use rates of 0 in the reference when
@@ -11,7 +13,7 @@ import torch
 from torch import Tensor
 
 from .. import ops
-from .layer import FeedForward, _KernelWeights, _linear_kn, _linear_tc
+from .layer import FeedForward, _KernelWeights, _act, _linear_kn, _linear_tc
 
 
 class Sp_GalerkinAttention(_KernelWeights):
@@ -71,6 +73,26 @@ class Sp_GalerkinAttention(_KernelWeights):
         return ops.linear_tc(X, wfc, d(self.fc_layer.bias), None, residual)
 
 
+def _attention_forward_train(self, Q: Tensor, K: Tensor, V: Tensor, position: Tensor) -> Tensor:
+    """Sp_GalerkinAttention.forward of the reference (network/sp_layer.py:52-78, drop rates 0) on the differentiable ops."""
+    from ..extension.bind.galerkin_attention import (multihead_galerkin_attention_cccr_cuda,
+                                                     multihead_projection_layernorm_with_position_rrc_cuda,
+                                                     multihead_projection_with_position_rrc_cuda)
+    H, dh, dp = self.num_head, self.dim_head, self.dim_position
+    N, S, _ = Q.shape
+    q = multihead_projection_with_position_rrc_cuda(Q, self.weight_Q, self.bias_Q, position, H, dh, dp)
+    k = multihead_projection_layernorm_with_position_rrc_cuda(K, self.weight_K, self.bias_K, self.ln_weight_K, self.ln_bias_K,
+                                                             position, self.norm_eps, H, dh, dp)
+    v = multihead_projection_layernorm_with_position_rrc_cuda(V, self.weight_V, self.bias_V, self.ln_weight_V, self.ln_bias_V,
+                                                             position, self.norm_eps, H, dh, dp)
+    X = multihead_galerkin_attention_cccr_cuda(q, k, v)                  # [N, H, S, d_pos + d_head]
+    X = X.transpose(1, 2).contiguous().view(N, S, H * (dp + dh))
+    return self.fc_layer(X)
+
+
+Sp_GalerkinAttention.forward_train = _attention_forward_train
+
+
 class Sp_EncoderLayer(torch.nn.Module):
     def __init__(self, dim_hidden, num_head, dim_position, norm_eps, attn_droprate, fc_droprate, xavier, diagonal,
                  symmetric, ffn_dim_hidden, ffn_droprate, ffn_activation) -> None:
@@ -83,6 +105,10 @@ class Sp_EncoderLayer(torch.nn.Module):
         """X [N,S,D], position [N,S,d_pos] -> X + attention(X) then + ffn(.)  (network/sp_layer.py:94-104)."""
         X = self.attention_layer(X, X, X, position, residual=X)
         return self.ffn_layer(X, residual=X)
+
+    def forward_train(self, X: Tensor, position: Tensor) -> Tensor:
+        X = X + self.attention_layer.forward_train(X, X, X, position)
+        return X + self.ffn_layer.forward_train(X)
 
 
 class Sp_SpectralConv2D(_KernelWeights):
@@ -121,3 +147,19 @@ class Sp_SpectralConv2D(_KernelWeights):
         Y = batched_transpose(Y, [N], [out_dim], [r, r])
         res = ops.linear(X, wr, br, out_dim, None, Y)             # X @ Wr + br + Y
         return torch.nn.functional.silu(res) if self.activation == 'silu' else torch.relu(res)
+
+    def forward_train(self, X: Tensor) -> Tensor:
+        """Differentiable path: the reference's op sequence (network/sp_layer.py:125-156, drop rate 0)."""
+        from ..extension.bind.datamove import batched_transpose, transpose_gather_dual, transpose_scatter_dual
+        N, r, _, in_dim = X.shape
+        m, out_dim = self.mode, self.out_dim
+        res = self.residual_layer(X)
+        Xt = batched_transpose(X.contiguous(), [N], [r, r], [in_dim])
+        X_ft = torch.fft.rfft2(Xt, s=(r, r), norm='ortho').contiguous()
+        a, b = transpose_gather_dual(X_ft, [N, in_dim], r, r // 2 + 1, m, m, 0, 0, r - m, 0)
+        a = a @ torch.view_as_complex(self.fourier_weight[0])
+        b = b @ torch.view_as_complex(self.fourier_weight[1])
+        Out_ft = transpose_scatter_dual(a.contiguous(), b.contiguous(), [N, out_dim], r, r // 2 + 1, m, m, 0, 0, r - m, 0)
+        Y = torch.fft.irfft2(Out_ft, s=(r, r), norm='ortho').contiguous()
+        Y = batched_transpose(Y, [N], [out_dim], [r, r])
+        return _act(self.activation)(Y + res)

@@ -1,5 +1,7 @@
 """Sp_EncoderMixer / Sp_DecoderRegressor / Sp_GalerkinTransformer2D: same constructors, parameter names
-(state_dict keys) and forward signatures as the reference's network/sp_model.py, inference only."""
+(state_dict keys) and forward signatures as the reference's network/sp_model.py.  Without gradients (eval, or
+torch.no_grad) the forward runs on the fused inference kernels; in training mode with gradients enabled it runs the
+differentiable path (`forward_train` of the modules)."""
 import numpy as np
 import torch
 from torch import Tensor
@@ -24,6 +26,14 @@ class Sp_EncoderMixer(torch.nn.Module):
         position = position.reshape(N, r_attn * r_attn, position.size(-1))
         for layer in self.layers:
             X = layer(X, position)
+        return X.view(N, r_attn, r_attn, dim_hidden)
+
+    def forward_train(self, X: Tensor, position: Tensor) -> Tensor:
+        N, r_attn, _, dim_hidden = X.shape
+        X = X.reshape(N, r_attn * r_attn, dim_hidden)
+        position = position.reshape(N, r_attn * r_attn, position.size(-1)).contiguous()
+        for layer in self.layers:
+            X = layer.forward_train(X, position)
         return X.view(N, r_attn, r_attn, dim_hidden)
 
 
@@ -55,6 +65,13 @@ class Sp_DecoderRegressor(_KernelWeights):
     def forward(self, X: Tensor, grid: Tensor = None) -> Tensor:
         """X [N,r,r,in_dim], grid [N,r,r,d_pos] -> [N,r,r,1]  (network/sp_model.py:53-64)."""
         return self._spectral_and_head(self._fc_split(X, grid), 1.0, 0.0, False)
+
+    def forward_train(self, X: Tensor, grid: Tensor) -> Tensor:
+        """Differentiable path (network/sp_model.py:53-64)."""
+        X = self.spatial_fc_layer(torch.concat([X, grid], dim=-1))
+        for layer in self.layers:
+            X = layer.forward_train(X)
+        return self.ffn_layer.forward_train(X)
 
     def _fc_split(self, X, grid):
         """spatial_fc_layer(concat(X, grid)) = X @ Wx + grid @ Wg + b without materialising the concatenation."""
@@ -119,10 +136,29 @@ class Sp_GalerkinTransformer2D(torch.nn.Module):
             cfg['num_frequence_mode'], cfg['drop_decoder_layer'], cfg['acti_decoder_layer'])
         self._affine = None
 
-    @torch.no_grad()
     def forward(self, X: Tensor, position: Tensor, grid: Tensor, taps: dict = None) -> Tensor:
         """X [N,r,r,1], position [N,r_attn,r_attn,2], grid [N,r,r,2] -> [N,r,r,1]; CUDA fp32 contiguous tensors.
-        `taps`, when a dict, receives intermediate tensors (down-scaler output, each encoder layer, ...)."""
+        `taps`, when a dict, receives intermediate tensors (down-scaler output, each encoder layer, ...).
+        In training mode with gradients enabled the differentiable path runs; otherwise the fused inference kernels."""
+        if self.training and torch.is_grad_enabled():
+            return self.forward_train(X, position, grid)
+        with torch.no_grad():
+            return self._forward_fused(X, position, grid, taps)
+
+    def forward_train(self, X: Tensor, position: Tensor, grid: Tensor) -> Tensor:
+        """The reference's forward (network/sp_model.py:91-113, every drop rate 0) on differentiable ops."""
+        X = self.down_scaler.forward_train(X)
+        X = self.encoder_mixer.forward_train(X, position)
+        X = self.up_scaler.forward_train(X)
+        X = self.decoder_regressor.forward_train(X, grid)
+        r = X.shape[1]
+        scale, shift, scale_map, shift_map = _normalizer_affine(self.normalizer, r, X.device)    # X * (std + eps) + mean
+        X = X * (scale if scale_map is None else scale_map.view(1, r, r, 1)) + (shift if shift_map is None else shift_map.view(1, r, r, 1))
+        if self.boundary_condition == 'dirichlet':
+            X = torch.nn.functional.pad(X[:, 1:-1, 1:-1].contiguous(), (0, 0, 1, 1, 1, 1), 'constant', 0)
+        return X
+
+    def _forward_fused(self, X: Tensor, position: Tensor, grid: Tensor, taps: dict = None) -> Tensor:
         r = X.shape[1]
         if self._affine is None or self._affine[0] != (r, X.device):
             self._affine = ((r, X.device), _normalizer_affine(self.normalizer, r, X.device))

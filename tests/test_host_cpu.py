@@ -139,3 +139,29 @@ def test_benchmark_weights_fit_the_model_and_the_cpu_baseline():
     from spgt_b200.dataset.darcy_dataset import synthetic_darcy_batch
     mine = synthetic_darcy_batch(range(2), 85, 3, 6, 4)
     assert all(torch.equal(mine[k], data[k]) for k in ('node', 'position', 'grid'))      # both arms see the same samples
+
+
+def test_weighted_l2_loss_formulas():
+    """WeightedL2Loss2D against its definition (and against the reference's class when a checkout is at hand)."""
+    from spgt_b200.engine.metric import WeightedL2Loss2D
+    g = torch.Generator().manual_seed(4)
+    N, r = 3, 11
+    pred, target = torch.randn(N, r, r, 1, generator=g), torch.randn(N, r, r, 1, generator=g)
+    tgrad, coeff = torch.randn(N, r, r, 2, generator=g), torch.rand(N, r, r, 1, generator=g) + 0.5
+    loss, reg, metric = WeightedL2Loss2D(S=r, is_regularization=True, gamma=0.5)(pred, target, None, tgrad, coeff)
+    e = ((pred - target) ** 2).mean(dim=[1, 2, 3]) / ((target ** 2).mean(dim=[1, 2, 3]) + 1e-10)
+    assert abs(float(loss) - float(e.sqrt().mean())) < 1e-6 and abs(float(metric) - float(e.sqrt().mean())) < 1e-6
+    p = pred.squeeze(-1)
+    d = torch.stack([(p[:, 2:, 1:-1] - p[:, :-2, 1:-1]) / 2, (p[:, 1:-1, 2:] - p[:, 1:-1, :-2]) / 2], dim=-1) * r
+    gn = 2 * (coeff * tgrad ** 2).mean(dim=[1, 2, 3]) + 1e-10
+    rr = 0.5 / r * ((coeff[:, 1:-1, 1:-1] * (tgrad[:, 1:-1, 1:-1] - d)) ** 2).mean(dim=[1, 2, 3]) / gn
+    assert abs(float(reg) - float(rr.sqrt().mean())) < 1e-6
+    l2, r2, m2 = WeightedL2Loss2D(S=r, metric_reduction='L2', is_normalization=False)(pred, target)
+    assert abs(float(m2) - float(e.mean().sqrt())) < 1e-6 and abs(float(l2) - float(e.mean())) < 1e-6 and float(r2) == 0.0
+    ref_root = os.environ.get('SPGT_REFERENCE', '')
+    if os.path.isdir(os.path.join(ref_root, 'engine')):
+        from tests.golden.make_golden import import_reference
+        import_reference(ref_root)
+        from SpGT.engine.metric import WeightedL2Loss2D as Ref
+        a = Ref(S=r, is_regularization=True, gamma=0.5)(pred, target, None, tgrad, coeff)
+        assert all(abs(float(x) - float(y)) < 1e-6 for x, y in zip(a, (loss, reg, metric)))
