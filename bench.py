@@ -289,6 +289,14 @@ def micro_cases(device):
         return (lambda: ops.conv3x3_tc(x, 0, C, w, b_, y, 0, C, 'silu2')), 2 * B * Hh * Hh * C * 4, 2 * B * Hh * Hh * 9 * C * C
     cases['conv128_tc'] = conv_tc
 
+    def conv_tc_down(B=64, Hh=106, Cin=44, Cout=44):
+        # down-scaler shapes: 42 / 44 channels zero-padded to 44 (64-wide column tile)
+        x, w, b_ = rnd(B, Hh, Hh, Cin), ops.TcWeight(rnd(9 * Cin, Cout) / 20), rnd(Cout)
+        y = torch.empty(B, Hh, Hh, Cout, device=device)
+        return (lambda: ops.conv3x3_tc(x, 0, Cin, w, b_, y, 0, Cout, 'silu')), B * Hh * Hh * (Cin + Cout) * 4, 2 * B * Hh * Hh * 9 * Cin * Cout
+    cases['conv44_tc'] = conv_tc_down
+    cases['conv128to44_tc'] = lambda: conv_tc_down(Cin=128)
+
     def head_tc(B=64, r=211):
         x, w1, b1, w2 = rnd(B, r, r, 32), ops.TcWeight(rnd(32, 128) / 6), rnd(128), rnd(128)
         return (lambda: ops.decoder_head_tc(x, w1, b1, w2, 0.1, 1.0, 0.0, True, 'silu')), B * r * r * 33 * 4, 2 * B * r * r * 32 * 128

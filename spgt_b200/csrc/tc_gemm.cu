@@ -33,13 +33,12 @@ constexpr int TC_BLOAD_WARP = 8, TC_MMA_WARP = 9, TC_EPI_WARPS = 8;
 // MMA-issuing warps: two with two row tiles per unit (one tile each), one otherwise; the epilogue warps follow them
 __host__ __device__ constexpr int tc_mma_warps(int mt) { return mt == 2 ? 2 : 1; }
 __host__ __device__ constexpr int tc_epi_warp0(int mt) { return TC_MMA_WARP + tc_mma_warps(mt); }
-__host__ __device__ constexpr int tc_threads(int mt) { return 32 * (tc_epi_warp0(mt) + TC_EPI_WARPS); }
-constexpr int TC_SLOT_BYTES = 144;            // per-epilogue-thread staging row: 32 floats + 16 bytes (bank skew)
+__host__ __device__ constexpr int tc_threads(int mt, int epi_groups = 1) { return 32 * (tc_epi_warp0(mt) + epi_groups * TC_EPI_WARPS); }
 
 __device__ int g_tc_status = 0;          // 0 = ok; otherwise the code of the first wait that gave up
 
 
-__host__ __device__ constexpr int tc_cols_per_thread(int bn, int mt) { return mt == 1 ? bn / 2 : bn; }
+__host__ __device__ constexpr int tc_cols_per_thread(int bn, int mt, bool colsplit = false) { return (mt == 1 ? bn / 2 : bn) / (colsplit ? 2 : 1); }
 
 // Position in a ring of N stages: stage index and the parity of the pass, advanced without division.
 struct TcRing {
@@ -63,9 +62,21 @@ struct TcRing {
 struct TcLoaderDefaults {
     static constexpr bool W_PER_UNIT = false, COLUMN_SPLIT = false, STAGING = true, CONST_A = false, REVERSE_UNITS = false, W_CONVERT = false;
     static constexpr int RAW_STAGES = 0, W_STAGES = 0, A_STAGES = 0, ACC_BUFS = 0;
+    // Groups of eight epilogue warps.  With two, group g finishes the units whose accumulator buffer is g (every second
+    // unit), so one unit's activation and stores overlap the next unit's: for short k, where the epilogue is the longest stage.
+    static constexpr int EPI_GROUPS = 1;
+    // Two groups working on the same unit instead (two row tiles of 128 columns only): a thread finishes half of its row's
+    // columns, so the accumulator is held for a shorter time; for long k with one accumulator buffer, where the MMAs wait for
+    // the epilogue.  (With 64-wide tiles the extra warps slowed the producers down more than the epilogue gained.)
+    static constexpr bool EPI_COLSPLIT = false;
+    static constexpr bool RESIDUAL = true;        // false: the LINEAR epilogue's residual path is compiled out
+    // With W_CONVERT and two k-blocks: the prepared image of the first k-block is the same for every unit and stays in the
+    // last W stage (loaded once), the ring of the other stages carries the converted blocks only.
+    static constexpr bool W_TAIL_RESIDENT = false;
     __device__ __forceinline__ const float* const_row(int) const { return nullptr; }
     __device__ __forceinline__ const float* w_plain(int) const { return nullptr; }
     __device__ __forceinline__ int w_plain_rows() const { return 0; }
+    __device__ __forceinline__ int const_ksteps() const { return TC_BK / 8; }     // k-steps of 8 the constant A block really has
 };
 struct TcDense : TcLoaderDefaults {
     const float* x; int lda; int rows; int K;
@@ -82,6 +93,7 @@ struct TcDense : TcLoaderDefaults {
     __device__ __forceinline__ const float* ptr(const Row& r, const Kst& k, bool& ok) const { ok = r.ok && k.ok; return r.p + k.kc; }
 };
 struct TcConv : TcLoaderDefaults {          // 3x3, padding 1, NHWC; k = tap * Cin + c with Cin % 4 == 0
+    static constexpr bool EPI_COLSPLIT = true;
     const float* x; int cin_pitch, cin_off, Cin, Hh, Ww; int rows; int K;
     __device__ __forceinline__ const float* w_src(const float* wtile, int, int kb, int stage_floats) const { return wtile + (int64_t)kb * stage_floats; }
     __device__ __forceinline__ int64_t out_row(int row) const { return row < rows ? row : -1; }
@@ -156,11 +168,13 @@ struct TcSpecInv : TcLoaderDefaults {
 // read last are the ones still in L2.
 struct TcSpecInvC : TcLoaderDefaults {
     static constexpr bool W_PER_UNIT = true, CONST_A = true, REVERSE_UNITS = true, W_CONVERT = true;     // (W_CONVERT needs 32-wide column tiles: lane = image row)
-    static constexpr int RAW_STAGES = 4, W_STAGES = 4, A_STAGES = 1;
+    static constexpr int RAW_STAGES = 3, W_STAGES = 4, A_STAGES = 1, EPI_GROUPS = 2;
+    static constexpr bool RESIDUAL = false, W_TAIL_RESIDENT = true;
     const float* x; const float* f3; const float* wr_img; const float* p; int J; int r; int rows; int K;
     __device__ __forceinline__ const float* w_src(const float*, int, int, int) const { return wr_img; }
     __device__ __forceinline__ const float* w_plain(int unit) const { return p + (int64_t)unit * J * 32; }
     __device__ __forceinline__ int w_plain_rows() const { return J; }
+    __device__ __forceinline__ int const_ksteps() const { return (J + 7) / 8; }
     __device__ __forceinline__ int64_t out_row(int row) const {
         const int y = row & 255;
         return (row < rows && y < r) ? (int64_t)(row >> 8) * r + y : -1;
@@ -219,6 +233,10 @@ struct TcHeadEpi {
 struct TcSpecFwdEpi { float* y1; int J; int64_t nimg; };     // Y1 [image row][J][32 channels]
 enum { EPI_LINEAR = 0, EPI_PROJ = 1, EPI_HEAD = 2, EPI_SPECF = 3 };
 
+template <class Loader, int MT, int BN> __host__ __device__ constexpr int tc_epi_groups() {
+    return Loader::EPI_COLSPLIT ? ((MT == 2 && BN == 128) ? 2 : 1) : Loader::EPI_GROUPS;
+}
+
 template <int BN, int MT, class Loader = TcDense> struct TcCfg {
     // Column tiles of up to 64: W_hi and W_lo of a k-block lie one after the other in shared memory, so one MMA of
     // twice the width computes A_hi W_hi and A_hi W_lo side by side (two partial accumulators, summed by the epilogue)
@@ -235,7 +253,12 @@ template <int BN, int MT, class Loader = TcDense> struct TcCfg {
                                                : ((BN == 128) ? (MT == 1 ? 4 : 3) : ((MT == 1 || BN == 32) ? 8 : 6));  // W stages in shared memory
     static constexpr int RAW_BYTES = MT * TC_BM * TC_BK * 4;        // raw fp32 A tile(s) of one k-block
     static constexpr int SR = Loader::RAW_STAGES ? Loader::RAW_STAGES : ((MT == 1) ? 3 : 2);   // raw A stages in shared memory
-    static constexpr int STAGING_BYTES = Loader::STAGING ? 32 * TC_EPI_WARPS * TC_SLOT_BYTES : 0;
+    static constexpr bool CS = Loader::EPI_COLSPLIT && MT == 2 && BN == 128;     // sixteen epilogue warps share every unit
+    static constexpr int EG = tc_epi_groups<Loader, MT, BN>();
+    static constexpr int CPT = tc_cols_per_thread(BN, MT, CS);      // columns an epilogue thread finishes
+    static constexpr int PASS = CS ? 16 : (CPT > 32 ? 32 : CPT);    // columns per staging pass of the LINEAR epilogue
+    static constexpr int SLOT_BYTES = PASS * 4 + 16;                // per-epilogue-thread staging row + 16 bytes (bank skew)
+    static constexpr int STAGING_BYTES = Loader::STAGING ? 32 * EG * TC_EPI_WARPS * SLOT_BYTES : 0;
     static constexpr int CONST_BYTES = 2048;                        // per-CTA epilogue constants (bias, LayerNorm affine, head vectors)
     static constexpr int BAR_BYTES = 384;
     static constexpr int PLAIN_BYTES = Loader::W_CONVERT ? 4 * 32 * 32 * 4 : 0;       // ring of plain W blocks (after the barriers)
@@ -244,14 +267,17 @@ template <int BN, int MT, class Loader = TcDense> struct TcCfg {
 };
 
 template <int BN, int MT, class Loader, int EPI, class EpiParams>
-__global__ void __launch_bounds__(tc_threads(MT), 1)
+__global__ void __launch_bounds__(tc_threads(MT, tc_epi_groups<Loader, MT, BN>()), 1)
 tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_units, EpiParams ep) {
     using C = TcCfg<BN, MT, Loader>;
     constexpr int SA = C::SA, NBUF = C::NBUF, SR = C::SR;
     constexpr int SB = C::SB;
     constexpr uint32_t B_STAGE = C::B_BYTES;
     constexpr int NIWARPS = tc_mma_warps(MT);                       // MMA-issuing warps
-    constexpr int TC_THREADS = tc_threads(MT), TC_EPI_WARP0 = tc_epi_warp0(MT);
+    constexpr int EG = C::EG;
+    constexpr bool CS = C::CS;
+    constexpr int TC_THREADS = tc_threads(MT, EG), TC_EPI_WARP0 = tc_epi_warp0(MT);
+    static_assert(EG == 1 || (EG == 2 && (CS || C::NBUF == 2) && EPI == EPI_LINEAR), "two epilogue groups: one per accumulator buffer, or sharing every unit");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // 1024-aligned for the 128B swizzle
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -282,7 +308,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), NIWARPS); }
         for (int s = 0; s < SR; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
         for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), NIWARPS); }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), NIWARPS); mbar_init(acc_empty(b), 32 * TC_EPI_WARPS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), NIWARPS); mbar_init(acc_empty(b), 32 * TC_EPI_WARPS * (CS ? 2 : 1)); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -421,9 +447,6 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
 #pragma unroll
                     for (int k = 0; k < 32; ++k)
                         vf[k] = *reinterpret_cast<const float*>(src + tc_swz(q * 32 + k, lane >> 2) + (lane & 3) * 4);
-                } else {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(src + roff[c]);
                 }
                 const uint32_t a_hi = tmem_a + lane_addr + (sa * MT + m) * 64;
 #pragma unroll
@@ -431,7 +454,9 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     uint32_t hi[16], lo[16];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float4 w = v[4 * h + j];
+                        float4 w;
+                        if constexpr (Loader::COLUMN_SPLIT) w = v[4 * h + j];
+                        else w = *reinterpret_cast<const float4*>(src + roff[4 * h + j]);      // (loaded per half: fewer live registers)
                         split_tf32(w.x, hi[4 * j], lo[4 * j]); split_tf32(w.y, hi[4 * j + 1], lo[4 * j + 1]);
                         split_tf32(w.z, hi[4 * j + 2], lo[4 * j + 2]); split_tf32(w.w, hi[4 * j + 3], lo[4 * j + 3]);
                     }
@@ -451,9 +476,16 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             // unit's plain [rows][32] block is fetched with cp.async into a small ring three units ahead (a global load
             // takes longer than a unit), then lane n splits column n and stores it as row n of the W stage image (k = row of
             // the block; the k padding of the stages is cleared once).
-            for (int i = lane; i < SB * (int)B_STAGE / 16; i += 32)
+            constexpr int SBR = Loader::W_TAIL_RESIDENT ? SB - 1 : SB;          // stages of the ring
+            for (int i = lane; i < SBR * (int)B_STAGE / 16; i += 32)
                 reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
             __syncwarp();
+            if (Loader::W_TAIL_RESIDENT && lane == 0 && n_my_units > 0) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(SB - 1)), "r"((uint32_t)C::B_BYTES) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(smem_base + (SB - 1) * B_STAGE), "l"(ld.w_src(wtile, 0, 0, C::B_BYTES / 4)),
+                               "r"((uint32_t)C::B_BYTES), "r"(b_full(SB - 1)) : "memory");
+            }
             const int prow = ld.w_plain_rows();
             float* praw = reinterpret_cast<float*>(bar_mem + C::BAR_BYTES);           // [4][32 rows][32] plain blocks
             auto fetch = [&](int ui_) {
@@ -492,9 +524,9 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 fence_proxy_async();                            // generic-proxy stores before the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(b_full(rb.s));
-                rb.template next<SB>();
+                rb.template next<SBR>();
                 fetch(ui + 3);                                  // into the slot of unit ui - 1, which has been stored
-                for (int kb = 0; kb < KB - 1; ++kb, rb.template next<SB>()) {
+                for (int kb = 0; kb < (Loader::W_TAIL_RESIDENT ? 0 : KB - 1); ++kb, rb.template next<SBR>()) {
                     if (!mbar_wait(b_empty(rb.s), rb.ph ^ 1, abort_flag, 6, &g_tc_status)) { alive = false; break; }
                     if (lane == 0) {
                         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b_full(rb.s)), "r"((uint32_t)C::B_BYTES) : "memory");
@@ -549,18 +581,20 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 if (!okc) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * MT * C::ACCW + d_off;
-                for (int ki = 0; ki < KB; ++ki, rb.template next<SB>()) {
+                for (int ki = 0; ki < KB; ++ki) {
                     // With a constant A block its k-block comes first: it needs no A stage, so its MMAs are issued while
                     // the splitters still work on the unit (the W loader fills the stages in the same order).
                     const int kb = Loader::CONST_A ? (ki == 0 ? KB - 1 : ki - 1) : ki;
                     const uint32_t sa = ra.s, pa = ra.ph;
-                    const uint32_t sb = resident ? (uint32_t)kb : rb.s;
                     const bool a_ring = kb < KBA;                     // else: the constant A k-block
+                    const bool tail = Loader::W_TAIL_RESIDENT && a_ring;   // this k-block's W image stays in the last stage
+                    constexpr int SBR = Loader::W_TAIL_RESIDENT ? SB - 1 : SB;
+                    const uint32_t sb = resident ? (uint32_t)kb : (tail ? (uint32_t)(SB - 1) : rb.s);
                     bool oka = true, okb = true;
                     if (a_ring) oka = mbar_wait(a_full(sa), pa, abort_flag, 3, &g_tc_status);
                     if (!oka) { alive = false; break; }
-                    if (!resident || ui == 0) {
-                        okb = mbar_wait(b_full(sb), resident ? 0u : rb.ph, abort_flag, 7, &g_tc_status);
+                    if ((!resident && !tail) || ui == 0) {
+                        okb = mbar_wait(b_full(sb), (resident || tail) ? 0u : rb.ph, abort_flag, 7, &g_tc_status);
                         if (!okb) { alive = false; break; }
                     }
                     tc_fence_after();
@@ -568,12 +602,15 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     const uint32_t ah = (a_ring ? tmem_a + sa * MT * 64 : tmem_c) + a_off, al = ah + 32;
                     if constexpr (C::MERGE) {
                         constexpr uint32_t idesc2 = tc_idesc(2 * NI);           // [W_hi | W_lo] as one operand of twice the rows
+                        const int nk8 = (Loader::CONST_A && !a_ring) ? ld.const_ksteps() : TC_BK / 8;   // (zero k-steps of the constant block are skipped)
                         tc_mma_tf32_ts_p(d, ah, bh, desc_hi, idesc2, ki > 0 ? 1u : 0u);
                         tc_mma_tf32_ts_acc(d, al, bh, desc_hi, idesc);
 #pragma unroll
                         for (int k8 = 1; k8 < TC_BK / 8; ++k8) {
-                            tc_mma_tf32_ts_acc(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc2);
-                            tc_mma_tf32_ts_acc(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc);
+                            if (k8 < nk8) {
+                                tc_mma_tf32_ts_acc(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc2);
+                                tc_mma_tf32_ts_acc(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc);
+                            }
                         }
                     } else {
                     tc_mma_tf32_ts_p(d, al, bh, desc_hi, idesc, ki > 0 ? 1u : 0u);
@@ -588,7 +625,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     }
                     // the A stage (and a streamed W stage) is reusable once every issuer's MMAs have read it
                     if (a_ring) { tc_commit(a_empty(sa)); ra.template next<SA>(); }
-                    if (!resident) tc_commit(b_empty(sb));
+                    if (!resident && !tail) { tc_commit(b_empty(sb)); rb.template next<SBR>(); }
                 }
                 if (alive) tc_commit(acc_full(buf));
             }
@@ -598,22 +635,26 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     } else {
         // ------------------------------------------ epilogue ------------------------------------------
         const int q = warp & 3;                                   // TMEM lane quarter this warp may access
-        const int half = (warp - TC_EPI_WARP0) >> 2;              // 0 or 1
+        const int ew = warp - TC_EPI_WARP0;
+        const int egroup = CS ? 0 : ew >> 3;                      // which units this warp finishes (0 unless two groups alternate)
+        const int half = (ew >> 2) & 1;                           // 0 or 1
+        const int chalf = CS ? ew >> 3 : 0;                       // column half of the row tile (two groups sharing the units)
+        constexpr int UI_STEP = CS ? 1 : EG;
         const int r_in_tile = q * 32 + lane;
         const int mt_e = (MT == 1) ? 0 : half;                    // M-tile served by this thread
-        constexpr int CPT = tc_cols_per_thread(BN, MT);           // columns served by this thread
-        const int col_lo = (MT == 1) ? half * CPT : 0;
-        const int epi_idx = (warp - TC_EPI_WARP0) * 32 + lane;
-        float* slot_ptr = reinterpret_cast<float*>(staging + epi_idx * TC_SLOT_BYTES);
+        constexpr int CPT = C::CPT;                               // columns served by this thread
+        const int col_lo = (MT == 1) ? half * CPT : chalf * CPT;
+        const int epi_idx = ew * 32 + lane;
+        float* slot_ptr = reinterpret_cast<float*>(staging + epi_idx * C::SLOT_BYTES);
         bool alive = true;
         // LINEAR epilogue with a residual: the residual values of the elements this thread stores in the next store
         // phase are fetched one phase ahead (the first ones while the accumulator is still being computed); a load
         // issued where it is needed queues behind the producers' traffic and stalls the store phase for microseconds.
-        constexpr int EP_PASS = tc_cols_per_thread(BN, MT) > 32 ? 32 : tc_cols_per_thread(BN, MT);
+        constexpr int EP_PASS = C::PASS;
         constexpr int EP_LPR = EP_PASS / 4, EP_RPI = 32 / EP_LPR, EP_NIT = 32 / EP_RPI;
         float4 rres[EP_NIT];
         auto res_fetch = [&](int ui_, int c0_) {
-            if constexpr (EPI == EPI_LINEAR) {
+            if constexpr (EPI == EPI_LINEAR && Loader::RESIDUAL) {
                 const TcLinearEpi& e = ep;
                 const int row0_ = (unit_tile0(ui_) + mt_e) * TC_BM + q * 32 + lane / EP_LPR;
                 const int col_ = nt * BN + c0_ + (lane % EP_LPR) * 4;
@@ -625,10 +666,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 }
             }
         };
-        if constexpr (EPI == EPI_LINEAR) {
-            if (ep.residual != nullptr && n_my_units > 0) res_fetch(0, (MT == 1) ? half * tc_cols_per_thread(BN, MT) : 0);
+        if constexpr (EPI == EPI_LINEAR && Loader::RESIDUAL) {
+            if (ep.residual != nullptr && egroup < n_my_units) res_fetch(egroup, col_lo);
         }
-        for (int ui = 0; ui < n_my_units && alive; ++ui) {
+        for (int ui = egroup; ui < n_my_units && alive; ui += UI_STEP) {
             const uint32_t buf = (uint32_t)(ui % NBUF), aph = (uint32_t)((ui / NBUF) & 1);
             float posv[8];                     // PROJ: this row's position values, fetched while the accumulator is still being computed
             if constexpr (EPI == EPI_PROJ) {
@@ -658,14 +699,16 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
 
             if constexpr (EPI == EPI_LINEAR) {
                 const TcLinearEpi& e = ep;
-                constexpr int PASS = CPT > 32 ? 32 : CPT;        // columns per staging pass
+                constexpr int PASS = C::PASS;                    // columns per staging pass
                 constexpr int LPR = PASS / 4;                    // lanes per row in the store phase (float4 each)
                 constexpr int RPI = 32 / LPR;                    // rows per store instruction
-                const uint8_t* warp_stage = staging + (warp - TC_EPI_WARP0) * 32 * TC_SLOT_BYTES;
+                const uint8_t* warp_stage = staging + ew * 32 * C::SLOT_BYTES;
                 const int tile_row0 = tile * TC_BM + q * 32;
                 // One pass (at most 32 columns per thread): the thread first takes its whole accumulator row into registers
                 // and frees the buffer, so the next unit's MMAs start while this one is finished and stored.
-                constexpr bool EARLY = CPT <= 32 && NBUF == 1;     // (with two buffers the next unit does not wait for this one anyway)
+                // (with two buffers the early release measured slower, with one and with two epilogue groups: 396 against 378 us
+                // for the spectral layer at batch 64)
+                constexpr bool EARLY = CPT <= 32 && NBUF == 1;
                 float vall[EARLY ? CPT : 16];
                 if constexpr (EARLY) {
 #pragma unroll
@@ -678,15 +721,16 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     tc_fence_before();
                     mbar_arrive(acc_empty(buf));
                 }
-#pragma unroll 1
-                for (int c0 = col_lo; c0 < col_lo + CPT; c0 += PASS) {
+#pragma unroll (EARLY ? CPT / PASS : 1)
+                for (int pi = 0; pi < CPT / PASS; ++pi) {
+                    const int c0 = col_lo + pi * PASS;
                     // phase 1: each thread finishes its own row (bias, activation) into its padded staging slot
 #pragma unroll (EARLY ? 2 : 1)
                     for (int cc = 0; cc < PASS; cc += 16) {
                         float v[16];
                         if constexpr (EARLY) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] = vall[cc + j];
+                            for (int j = 0; j < 16; ++j) v[j] = vall[pi * PASS + cc + j];
                         } else {
                             if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + cc, BN, v); else tc_ld16(taddr + c0 + cc, v);
                         }
@@ -710,13 +754,13 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     const int col = nt * BN + c0 + (lane % LPR) * 4;
                     static_assert(PASS == EP_PASS && 32 / RPI == EP_NIT, "residual prefetch follows the store phase's mapping");
                     if (col < e.N) {
-                        if (e.residual) {
+                        if (Loader::RESIDUAL && e.residual) {
 #pragma unroll
                             for (int i = 0; i < 32 / RPI; ++i) {
                                 const int rr = i * RPI + lane / LPR;
                                 const int64_t orow = ld.out_row(tile_row0 + rr);
                                 if (orow >= 0) {
-                                    float4 o = *reinterpret_cast<const float4*>(warp_stage + rr * TC_SLOT_BYTES + (lane % LPR) * 16);
+                                    float4 o = *reinterpret_cast<const float4*>(warp_stage + rr * C::SLOT_BYTES + (lane % LPR) * 16);
                                     o.x += rres[i].x; o.y += rres[i].y; o.z += rres[i].z; o.w += rres[i].w;
                                     *reinterpret_cast<float4*>(e.y + orow * e.ldc + col) = o;
                                 }
@@ -728,13 +772,13 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                                 const int64_t orow = ld.out_row(tile_row0 + rr);
                                 if (orow >= 0)
                                     *reinterpret_cast<float4*>(e.y + orow * e.ldc + col) =
-                                        *reinterpret_cast<const float4*>(warp_stage + rr * TC_SLOT_BYTES + (lane % LPR) * 16);
+                                        *reinterpret_cast<const float4*>(warp_stage + rr * C::SLOT_BYTES + (lane % LPR) * 16);
                             }
                         }
                     }
-                    if (e.residual) {                // the next store phase's residual values: next pass, else next unit
+                    if (Loader::RESIDUAL && e.residual) {                // the next store phase's residual values: next pass, else next unit
                         if (c0 + PASS < col_lo + CPT) res_fetch(ui, c0 + PASS);
-                        else if (ui + 1 < n_my_units) res_fetch(ui + 1, col_lo);
+                        else if (ui + UI_STEP < n_my_units) res_fetch(ui + UI_STEP, col_lo);
                     }
                     __syncwarp();
                 }
@@ -881,7 +925,7 @@ static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_til
     if (per_nt < 1) per_nt = 1;
     if (per_nt > m_units) per_nt = m_units;
     const int grid = per_nt * n_tiles;
-    kern<<<grid, tc_threads(MT), TcCfg<BN, MT, Loader>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
+    kern<<<grid, tc_threads(MT, tc_epi_groups<Loader, MT, BN>()), TcCfg<BN, MT, Loader>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
     return launch_status();
 }
 
