@@ -355,6 +355,8 @@ def main():
     ap.add_argument('--batch', type=int, default=GLOBAL_BATCH, help='global batch per step, sharded evenly over the ranks')
     ap.add_argument('--min-seconds', type=float, default=1.0, help='repeat the K-step block until this much time has been measured')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--e2e-download', default='metric', choices=['metric', 'predictions'],
+                    help="what the end-to-end leg reads back per step: the reduced metric (as the reference's driver does) or also the gathered predictions")
     ap.add_argument('--no-graphs', action='store_true', help='launch the kernels eagerly instead of replaying CUDA graphs')
     ap.add_argument('--no-weak-leg', action='store_true', help='skip the secondary 64-samples-per-GPU measurement of multi-GPU runs')
     ap.add_argument('--breakdown', action='store_true', help='also print a per-entry-point time table to stderr')
@@ -463,7 +465,7 @@ def main():
     # synthetic stand-in for the solution the metric compares with are the same host tensors in every step and are
     # uploaded once per staging slot.
     engine = HostInference(model, device, use_graphs=not args.no_graphs, static_keys=('position', 'grid', 'target'))
-    gather = ShardedGather(G, rank, world, (r, r, 1), device)
+    gather = ShardedGather(G, rank, world, (r, r, 1), device, download=args.e2e_download)
     engine.run([host] * args.warmup, post=gather)
     barrier()
     t0 = time.perf_counter()
@@ -485,7 +487,8 @@ def main():
     else:
         sums = csum
     if rank == 0:
-        full = results[-1]                                   # pinned host copy of the last step's gathered predictions
+        # the last step's gathered predictions: their pinned host copy, or (metric-only download) fetched from the device now
+        full = results[-1] if args.e2e_download == 'predictions' else gather.last_full.cpu()
         ok = torch.equal(full[begin:end], pred_local.cpu())
         for rk in range(world):
             b, e = shard_range(G, rk, world)
@@ -552,7 +555,8 @@ def main():
                        'timing': f'median of {len(blocks)} blocks of {args.steps} steps (CUDA events, max over ranks per block)'},
             'clocks': clocks.summary(), 'gpu_launches': launches_per_forward * args.steps, 'launches_per_forward': launches_per_forward,
             'block_ms': {'min': blocks_sorted[0], 'median': elapsed_ms, 'max': blocks_sorted[-1], 'n': len(blocks)},
-            'e2e': {'value': e2e_value, 'unit': 'samples/s', 'h2d_bytes_per_step': nb['h2d'] * world, 'd2h_bytes_per_step': G * r * r * 4 + 16 * world,
+            'e2e': {'value': e2e_value, 'unit': 'samples/s', 'h2d_bytes_per_step': nb['h2d'] * world, 'd2h_bytes_per_step': (G * r * r * 4 + 16 * world) if args.e2e_download == 'predictions' else 32 * world,
+                    'downloads': args.e2e_download,
                     'ms_per_step': e2e_s * 1e3 / args.steps,
                     'collectives_per_step': 0 if world == 1 else 2, 'gather_check': gather_check, 'metric': metric_value},
             'roofline': roof_attn, 'roofline_spectral': roof_spec, 'cpu_baseline': cpu, 'weak_64_per_gpu': weak,

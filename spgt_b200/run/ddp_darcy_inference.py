@@ -67,14 +67,20 @@ def reduce_metric(metric_sum: torch.Tensor, count: torch.Tensor, world: int) -> 
 class ShardedGather:
     """`post` hook of HostInference for a rank of a sharded run: after the forward of the rank's slice of a global batch it
     gathers all ranks' predictions into the global batch (one all_gather_into_tensor) and sums the per-sample metric over
-    all ranks (one all_reduce of (sum, count)), both on the compute stream.  Rank 0 gets the gathered predictions as the
-    tensor to download, the other ranks the reduced (sum, count); `metric(i)` gives the global mean of batch i afterwards.
+    all ranks (one all_reduce of (sum, count)), both on the compute stream.  What the host loop downloads per batch:
+    download='predictions': rank 0 the gathered predictions, the other ranks the reduced (sum, count);
+    download='metric': every rank the reduced (sum, count) only, as the reference's driver reads back nothing but the metric
+    (run/ddp_darcy_inference.py:62, engine/darcy_engine.py:33-46); the gathered predictions of the last batch stay on the
+    device in `last_full`.  `metric(i)` gives the global mean of batch i afterwards.
     The global batch must split evenly over the ranks (collectives need equal block sizes)."""
 
-    def __init__(self, n_total: int, rank: int, world: int, sample_shape, device):
+    def __init__(self, n_total: int, rank: int, world: int, sample_shape, device, download: str = 'predictions'):
         if n_total % world != 0:
             raise ValueError('ShardedGather needs a global batch that is a multiple of the number of ranks')
-        self.n_total, self.rank, self.world = n_total, rank, world
+        if download not in ('predictions', 'metric'):
+            raise ValueError("download must be 'predictions' or 'metric'")
+        self.n_total, self.rank, self.world, self.download = n_total, rank, world, download
+        self.last_full = None
         self.full = [torch.empty((n_total, *sample_shape), dtype=torch.float32, device=device) for _ in range(2)] if world > 1 else None
         self.packed = [torch.zeros(2, dtype=torch.float64, device=device) for _ in range(2)]
         self.packed_host = {}
@@ -96,7 +102,8 @@ class ShardedGather:
         if i not in self.packed_host:
             self.packed_host[i] = torch.empty(2, dtype=torch.float64, pin_memory=pred.is_cuda)
         self.packed_host[i].copy_(packed, non_blocking=True)
-        return full if self.rank == 0 else packed
+        self.last_full = full
+        return full if (self.rank == 0 and self.download == 'predictions') else packed
 
     def metric(self, i: int) -> float:
         """Global mean of the per-sample metric of batch i (valid once the run has returned)."""

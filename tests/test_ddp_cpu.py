@@ -77,7 +77,13 @@ def _gather_worker(rank, world, port, out_dir):
         pred = (torch.arange(b, e, dtype=torch.float32) + 10 * step).view(-1, 1, 1, 1).expand(-1, 3, 3, 1).contiguous()
         slot = {'target': pred + 0.5}
         outs.append(gather(pred, slot, step).clone())
-    torch.save({'outs': outs, 'metrics': [gather.metric(i) for i in range(3)]}, os.path.join(out_dir, f'g{rank}.pt'))
+    # metric-only download (what the reference's driver reads back): every rank gets the reduced (sum, count), the gathered
+    # predictions stay in `last_full`
+    gm = ShardedGather(n_total, r, w, (3, 3, 1), 'cpu', download='metric')
+    pred = torch.arange(b, e, dtype=torch.float32).view(-1, 1, 1, 1).expand(-1, 3, 3, 1).contiguous()
+    got = gm(pred, {'target': pred + 0.5}, 0).clone()
+    torch.save({'outs': outs, 'metrics': [gather.metric(i) for i in range(3)], 'metric_only': got, 'last_full': gm.last_full.clone(),
+                'metric_only_value': gm.metric(0)}, os.path.join(out_dir, f'g{rank}.pt'))
     dist.destroy_process_group()
 
 
@@ -93,3 +99,8 @@ def test_sharded_gather_hook_two_ranks(tmp_path):
         assert res[1]['outs'][step].shape == (2,) and abs(float(res[1]['outs'][step][0] / res[1]['outs'][step][1]) - ref_metric) < 1e-6
         for r in range(world):
             assert abs(res[r]['metrics'][step] - ref_metric) < 1e-6
+    ref0 = float((0.5 / (torch.arange(6, dtype=torch.float64) + 0.5)).mean())
+    for r in range(world):
+        assert res[r]['metric_only'].shape == (2,) and float(res[r]['metric_only'][1]) == 6.0
+        assert abs(res[r]['metric_only_value'] - ref0) < 1e-6
+        assert torch.equal(res[r]['last_full'], torch.arange(6, dtype=torch.float32).view(-1, 1, 1, 1).expand(-1, 3, 3, 1))
