@@ -256,7 +256,7 @@ template <int BN, int MT, class Loader = TcDense> struct TcCfg {
     static constexpr bool CS = Loader::EPI_COLSPLIT && MT == 2 && BN == 128;     // sixteen epilogue warps share every unit
     static constexpr int EG = tc_epi_groups<Loader, MT, BN>();
     static constexpr int CPT = tc_cols_per_thread(BN, MT, CS);      // columns an epilogue thread finishes
-    static constexpr int PASS = CS ? 16 : (CPT > 32 ? 32 : CPT);    // columns per staging pass of the LINEAR epilogue
+    static constexpr int PASS = CS ? 16 : (CPT > 32 ? (CPT % 32 == 0 ? 32 : 16) : CPT);    // columns per staging pass of the LINEAR epilogue
     static constexpr int SLOT_BYTES = PASS * 4 + 16;                // per-epilogue-thread staging row + 16 bytes (bank skew)
     static constexpr int STAGING_BYTES = Loader::STAGING ? 32 * EG * TC_EPI_WARPS * SLOT_BYTES : 0;
     static constexpr int CONST_BYTES = 2048;                        // per-CTA epilogue constants (bias, LayerNorm affine, head vectors)
@@ -909,8 +909,11 @@ __global__ void tc_weight_prepare_kernel(const float* __restrict__ w, int ldw, i
 // for every row tile, the second read of the rows coming from L2.  At K = 256 the doubled row traffic costs more
 // than the W stream (measured: 0.125 vs 0.094 ms for 180k rows).
 
+// 33 - 48 columns with long K (the 42 / 44-channel convs): a 48-wide tile, whose MMAs take three quarters of the time of a
+// 64-wide one; only with two row tiles per unit, which is what K > 256 selects below.
 static int tc_bn_for(int N, int K) {
     if (N <= 32) return 32;
+    if (N <= 48 && K > 256) return 48;
     if (N <= 64) return 64;
     return (K > 128 && K <= 192) ? 64 : 128;
 }
@@ -935,6 +938,8 @@ static int tc_dispatch_linear(Loader ld, const float* wprep, int K, int N, int r
     const int n_tiles = npad / bn;
     if (long_k && bn == 128) return tc_launch<128, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
     if (long_k && bn == 64) return tc_launch<64, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+    if (long_k && bn == 48) return tc_launch<48, 2, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
+    if (bn == 48) return SPGT_ERR_SHAPE;              // (48-wide images are only prepared for K > 256)
     switch (bn) {
         case 32: return tc_launch<32, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
         case 64: return tc_launch<64, 1, Loader, EPI_LINEAR, TcLinearEpi>(ld, wprep, kpad, rows, n_tiles, ep, st);
