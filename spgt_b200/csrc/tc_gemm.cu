@@ -44,6 +44,7 @@ __host__ __device__ constexpr int tc_cols_per_thread(int bn, int mt, bool colspl
 struct TcRing {
     uint32_t s = 0, ph = 0;
     template <int N> __device__ __forceinline__ void next() { if (++s == (uint32_t)N) { s = 0; ph ^= 1u; } }
+    __device__ __forceinline__ void next_of(uint32_t n) { if (++s == n) { s = 0; ph ^= 1u; } }
 };
 
 // ---- A-operand loaders.  A loader thread copies 16-byte chunk (t & 7) of rows (t >> 3) + 16 i of every tile:
@@ -237,7 +238,7 @@ template <class Loader, int MT, int BN> __host__ __device__ constexpr int tc_epi
     return Loader::EPI_COLSPLIT ? ((MT == 2 && BN == 128) ? 2 : 1) : Loader::EPI_GROUPS;
 }
 
-template <int BN, int MT, class Loader = TcDense> struct TcCfg {
+template <int BN, int MT, class Loader = TcDense, int EPI = EPI_LINEAR> struct TcCfg {
     // Column tiles of up to 64: W_hi and W_lo of a k-block lie one after the other in shared memory, so one MMA of
     // twice the width computes A_hi W_hi and A_hi W_lo side by side (two partial accumulators, summed by the epilogue)
     // and a k-step of 8 takes two MMA instructions instead of three; the issuing thread is what limits these tiles.
@@ -252,13 +253,17 @@ template <int BN, int MT, class Loader = TcDense> struct TcCfg {
     static constexpr int SB = Loader::W_STAGES ? Loader::W_STAGES
                                                : ((BN == 128) ? (MT == 1 ? 4 : 3) : ((MT == 1 || BN == 32) ? 8 : 6));  // W stages in shared memory
     static constexpr int RAW_BYTES = MT * TC_BM * TC_BK * 4;        // raw fp32 A tile(s) of one k-block
-    static constexpr int SR = Loader::RAW_STAGES ? Loader::RAW_STAGES : ((MT == 1) ? 3 : 2);   // raw A stages in shared memory
+    // Raw A stages in shared memory.  Epilogues without staging rows (PROJ, HEAD) spend that memory on two more stages: the
+    // dense kernels are bound by the bytes they keep in flight.  At run time the stages of the W ring that a resident W does
+    // not need are added to the raw ring as well (up to eight stages).
+    static constexpr bool EPI_STAGING = Loader::STAGING && EPI == EPI_LINEAR;
+    static constexpr int SR = Loader::RAW_STAGES ? Loader::RAW_STAGES : ((MT == 1) ? ((!EPI_STAGING && BN == 128) ? 5 : 3) : 2);
     static constexpr bool CS = Loader::EPI_COLSPLIT && MT == 2 && BN == 128;     // sixteen epilogue warps share every unit
     static constexpr int EG = tc_epi_groups<Loader, MT, BN>();
     static constexpr int CPT = tc_cols_per_thread(BN, MT, CS);      // columns an epilogue thread finishes
     static constexpr int PASS = CS ? 16 : (CPT > 32 ? (CPT % 32 == 0 ? 32 : 16) : CPT);    // columns per staging pass of the LINEAR epilogue
     static constexpr int SLOT_BYTES = PASS * 4 + 16;                // per-epilogue-thread staging row + 16 bytes (bank skew)
-    static constexpr int STAGING_BYTES = Loader::STAGING ? 32 * EG * TC_EPI_WARPS * SLOT_BYTES : 0;
+    static constexpr int STAGING_BYTES = EPI_STAGING ? 32 * EG * TC_EPI_WARPS * SLOT_BYTES : (EPI == EPI_HEAD ? 1024 : 0);   // (HEAD: [2][128] partial row sums)
     static constexpr int CONST_BYTES = 2048;                        // per-CTA epilogue constants (bias, LayerNorm affine, head vectors)
     static constexpr int BAR_BYTES = 384;
     static constexpr int PLAIN_BYTES = Loader::W_CONVERT ? 4 * 32 * 32 * 4 : 0;       // ring of plain W blocks (after the barriers)
@@ -269,7 +274,7 @@ template <int BN, int MT, class Loader = TcDense> struct TcCfg {
 template <int BN, int MT, class Loader, int EPI, class EpiParams>
 __global__ void __launch_bounds__(tc_threads(MT, tc_epi_groups<Loader, MT, BN>()), 1)
 tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_units, EpiParams ep) {
-    using C = TcCfg<BN, MT, Loader>;
+    using C = TcCfg<BN, MT, Loader, EPI>;
     constexpr int SA = C::SA, NBUF = C::NBUF, SR = C::SR;
     constexpr int SB = C::SB;
     constexpr uint32_t B_STAGE = C::B_BYTES;
@@ -281,8 +286,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // 1024-aligned for the 128B swizzle
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint8_t* raw = smem + C::SB * C::B_BYTES;                                      // raw A ring (1024-aligned stages)
-    uint8_t* staging = raw + SR * C::RAW_BYTES;
+    uint8_t* staging = smem + C::SB * C::B_BYTES + SR * C::RAW_BYTES;
     float* consts = reinterpret_cast<float*>(staging + C::STAGING_BYTES);
     uint8_t* bar_mem = staging + C::STAGING_BYTES + C::CONST_BYTES;
     const uint32_t bars = smem_u32(bar_mem);
@@ -303,10 +307,17 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     const int KB = kpad / TC_BK;
     const int KBA = Loader::CONST_A ? KB - 1 : KB;                   // k-blocks whose A operand passes through the rings
     const bool resident = !Loader::W_PER_UNIT && KB <= SB;          // the whole column tile of W stays in shared memory
+    // Raw A ring (1024-aligned stages): it begins after the W stages in use, so a resident W of fewer than SB k-blocks
+    // leaves its unused stages to the raw ring.
+    const int sb_used = resident ? KB : SB;
+    int sr_n = SR + ((SB - sb_used) * C::B_BYTES) / C::RAW_BYTES;
+    if (sr_n > 8) sr_n = 8;
+    const uint32_t SRn = (uint32_t)sr_n;
+    uint8_t* raw = smem + sb_used * C::B_BYTES;
 
     if (tid == 0) {
         for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), NIWARPS); }
-        for (int s = 0; s < SR; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
+        for (int s = 0; s < 8; ++s) { mbar_init(raw_full(s), 128); mbar_init(raw_empty(s), 128); }
         for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), NIWARPS); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), NIWARPS); mbar_init(acc_empty(b), 32 * TC_EPI_WARPS * (CS ? 2 : 1)); }
         *abort_flag = 0;
@@ -397,7 +408,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
             for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) rs[m][i] = ld.row_state(row0 + m * TC_BM + 16 * i);
-            for (int kb = 0; kb < KBA; ++kb, rr.template next<SR>()) {
+            for (int kb = 0; kb < KBA; ++kb, rr.next_of(SRn)) {
                 const uint32_t sr = rr.s, ph = rr.ph;
                 bool okw; okw = mbar_wait(raw_empty(sr), ph ^ 1, abort_flag, 1, &g_tc_status);
                 if (!okw) { alive = false; break; }
@@ -427,7 +438,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         for (int c = 0; c < 8; ++c) roff[c] = tc_swz(r, c);
         const int64_t total = (int64_t)n_my_units * KBA;
         TcRing rr, ra;
-        for (int64_t slot = 0; slot < total; ++slot, rr.template next<SR>(), ra.template next<SA>()) {
+        for (int64_t slot = 0; slot < total; ++slot, rr.next_of(SRn), ra.template next<SA>()) {
             const uint32_t sr = rr.s, pr = rr.ph;
             const uint32_t sa = ra.s, pa = ra.ph;
             bool ok1, ok2;
@@ -922,13 +933,13 @@ template <int BN, int MT, class Loader, int EPI, class EpiParams>
 static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_tiles, const EpiParams& ep, cudaStream_t st) {
     static SmemOptIn configured;
     auto kern = tc_gemm_kernel<BN, MT, Loader, EPI, EpiParams>;
-    if (int e = smem_opt_in(kern, TcCfg<BN, MT, Loader>::BYTES, configured)) return e;
+    if (int e = smem_opt_in(kern, TcCfg<BN, MT, Loader, EPI>::BYTES, configured)) return e;
     const int m_units = ceil_div(rows, TC_BM * MT);
     int per_nt = num_sms() / n_tiles;                 // CTAs per column tile
     if (per_nt < 1) per_nt = 1;
     if (per_nt > m_units) per_nt = m_units;
     const int grid = per_nt * n_tiles;
-    kern<<<grid, tc_threads(MT, tc_epi_groups<Loader, MT, BN>()), TcCfg<BN, MT, Loader>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
+    kern<<<grid, tc_threads(MT, tc_epi_groups<Loader, MT, BN>()), TcCfg<BN, MT, Loader, EPI>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
     return launch_status();
 }
 
