@@ -170,9 +170,13 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         const bool k_warp = q * 32 < D;                                 // this warp owns at least one valid K row
         const int krow_rd = krow < AT_RROWS ? krow : AT_RROWS - 1;      // lanes beyond dpk read an allocated row; their TMEM lanes are never used
         const int ksh = sh_tab[krow_rd];
-        int vrow[3], vsh[3];
+        // The V operand is converted by the warps that own no K row (the K warps' conversion of one row per thread is the
+        // longest chain of a sub-tile): NV threads, eight per row, VN rows each.
+        constexpr int NKQ = (D + 31) / 32, NV = (4 - NKQ) * 32, VR = NV / 8, VN = (D + VR - 1) / VR;
+        const int tv = t - NKQ * 32;                                    // index among the V threads (negative: a K warp)
+        int vrow[VN], vsh[VN];
 #pragma unroll
-        for (int n = 0; n < 3; ++n) { vrow[n] = (t >> 3) + 16 * n; vsh[n] = vrow[n] < D ? sh_tab[vrow[n]] : 0; }
+        for (int n = 0; n < VN; ++n) { vrow[n] = (tv >> 3) + VR * n; vsh[n] = (tv >= 0 && vrow[n] < D) ? sh_tab[vrow[n]] : 0; }
         for (int it = 0; it < nmine; ++it) {
             const uint32_t st = (uint32_t)(it % AT_NR), ph = (uint32_t)((it / AT_NR) & 1);
             const uint32_t so = (uint32_t)(it & 1), po = (uint32_t)((it >> 1) & 1);
@@ -197,36 +201,51 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 }
             }
             if (!mbar_wait(raw_full(st), ph, abort_flag, 2, &g_attn_status)) break;
-            if (!mbar_wait(op_empty(so), po ^ 1, abort_flag, 9, &g_attn_status)) break;    // MMAs two sub-tiles back are done
+            // The operand stage is free once the MMAs two sub-tiles back are done.  The question is asked here, the answer is needed
+            // only before the first store: the splits below run while it is on its way.
+            const uint32_t op_ok = mbar_test_wait(op_empty(so), po ^ 1);
             const float* kraw = reinterpret_cast<const float*>(smem + st * AT_RAW_STAGE);
             const float* vraw = kraw + AT_RROWS * AT_RP;
             uint8_t* vhi = opr + so * (2 * AT_TILE);
             uint8_t* vlo = vhi + AT_TILE;
-            // V: raw rows -> hi / lo B operands (row = j, 32 k-values = grid nodes, 128B swizzle)
+            if (!k_warp) {
+                // V: raw rows -> hi / lo B operands (row = j, 32 k-values = grid nodes, 128B swizzle)
+                uint32_t h[VN][4], l[VN][4];
 #pragma unroll
-            for (int n = 0; n < 3; ++n) {
-                if (vrow[n] < D) {
-                    const float* p = vraw + vrow[n] * AT_RP + vsh[n] + 4 * (t & 7);
-                    uint32_t h[4], l[4];
-                    split_tf32_rn(p[0], h[0], l[0]); split_tf32_rn(p[1], h[1], l[1]); split_tf32_rn(p[2], h[2], l[2]); split_tf32_rn(p[3], h[3], l[3]);
-                    const uint32_t off = tc_swz(vrow[n], t & 7);
-                    *reinterpret_cast<uint4*>(vhi + off) = make_uint4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<uint4*>(vlo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                for (int n = 0; n < VN; ++n) {
+                    if (vrow[n] < D) {
+                        const float* p = vraw + vrow[n] * AT_RP + vsh[n] + 4 * (tv & 7);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) split_tf32_rn(p[e], h[n][e], l[n][e]);
+                    }
                 }
-            }
-            // K: one row per thread into tensor memory (stage `so`, freed together with the V operands)
-            if (k_warp) {
-                tc_fence_after();
+                if (!op_ok && !mbar_wait(op_empty(so), po ^ 1, abort_flag, 9, &g_attn_status)) break;
+#pragma unroll
+                for (int n = 0; n < VN; ++n) {
+                    if (vrow[n] < D) {
+                        const uint32_t off = tc_swz(vrow[n], tv & 7);
+                        *reinterpret_cast<uint4*>(vhi + off) = make_uint4(h[n][0], h[n][1], h[n][2], h[n][3]);
+                        *reinterpret_cast<uint4*>(vlo + off) = make_uint4(l[n][0], l[n][1], l[n][2], l[n][3]);
+                    }
+                }
+            } else {
+                // K: one row per thread into tensor memory (stage `so`, freed together with the V operands)
                 const uint32_t a_hi = tmem_base + lane_addr + AT_A1_COL + so * 64;
                 const float* p = kraw + krow_rd * AT_RP + ksh;
+                bool ok = true;
 #pragma unroll
                 for (int h2 = 0; h2 < 2; ++h2) {
                     uint32_t hi[16], lo[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) split_tf32_rn(p[16 * h2 + j], hi[j], lo[j]);
+                    if (h2 == 0) {
+                        if (!op_ok && !mbar_wait(op_empty(so), po ^ 1, abort_flag, 9, &g_attn_status)) { ok = false; break; }
+                        tc_fence_after();
+                    }
                     tc_st16(a_hi + 16 * h2, hi);
                     tc_st16(a_hi + 32 + 16 * h2, lo);
                 }
+                if (!ok) break;
             }
             mbar_arrive(raw_empty(st));                                 // this thread has read the raw stage
             if (k_warp) { tc_wait_st(); tc_fence_before(); }
