@@ -177,8 +177,8 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
         int vrow[VN], vsh[VN];
 #pragma unroll
         for (int n = 0; n < VN; ++n) { vrow[n] = (tv >> 3) + VR * n; vsh[n] = (tv >= 0 && vrow[n] < D) ? sh_tab[vrow[n]] : 0; }
-        for (int it = 0; it < nmine; ++it) {
-            const uint32_t st = (uint32_t)(it % AT_NR), ph = (uint32_t)((it / AT_NR) & 1);
+        uint32_t st = 0, ph = 0;                                      // raw ring position, advanced without division
+        for (int it = 0; it < nmine; ++it, st = (st + 1 == AT_NR ? 0u : st + 1), ph ^= (st == 0 ? 1u : 0u)) {
             const uint32_t so = (uint32_t)(it & 1), po = (uint32_t)((it >> 1) & 1);
             if (k_warp && it > 0 && it % AT_FLUSH == 0) {
                 // The accumulate step of an MMA truncates, so the error of one long chain grows with its length (worst for
@@ -237,7 +237,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
                 for (int h2 = 0; h2 < 2; ++h2) {
                     uint32_t hi[16], lo[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) split_tf32_rn(p[16 * h2 + j], hi[j], lo[j]);
+                    for (int j = 0; j < 16; ++j) split_tf32(p[16 * h2 + j], hi[j], lo[j]);
                     if (h2 == 0) {
                         if (!op_ok && !mbar_wait(op_empty(so), po ^ 1, abort_flag, 9, &g_attn_status)) { ok = false; break; }
                         tc_fence_after();
@@ -249,7 +249,7 @@ galerkin_attn_tc_kernel(const float* __restrict__ Q, const float* __restrict__ K
             }
             mbar_arrive(raw_empty(st));                                 // this thread has read the raw stage
             if (k_warp) { tc_wait_st(); tc_fence_before(); }
-            fence_proxy_async();
+            else fence_proxy_async();                                   // the V tiles were written with ordinary stores
             mbar_arrive(op_full(so));
         }
     } else {
