@@ -511,30 +511,43 @@ skinny_streamk_kernel(const float* __restrict__ A, const float* __restrict__ B, 
 #pragma unroll
             for (int h = 0; h < 2; ++h) a_sh[i][h] = (int)((a_row0 + (int64_t)(16 * i + g + 8 * h) * K) & 3);
 
+        // What a thread copies is the same for every slice but for the k offset, so the per-chunk values are computed once per
+        // item: the aligned source of A chunk idx = lane + 32 n -> (row, chunk in row) at this warp's first slice, and the
+        // elements from there to the end of the row (0 for rows beyond M).  This warp's slices are SKS_WARPS * SKS_K apart, a
+        // multiple of four elements, so the alignment shift of a row is the same in every slice.  (The address arithmetic was
+        // 40 % of the instructions of a slice.)
+        const int k00 = (sub0 + warp) * SKS_K;
+        const float* a_src[5];
+        int a_rem[5];
+        uint32_t a_dst[5];
+#pragma unroll
+        for (int n = 0; n < 5; ++n) {
+            const int idx = lane + 32 * n, row = idx / 5, ch = idx - 5 * row;
+            const int64_t e = a_row0 + (int64_t)row * K + k00;           // element index of the first wanted element
+            const int64_t start = (e & ~(int64_t)3) + 4 * ch;
+            int64_t rem = (tm * 32 + row < M) ? (a_row0 + (int64_t)row * K + K - start) : 0;
+            rem = rem < 0 ? 0 : (rem > 0x7fffffff ? 0x7fffffff : rem);
+            a_src[n] = A + start; a_rem[n] = (int)rem; a_dst[n] = (uint32_t)((row * SKS_AP + 4 * ch) * 4);
+        }
+        const int b_r4 = lane >> 3, b_c4 = (lane & 7) * 4;
+        const bool b_col_ok = tn * 32 + b_c4 < N;                        // N % 4 == 0: a chunk is all inside or all outside
+        const float* b_src = Bg + (int64_t)(k00 + b_r4) * N + (b_col_ok ? tn * 32 + b_c4 : 0);
         auto load = [&](int it, int stage) {
-            const int k0 = (sub0 + warp + it * SKS_WARPS) * SKS_K;
+            const int koff = it * (SKS_WARPS * SKS_K);
             float* as = wreg + stage * SKS_STAGE;
             float* bs = as + 32 * SKS_AP;
+            const uint32_t as_u = smem_u32(as);
 #pragma unroll
-            for (int n = 0; n < 5; ++n) {                                 // chunk idx = lane + 32 n -> (row, chunk in row)
-                const int idx = lane + 32 * n, row = idx / 5, ch = idx - 5 * row;
-                const int m = tm * 32 + row;
-                const int64_t e = a_row0 + (int64_t)row * K + k0;        // element index of the first wanted element
-                const int64_t start = (e & ~(int64_t)3) + 4 * ch;
-                int64_t valid = (m < M) ? (a_row0 + (int64_t)row * K + K - start) : 0;   // elements up to the end of the row
+            for (int n = 0; n < 5; ++n) {
+                int valid = a_rem[n] - koff;
                 valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(as + row * SKS_AP + 4 * ch)),
-                             "l"(valid > 0 ? A + start : A), "r"((int)valid * 4) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(as_u + a_dst[n]),
+                             "l"(valid > 0 ? a_src[n] + koff : A), "r"(valid * 4) : "memory");
             }
-            {
-                const int r4 = lane >> 3, c4 = (lane & 7) * 4;
-                const int n = tn * 32 + c4;
 #pragma unroll
-                for (int i = 0; i < SKS_K / 4; ++i) {
-                    const int k = k0 + i * 4 + r4;
-                    const bool ok = k < K && n < N;                      // N % 4 == 0: a chunk is all inside or all outside
-                    cp_async_zfill<16>(bs + (i * 4 + r4) * SKS_BP + c4, Bg + (int64_t)(ok ? k : 0) * N + (ok ? n : 0), ok);
-                }
+            for (int i = 0; i < SKS_K / 4; ++i) {
+                const bool ok = b_col_ok && k00 + koff + i * 4 + b_r4 < K;
+                cp_async_zfill<16>(bs + (i * 4 + b_r4) * SKS_BP + b_c4, ok ? b_src + (int64_t)(koff + i * 4) * N : Bg, ok);
             }
             cp_async_commit();
         };
