@@ -83,6 +83,7 @@ struct TcDense : TcLoaderDefaults {
     const float* x; int lda; int rows; int K;
     __device__ __forceinline__ const float* w_src(const float* wtile, int, int kb, int stage_floats) const { return wtile + (int64_t)kb * stage_floats; }
     __device__ __forceinline__ int64_t out_row(int row) const { return row < rows ? row : -1; }
+    __device__ __forceinline__ int out_valid(int row0) const { return rows - row0; }
     struct Row { const float* p; bool ok; };
     struct Kst { int kc; bool ok; };
     __device__ __forceinline__ Row row_state(int row) const {
@@ -98,6 +99,7 @@ struct TcConv : TcLoaderDefaults {          // 3x3, padding 1, NHWC; k = tap * C
     const float* x; int cin_pitch, cin_off, Cin, Hh, Ww; int rows; int K;
     __device__ __forceinline__ const float* w_src(const float* wtile, int, int kb, int stage_floats) const { return wtile + (int64_t)kb * stage_floats; }
     __device__ __forceinline__ int64_t out_row(int row) const { return row < rows ? row : -1; }
+    __device__ __forceinline__ int out_valid(int row0) const { return rows - row0; }
     struct Row { const float* p; uint32_t mask; };     // bit tap of mask: the tap's source pixel lies inside the image
     struct Kst { int off; int tap; };
     __device__ __forceinline__ Row row_state(int row) const {
@@ -146,6 +148,10 @@ struct TcSpecInv : TcLoaderDefaults {
         const int u = row >> 8, img = u / upr, y = (u - img * upr) * 256 + (row & 255);
         return (row < rows && y < r) ? (int64_t)img * r + y : -1;
     }
+    __device__ __forceinline__ int out_valid(int row0) const {
+        const int u = row0 >> 8, img = u / upr, y = (u - img * upr) * 256 + (row0 & 255);
+        return row0 < rows ? r - y : 0;
+    }
     struct Row { const float* px; const float* pf; bool ok; };
     struct Kst { int kb; int c4; };
     __device__ __forceinline__ Row row_state(int row) const {
@@ -180,6 +186,7 @@ struct TcSpecInvC : TcLoaderDefaults {
         const int y = row & 255;
         return (row < rows && y < r) ? (int64_t)(row >> 8) * r + y : -1;
     }
+    __device__ __forceinline__ int out_valid(int row0) const { return row0 < rows ? r - (row0 & 255) : 0; }
     __device__ __forceinline__ const float* const_row(int row_in_unit) const { return f3 + (int64_t)row_in_unit * 32; }
     struct Row { const float* px; bool ok; };
     struct Kst { int c4; };
@@ -204,6 +211,7 @@ struct TcSpecFwd : TcLoaderDefaults {
     const float* x; int r; int64_t nimg; int rows; int K;
     __device__ __forceinline__ const float* w_src(const float* wtile, int, int kb, int stage_floats) const { return wtile + (int64_t)kb * stage_floats; }
     __device__ __forceinline__ int64_t out_row(int row) const { return row < rows ? row : -1; }
+    __device__ __forceinline__ int out_valid(int row0) const { return rows - row0; }
     struct Row { const float* p; int y; bool ok; };
     struct Kst { int kb; int c4; };
     __device__ __forceinline__ Row row_state(int row) const {
@@ -715,6 +723,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 constexpr int RPI = 32 / LPR;                    // rows per store instruction
                 const uint8_t* warp_stage = staging + ew * 32 * C::SLOT_BYTES;
                 const int tile_row0 = tile * TC_BM + q * 32;
+                const int64_t out_base = ld.out_row(tile_row0);          // (-1 with out_nvalid <= 0: nothing is stored)
+                const int out_nvalid = ld.out_valid(tile_row0);
                 // One pass (at most 32 columns per thread): the thread first takes its whole accumulator row into registers
                 // and frees the buffer, so the next unit's MMAs start while this one is finished and stored.
                 // (with two buffers the early release measured slower, with one and with two epilogue groups: 396 against 378 us
@@ -777,13 +787,15 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                                 }
                             }
                         } else {
-#pragma unroll 4
+                            // The 32 GEMM rows of this warp map to consecutive output rows (out_base onwards, the first
+                            // out_nvalid of them exist): one address per pass, a constant stride per store.
+                            float* yp = e.y + (out_base + lane / LPR) * e.ldc + col;
+                            const uint8_t* sp = warp_stage + (lane / LPR) * C::SLOT_BYTES + (lane % LPR) * 16;
+#pragma unroll
                             for (int i = 0; i < 32 / RPI; ++i) {
-                                const int rr = i * RPI + lane / LPR;
-                                const int64_t orow = ld.out_row(tile_row0 + rr);
-                                if (orow >= 0)
-                                    *reinterpret_cast<float4*>(e.y + orow * e.ldc + col) =
-                                        *reinterpret_cast<const float4*>(warp_stage + rr * C::SLOT_BYTES + (lane % LPR) * 16);
+                                if (i * RPI + lane / LPR < out_nvalid)
+                                    *reinterpret_cast<float4*>(yp + (int64_t)(i * RPI) * e.ldc) =
+                                        *reinterpret_cast<const float4*>(sp + i * RPI * C::SLOT_BYTES);
                             }
                         }
                     }
