@@ -39,7 +39,7 @@ GLOBAL_BATCH = 64
 CPU_SAMPLE = 8                     # samples per forward of the CPU legs (a bounded sample of the 64-sample step)
 # DRAM bytes (read + write) of one launch at batch 64 from the committed ncu summaries of these kernels; they grow in
 # proportion to the batch, so a rank that holds 64/N samples is charged 1/N of them.
-ATTN_TRAFFIC_BYTES_B64 = 342_400_000
+ATTN_TRAFFIC_BYTES_B64 = 343_600_000
 SPECTRAL_TRAFFIC_BYTES_B64 = 1_174_600_000
 
 
