@@ -242,7 +242,8 @@ struct TcHeadEpi {
 struct TcSpecFwdEpi { float* y1; int J; int64_t nimg; };     // Y1 [image row][J][32 channels]
 enum { EPI_LINEAR = 0, EPI_PROJ = 1, EPI_HEAD = 2, EPI_SPECF = 3 };
 
-template <class Loader, int MT, int BN> __host__ __device__ constexpr int tc_epi_groups() {
+template <class Loader, int MT, int BN, int EPI = EPI_LINEAR> __host__ __device__ constexpr int tc_epi_groups() {
+    if (EPI == EPI_HEAD) return MT == 1 ? 2 : 1;     // the decoder head: 128 activations per row and one k-block, the epilogue is the longest stage
     return Loader::EPI_COLSPLIT ? ((MT == 2 && BN == 128) ? 2 : 1) : Loader::EPI_GROUPS;
 }
 
@@ -267,11 +268,11 @@ template <int BN, int MT, class Loader = TcDense, int EPI = EPI_LINEAR> struct T
     static constexpr bool EPI_STAGING = Loader::STAGING && EPI == EPI_LINEAR;
     static constexpr int SR = Loader::RAW_STAGES ? Loader::RAW_STAGES : ((MT == 1) ? ((!EPI_STAGING && BN == 128) ? 5 : 3) : 2);
     static constexpr bool CS = Loader::EPI_COLSPLIT && MT == 2 && BN == 128;     // sixteen epilogue warps share every unit
-    static constexpr int EG = tc_epi_groups<Loader, MT, BN>();
+    static constexpr int EG = tc_epi_groups<Loader, MT, BN, EPI>();
     static constexpr int CPT = tc_cols_per_thread(BN, MT, CS);      // columns an epilogue thread finishes
     static constexpr int PASS = CS ? 16 : (CPT > 32 ? (CPT % 32 == 0 ? 32 : 16) : CPT);    // columns per staging pass of the LINEAR epilogue
     static constexpr int SLOT_BYTES = PASS * 4 + 16;                // per-epilogue-thread staging row + 16 bytes (bank skew)
-    static constexpr int STAGING_BYTES = EPI_STAGING ? 32 * EG * TC_EPI_WARPS * SLOT_BYTES : (EPI == EPI_HEAD ? 1024 : 0);   // (HEAD: [2][128] partial row sums)
+    static constexpr int STAGING_BYTES = EPI_STAGING ? 32 * EG * TC_EPI_WARPS * SLOT_BYTES : (EPI == EPI_HEAD ? 2048 : 0);   // (HEAD: [2 units][2 groups][128] partial row sums)
     static constexpr int CONST_BYTES = 2048;                        // per-CTA epilogue constants (bias, LayerNorm affine, head vectors)
     static constexpr int BAR_BYTES = 384;
     static constexpr int PLAIN_BYTES = Loader::W_CONVERT ? 4 * 32 * 32 * 4 : 0;       // ring of plain W blocks (after the barriers)
@@ -280,7 +281,7 @@ template <int BN, int MT, class Loader = TcDense, int EPI = EPI_LINEAR> struct T
 };
 
 template <int BN, int MT, class Loader, int EPI, class EpiParams>
-__global__ void __launch_bounds__(tc_threads(MT, tc_epi_groups<Loader, MT, BN>()), 1)
+__global__ void __launch_bounds__(tc_threads(MT, tc_epi_groups<Loader, MT, BN, EPI>()), 1)
 tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, int n_tiles, int m_units, EpiParams ep) {
     using C = TcCfg<BN, MT, Loader, EPI>;
     constexpr int SA = C::SA, NBUF = C::NBUF, SR = C::SR;
@@ -290,7 +291,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
     constexpr int EG = C::EG;
     constexpr bool CS = C::CS;
     constexpr int TC_THREADS = tc_threads(MT, EG), TC_EPI_WARP0 = tc_epi_warp0(MT);
-    static_assert(EG == 1 || (EG == 2 && (CS || C::NBUF == 2) && EPI == EPI_LINEAR), "two epilogue groups: one per accumulator buffer, or sharing every unit");
+    static_assert(EG == 1 || (EG == 2 && (CS || C::NBUF == 2) && (EPI == EPI_LINEAR || EPI == EPI_HEAD)), "two epilogue groups: one per accumulator buffer, or sharing every unit");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // 1024-aligned for the 128B swizzle
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -868,7 +869,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                 }
             } else {
                 const TcHeadEpi& e = ep;
-                float* part = reinterpret_cast<float*>(staging);                 // [2][128] partial row sums
+                // partial row sums of the second column half: one slot per (unit parity within the group, group)
+                float* part = reinterpret_cast<float*>(staging) + (((ui / UI_STEP) & 1) * 2 + egroup) * 128;
                 const float4* cb = reinterpret_cast<const float4*>(consts);      // b1[128] then w2[128]
                 float acc = 0.0f;
 #pragma unroll 1
@@ -891,10 +893,10 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     else if (e.act == SPGT_ACT_SILU2) dot([](float x) { return silu_f(silu_f(x)); });
                     else dot([](float x) { return x; });
                 }
-                if (half == 1) part[(ui & 1) * 128 + r_in_tile] = acc;
-                asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");   // epilogue warps only
+                if (half == 1) part[r_in_tile] = acc;
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + egroup), "n"(32 * TC_EPI_WARPS) : "memory");   // the eight epilogue warps of this group
                 if (half == 0 && row < rows) {
-                    acc += part[(ui & 1) * 128 + r_in_tile];
+                    acc += part[r_in_tile];
                     e.out[row] = head_edge ? 0.0f : (acc + e.b2) * head_sc + head_sh;
                 }
             }
@@ -951,7 +953,7 @@ static int tc_launch(Loader ld, const float* wimg, int kpad, int rows, int n_til
     if (per_nt < 1) per_nt = 1;
     if (per_nt > m_units) per_nt = m_units;
     const int grid = per_nt * n_tiles;
-    kern<<<grid, tc_threads(MT, tc_epi_groups<Loader, MT, BN>()), TcCfg<BN, MT, Loader, EPI>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
+    kern<<<grid, tc_threads(MT, tc_epi_groups<Loader, MT, BN, EPI>()), TcCfg<BN, MT, Loader, EPI>::BYTES, st>>>(ld, wimg, kpad, rows, n_tiles, m_units, ep);
     return launch_status();
 }
 
