@@ -95,6 +95,35 @@ __device__ __forceinline__ void tc_mma_tf32_ts_p(uint32_t d_tmem, uint32_t a_tme
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], bd, %4, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same three, executed by a whole warp with one issuing lane: `leader` is non-zero in that lane only.  The warp stays
+// converged around them (the guard is a predicate, not a branch).
+__device__ __forceinline__ void tc_mma_tf32_ts_acc_w(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t b_desc_hi, uint32_t idesc,
+                                                     uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred p, g;\n\t.reg .b64 bd;\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "setp.ne.b32 g, %5, 0;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "@g tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], bd, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32_ts_p_w(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t b_desc_hi, uint32_t idesc,
+                                                   uint32_t accumulate, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred p, g;\n\t.reg .b64 bd;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "setp.ne.b32 g, %6, 0;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "@g tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], bd, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void tc_commit_w(uint32_t bar, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred g;\n\t"
+        "setp.ne.b32 g, %1, 0;\n\t"
+        "@g tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(leader) : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t* u = reinterpret_cast<uint32_t*>(v);
     asm volatile(

@@ -590,7 +590,8 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
         const uint32_t b_off = (MT == 2) ? 0u : (uint32_t)(iw * NI * 128);   // NI rows of 128 bytes
         // Only lane 0 runs the loop (waits included): no divergence and reconvergence per k-block.  The B descriptors
         // differ between stages only in the address field of their low word, so they are advanced with 32-bit adds.
-        if (lane == 0) {
+        {
+            const uint32_t leader = lane == 0 ? 1u : 0u;      // the whole warp runs the loop, this lane issues
             const uint64_t desc0 = tc_smem_desc(smem_base + b_off);
             const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
             TcRing ra, rb;
@@ -623,31 +624,31 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     if constexpr (C::MERGE) {
                         constexpr uint32_t idesc2 = tc_idesc(2 * NI);           // [W_hi | W_lo] as one operand of twice the rows
                         const int nk8 = (Loader::CONST_A && !a_ring) ? ld.const_ksteps() : TC_BK / 8;   // (zero k-steps of the constant block are skipped)
-                        tc_mma_tf32_ts_p(d, ah, bh, desc_hi, idesc2, ki > 0 ? 1u : 0u);
-                        tc_mma_tf32_ts_acc(d, al, bh, desc_hi, idesc);
+                        tc_mma_tf32_ts_p_w(d, ah, bh, desc_hi, idesc2, ki > 0 ? 1u : 0u, leader);
+                        tc_mma_tf32_ts_acc_w(d, al, bh, desc_hi, idesc, leader);
 #pragma unroll
                         for (int k8 = 1; k8 < TC_BK / 8; ++k8) {
                             if (k8 < nk8) {
-                                tc_mma_tf32_ts_acc(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc2);
-                                tc_mma_tf32_ts_acc(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc);
+                                tc_mma_tf32_ts_acc_w(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc2, leader);
+                                tc_mma_tf32_ts_acc_w(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc, leader);
                             }
                         }
                     } else {
-                    tc_mma_tf32_ts_p(d, al, bh, desc_hi, idesc, ki > 0 ? 1u : 0u);
-                    tc_mma_tf32_ts_acc(d, ah, bl, desc_hi, idesc);
-                    tc_mma_tf32_ts_acc(d, ah, bh, desc_hi, idesc);
+                    tc_mma_tf32_ts_p_w(d, al, bh, desc_hi, idesc, ki > 0 ? 1u : 0u, leader);
+                    tc_mma_tf32_ts_acc_w(d, ah, bl, desc_hi, idesc, leader);
+                    tc_mma_tf32_ts_acc_w(d, ah, bh, desc_hi, idesc, leader);
 #pragma unroll
                     for (int k8 = 1; k8 < TC_BK / 8; ++k8) {          // 32 bytes (2 descriptor units) and 8 TMEM columns per k-step
-                        tc_mma_tf32_ts_acc(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc);
-                        tc_mma_tf32_ts_acc(d, ah + k8 * 8, bl + k8 * 2, desc_hi, idesc);
-                        tc_mma_tf32_ts_acc(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc);
+                        tc_mma_tf32_ts_acc_w(d, al + k8 * 8, bh + k8 * 2, desc_hi, idesc, leader);
+                        tc_mma_tf32_ts_acc_w(d, ah + k8 * 8, bl + k8 * 2, desc_hi, idesc, leader);
+                        tc_mma_tf32_ts_acc_w(d, ah + k8 * 8, bh + k8 * 2, desc_hi, idesc, leader);
                     }
                     }
                     // the A stage (and a streamed W stage) is reusable once every issuer's MMAs have read it
-                    if (a_ring) { tc_commit(a_empty(sa)); ra.template next<SA>(); }
-                    if (!resident && !tail) { tc_commit(b_empty(sb)); rb.template next<SBR>(); }
+                    if (a_ring) { tc_commit_w(a_empty(sa), leader); ra.template next<SA>(); }
+                    if (!resident && !tail) { tc_commit_w(b_empty(sb), leader); rb.template next<SBR>(); }
                 }
-                if (alive) tc_commit(acc_full(buf));
+                if (alive) tc_commit_w(acc_full(buf), leader);
             }
         }
         __syncwarp();
