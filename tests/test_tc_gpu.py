@@ -16,7 +16,10 @@ def dev():
 
 @pytest.mark.parametrize('rows,K,N,act,res', [(128, 32, 32, None, False), (300, 128, 256, 'relu', False), (257, 256, 128, None, True),
                                               (1000, 136, 128, None, True), (5000, 128, 32, None, False), (77, 32, 44, 'silu', False),
-                                              (40000, 128, 128, 'silu2', True), (1, 64, 64, None, False)])
+                                              (40000, 128, 128, 'silu2', True), (1, 64, 64, None, False),
+                                              # K > 256 (two row tiles per unit): 48-wide, 64-wide and 128-wide column tiles
+                                              (700, 288, 44, 'silu', True), (515, 320, 36, None, False), (300, 288, 64, 'relu', False),
+                                              (513, 384, 128, None, True)])
 def test_linear_tc(dev, rows, K, N, act, res):
     from spgt_b200 import ops
     g = torch.Generator().manual_seed(rows + K)
