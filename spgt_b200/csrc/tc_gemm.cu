@@ -744,6 +744,13 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     tc_fence_before();
                     mbar_arrive(acc_empty(buf));
                 }
+                // One accumulator buffer and more columns than fit in registers: the buffer is freed as soon as its last columns
+                // have been read.  With 16-column passes the last pass's columns are read one pass early (TAIL2), so the MMAs of
+                // the next unit wait for all passes but the last two instead of for all of them.
+                constexpr int NP = CPT / PASS;
+                constexpr bool TAIL = !EARLY && NBUF == 1 && CS;      // (measured slower on the 48 / 64-wide tiles: 289 against 283 us)
+                constexpr bool TAIL2 = TAIL && PASS == 16 && NP >= 2;
+                float vlast[TAIL2 ? 16 : 1];
 #pragma unroll (EARLY ? CPT / PASS : 1)
                 for (int pi = 0; pi < CPT / PASS; ++pi) {
                     const int c0 = col_lo + pi * PASS;
@@ -755,7 +762,21 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
 #pragma unroll
                             for (int j = 0; j < 16; ++j) v[j] = vall[pi * PASS + cc + j];
                         } else {
-                            if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + cc, BN, v); else tc_ld16(taddr + c0 + cc, v);
+                            if (TAIL2 && pi == NP - 1) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) v[j] = vlast[j];
+                            } else {
+                                if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + cc, BN, v); else tc_ld16(taddr + c0 + cc, v);
+                            }
+                            if constexpr (TAIL2) {
+                                if (pi == NP - 2) {
+                                    if constexpr (C::MERGE) tc_ld16_sum(taddr + c0 + PASS, BN, vlast); else tc_ld16(taddr + c0 + PASS, vlast);
+                                    tc_fence_before();
+                                    mbar_arrive(acc_empty(buf));
+                                }
+                            } else if constexpr (TAIL) {
+                                if (pi == NP - 1 && cc + 16 >= PASS) { tc_fence_before(); mbar_arrive(acc_empty(buf)); }
+                            }
                         }
                         // one branch on the activation per 16 columns, not per element (padding columns beyond N carry a
                         // zero bias and are never stored)
@@ -901,7 +922,7 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     e.out[row] = head_edge ? 0.0f : (acc + e.b2) * head_sc + head_sh;
                 }
             }
-            if constexpr (!(EPI == EPI_LINEAR && CPT <= 32 && NBUF == 1)) {     // (else the LINEAR epilogue has freed the buffer already)
+            if constexpr (!(EPI == EPI_LINEAR && NBUF == 1 && (CPT <= 32 || CS))) {     // (else the LINEAR epilogue has freed the buffer already)
                 tc_fence_before();
                 mbar_arrive(acc_empty(buf));
             }
