@@ -464,9 +464,13 @@ tc_gemm_kernel(Loader ld, const float* __restrict__ wimg, int kpad, int rows, in
                     // element k of this thread's row of A is float `lane` of tile row q * 32 + k (consecutive lanes read
                     // consecutive floats of one 128-byte tile row: no bank conflicts)
                     float* vf = reinterpret_cast<float*>(v);
+                    // tile row q * 32 + k: byte offset (4 q + k / 8) * 1024 + (k % 8) * 128, chunk (lane / 4) ^ (k % 8): eight
+                    // per-thread bases (one per k % 8), everything else is a constant offset of the load
+                    const uint8_t* cb[8];
 #pragma unroll
-                    for (int k = 0; k < 32; ++k)
-                        vf[k] = *reinterpret_cast<const float*>(src + tc_swz(q * 32 + k, lane >> 2) + (lane & 3) * 4);
+                    for (int j = 0; j < 8; ++j) cb[j] = src + q * 4096 + j * 128 + (((lane >> 2) ^ j) << 4) + (lane & 3) * 4;
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) vf[k] = *reinterpret_cast<const float*>(cb[k & 7] + (k >> 3) * 1024);
                 }
                 const uint32_t a_hi = tmem_a + lane_addr + (sa * MT + m) * 64;
 #pragma unroll
